@@ -1,0 +1,44 @@
+// The C interface of the kernel library.  Every function launches on `stream`, allocates
+// nothing and returns 0, a cudaError_t value, or one of the WPC_ERR_* codes of common.cuh.
+// Element types are named by WPC_DTYPE_F32 (0) and WPC_DTYPE_BF16 (1).
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+int wpc_embed(const int* tokens, const void* table, int table_dtype, float* out, int T, int H, int V,
+              cudaStream_t stream);
+int wpc_rmsnorm(const float* x, const float* gain, float eps, void* out, int out_dtype, int T, int H,
+                cudaStream_t stream);
+int wpc_silu_mul(const void* gu, void* out, int dtype, int T, int I, cudaStream_t stream);
+int wpc_add(float* x, const void* y, int y_dtype, size_t n, cudaStream_t stream);
+int wpc_gather_rows(const float* x, const int* idx, float* out, int n_rows, int H, int T, cudaStream_t stream);
+int wpc_convert(const void* in, int in_dtype, void* out, int out_dtype, size_t n, cudaStream_t stream);
+int wpc_rope_angles(const int* positions, const double* inv_freq, float* cosv, float* sinv, int T, int R,
+                    cudaStream_t stream);
+int wpc_rope_inplace(void* x, int dtype, int row_stride, int T, int n_heads, int hd, int R, const float* cosv,
+                     const float* sinv, cudaStream_t stream);
+int wpc_qk_rope_kv_store(void* qkv, int dtype, int row_stride, int T, int nh, int nkv, int hd, int R,
+                         const float* cosv, const float* sinv, void* k_pages, void* v_pages,
+                         const int* page_table, int table_width, const int* seq_of_token, const int* positions,
+                         int n_pages, int* status, cudaStream_t stream);
+int wpc_fill_normal(void* out, int dtype, size_t n, uint64_t key, float mean, float std, cudaStream_t stream);
+
+int wpc_gemm_simt(const void* A, int a_dtype, int lda, const void* W, int w_dtype, int ldw, const float* bias,
+                  void* C, int out_dtype, int ldc, int accumulate, int M, int N, int K, cudaStream_t stream);
+
+int wpc_attention_plain(const void* q, int q_stride, void* out, int out_stride, int dtype, const void* k_pages,
+                        const void* v_pages, const int* page_table, int table_width, const int* seq_of_token,
+                        const int* positions, int T, int nh, int nkv, int hd, float scale, int window,
+                        cudaStream_t stream);
+
+int wpc_sample(const float* logits, int n_rows, int V, const int* slots, long long* seq_state, float temperature,
+               const int* banned, int n_banned, int* out, cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif

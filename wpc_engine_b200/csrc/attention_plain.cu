@@ -1,0 +1,105 @@
+// Attention over the paged cache, the plain way: one block per (query token, query head),
+// any head size, any context length, float32 arithmetic with an online softmax over chunks
+// of keys.  It is the attention of the true 32-bit path and the plain twin of the fast
+// kernels (wpc-runtime/src/model.rs:476-510).
+#include "api.h"
+#include "common.cuh"
+
+namespace wpc {
+
+constexpr int AP_THREADS = 128;
+constexpr int AP_CHUNK = 512;        // keys per chunk; their scores live in shared memory
+
+template <typename T>
+__global__ void __launch_bounds__(AP_THREADS)
+attention_plain_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out, int out_stride,
+                       const T* __restrict__ k_pages, const T* __restrict__ v_pages,
+                       const int* __restrict__ page_table, int table_width,
+                       const int* __restrict__ seq_of_token, const int* __restrict__ positions,
+                       int nh, int nkv, int hd, float scale, int window) {
+  extern __shared__ float smem[];
+  float* qs = smem;                    // [hd]
+  float* ps = smem + hd;               // [AP_CHUNK]
+  __shared__ float red[32];
+  const int t = blockIdx.x, h = blockIdx.y;
+  const int kvh = h / (nh / nkv);
+  const int pos = positions[t];
+  const int b = seq_of_token[t];
+  const int* table = page_table + (size_t)b * table_width;
+  const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const int n_keys = pos - lo + 1;
+
+  const T* qrow = q + (size_t)t * q_stride + (size_t)h * hd;
+  for (int d = threadIdx.x; d < hd; d += AP_THREADS) qs[d] = to_float(qrow[d]);
+  __syncthreads();
+
+  float m_run = -INFINITY, l_run = 0.f;
+  float acc[2] = {0.f, 0.f};           // outputs d = tid and d = tid + AP_THREADS (hd <= 256)
+
+  for (int c0 = 0; c0 < n_keys; c0 += AP_CHUNK) {
+    const int cn = min(AP_CHUNK, n_keys - c0);
+    float m_loc = -INFINITY;
+    for (int j = threadIdx.x; j < cn; j += AP_THREADS) {
+      const int p = lo + c0 + j;
+      const int page = table[p / WPC_PAGE];
+      const T* kr = k_pages + (((size_t)page * nkv + kvh) * WPC_PAGE + p % WPC_PAGE) * hd;
+      float dot = 0.f;
+      for (int d = 0; d < hd; ++d) dot = fmaf(qs[d], to_float(kr[d]), dot);
+      dot *= scale;
+      ps[j] = dot;
+      m_loc = fmaxf(m_loc, dot);
+    }
+    m_loc = block_max(m_loc, red);
+    const float m_new = fmaxf(m_run, m_loc);
+    const float corr = (m_run == -INFINITY) ? 0.f : expf(m_run - m_new);
+    float l_loc = 0.f;
+    for (int j = threadIdx.x; j < cn; j += AP_THREADS) {
+      const float e = expf(ps[j] - m_new);
+      ps[j] = e;
+      l_loc += e;
+    }
+    l_loc = block_sum(l_loc, red);       // also orders the writes of ps before the reads below
+    l_run = l_run * corr + l_loc;
+    m_run = m_new;
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int d = threadIdx.x + u * AP_THREADS;
+      if (d < hd) {
+        float a = acc[u] * corr;
+        for (int j = 0; j < cn; ++j) {
+          const int p = lo + c0 + j;
+          const int page = table[p / WPC_PAGE];
+          a = fmaf(ps[j], to_float(v_pages[(((size_t)page * nkv + kvh) * WPC_PAGE + p % WPC_PAGE) * hd + d]), a);
+        }
+        acc[u] = a;
+      }
+    }
+    __syncthreads();
+  }
+  T* orow = out + (size_t)t * out_stride + (size_t)h * hd;
+  const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+#pragma unroll
+  for (int u = 0; u < 2; ++u) {
+    const int d = threadIdx.x + u * AP_THREADS;
+    if (d < hd) orow[d] = from_float<T>(acc[u] * inv);
+  }
+}
+
+}  // namespace wpc
+
+using namespace wpc;
+
+extern "C" int wpc_attention_plain(const void* q, int q_stride, void* out, int out_stride, int dtype,
+                                   const void* k_pages, const void* v_pages, const int* page_table,
+                                   int table_width, const int* seq_of_token, const int* positions, int T, int nh,
+                                   int nkv, int hd, float scale, int window, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (hd < 1 || hd > 2 * AP_THREADS || nkv < 1 || nh % nkv) return WPC_ERR_UNSUPPORTED;
+  const size_t smem = (size_t)(hd + AP_CHUNK) * sizeof(float);
+  dim3 grid(T, nh);
+  WPC_DISPATCH_DTYPE(dtype, Tt,
+                     attention_plain_kernel<Tt><<<grid, AP_THREADS, smem, stream>>>(
+                         (const Tt*)q, q_stride, (Tt*)out, out_stride, (const Tt*)k_pages, (const Tt*)v_pages,
+                         page_table, table_width, seq_of_token, positions, nh, nkv, hd, scale, window));
+  return launch_status();
+}

@@ -1,0 +1,88 @@
+// Shared helpers of the kernels: element types, conversions, reductions, launch checks.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define WPC_DTYPE_F32 0
+#define WPC_DTYPE_BF16 1
+
+// error codes returned by the launchers (besides cudaError_t values, which are < 1000)
+#define WPC_ERR_BAD_ARGUMENT 1001
+#define WPC_ERR_UNSUPPORTED 1002
+#define WPC_ERR_TOO_LARGE 1003
+#define WPC_ERR_DEVICE_WAIT 1004
+
+#define WPC_PAGE 64
+
+namespace wpc {
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block of up to 1024 threads; `red` is shared memory of 32 floats.  All threads
+// get the result.  Fixed order, so a row's result does not depend on its neighbours.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  const int nwarps = (blockDim.x + 31) >> 5;
+  float t = (lane < nwarps) ? red[lane] : 0.f;
+  t = warp_sum(t);
+  return t;
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  const int nwarps = (blockDim.x + 31) >> 5;
+  float t = (lane < nwarps) ? red[lane] : -INFINITY;
+  t = warp_max(t);
+  return t;
+}
+
+__host__ __device__ __forceinline__ uint64_t mix64(uint64_t z) {
+  z += 0x9E3779B97F4A7C15ull;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
+
+inline int launch_status() { return (int)cudaGetLastError(); }
+
+}  // namespace wpc
+
+// Runs the statement given last with `T` bound to the element type that `code` names.
+#define WPC_DISPATCH_DTYPE(code, T, ...)                   \
+  do {                                                     \
+    if ((code) == WPC_DTYPE_F32) {                         \
+      using T = float;                                     \
+      __VA_ARGS__;                                         \
+    } else if ((code) == WPC_DTYPE_BF16) {                 \
+      using T = __nv_bfloat16;                             \
+      __VA_ARGS__;                                         \
+    } else {                                               \
+      return WPC_ERR_BAD_ARGUMENT;                         \
+    }                                                      \
+  } while (0)

@@ -1,0 +1,267 @@
+// Row-wise and element-wise kernels: embedding rows, RMS norm, SiLU*up, residual add, row
+// gather, rotation angles, rotation + cache append, normal fill.  Each works for float32
+// and bfloat16 storage with float32 arithmetic, for any width.
+#include "api.h"
+#include "common.cuh"
+
+namespace wpc {
+
+// ---- embedding: out[t, :] = table[tokens[t], :] as float32 (wpc-runtime/src/weights.rs:101-105)
+template <typename Tw>
+__global__ void embed_kernel(const int* __restrict__ tokens, const Tw* __restrict__ table,
+                             float* __restrict__ out, int H, int V) {
+  const int t = blockIdx.x;
+  int id = tokens[t];
+  if (id < 0 || id >= V) id = 0;                 // the host checks ids; never read outside
+  const Tw* row = table + (size_t)id * H;
+  float* o = out + (size_t)t * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_float(row[i]);
+}
+
+// ---- RMS norm: out = x * rsqrt(mean(x^2) + eps) * gain (wpc-runtime/src/norm.rs:4-13)
+template <typename To>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ gain,
+                               float eps, To* __restrict__ out, int H) {
+  __shared__ float red[32];
+  const float* row = x + (size_t)blockIdx.x * H;
+  To* o = out + (size_t)blockIdx.x * H;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float v = row[i];
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  const float scale = 1.0f / sqrtf(ss / (float)H + eps);
+  for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_float<To>(row[i] * scale * gain[i]);
+}
+
+// ---- SiLU(gate) * up; gate = gu[:, 0:I], up = gu[:, I:2I] (wpc-runtime/src/model.rs:527-531)
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t n) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / I;
+    const int c = (int)(i - t * I);
+    const float g = to_float(gu[t * 2 * I + c]);
+    const float u = to_float(gu[t * 2 * I + I + c]);
+    out[i] = from_float<T>(g / (1.0f + expf(-g)) * u);
+  }
+}
+
+template <typename T>
+__global__ void add_kernel(float* __restrict__ x, const T* __restrict__ y, size_t n) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    x[i] += to_float(y[i]);
+}
+
+__global__ void gather_rows_kernel(const float* __restrict__ x, const int* __restrict__ idx,
+                                   float* __restrict__ out, int H, int T) {
+  int r = idx[blockIdx.x];
+  if (r < 0 || r >= T) r = 0;
+  const float* row = x + (size_t)r * H;
+  float* o = out + (size_t)blockIdx.x * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = row[i];
+}
+
+template <typename Ti, typename To>
+__global__ void convert_kernel(const Ti* __restrict__ in, To* __restrict__ out, size_t n) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    out[i] = from_float<To>(to_float(in[i]));
+}
+
+// ---- rotation angles in float64, as wpc-runtime/src/rope.rs:30-33 computes them
+__global__ void rope_angles_kernel(const int* __restrict__ positions, const double* __restrict__ inv_freq,
+                                   float* __restrict__ cosv, float* __restrict__ sinv, int R, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int t = i / R, r = i - t * R;
+  const double a = (double)positions[t] * inv_freq[r];
+  double s, c;
+  sincos(a, &s, &c);
+  cosv[i] = (float)c;
+  sinv[i] = (float)s;
+}
+
+// rotates the pair (r, r + half) of one head vector (wpc-runtime/src/rope.rs:34-37)
+template <typename T>
+__device__ __forceinline__ void rotate_pair(const T* v, int r, int half, float c, float s, float& o1, float& o2) {
+  const float x1 = to_float(v[r]), x2 = to_float(v[r + half]);
+  o1 = x1 * c - x2 * s;
+  o2 = x2 * c + x1 * s;
+}
+
+template <typename T>
+__global__ void rope_inplace_kernel(T* __restrict__ x, int row_stride, int n_heads, int hd, int R,
+                                    const float* __restrict__ cosv, const float* __restrict__ sinv) {
+  const int t = blockIdx.x, half = hd / 2;
+  T* row = x + (size_t)t * row_stride;
+  for (int i = threadIdx.x; i < n_heads * R; i += blockDim.x) {
+    const int h = i / R, r = i - h * R;
+    float o1, o2;
+    rotate_pair(row + h * hd, r, half, cosv[(size_t)t * R + r], sinv[(size_t)t * R + r], o1, o2);
+    row[h * hd + r] = from_float<T>(o1);
+    row[h * hd + r + half] = from_float<T>(o2);
+  }
+}
+
+// ---- q and k rotated (q in place), k and v appended to the pages of their sequence
+//      (wpc-runtime/src/model.rs:464-475: keys are stored after rotation, values as they are).
+//      Row layout of qkv: nh query heads, then nkv key heads, then nkv value heads.
+template <typename T>
+__global__ void qk_rope_kv_store_kernel(T* __restrict__ qkv, int row_stride, int nh, int nkv, int hd, int R,
+                                        const float* __restrict__ cosv, const float* __restrict__ sinv,
+                                        T* __restrict__ k_pages, T* __restrict__ v_pages,
+                                        const int* __restrict__ page_table, int table_width,
+                                        const int* __restrict__ seq_of_token, const int* __restrict__ positions,
+                                        int n_pages, int* __restrict__ status) {
+  const int t = blockIdx.x, half = hd / 2;
+  T* row = qkv + (size_t)t * row_stride;
+  const int pos = positions[t];
+  const int b = seq_of_token[t];
+  const int block = pos / WPC_PAGE;
+  const int page = (block < table_width) ? page_table[(size_t)b * table_width + block] : -1;
+  const bool ok = page >= 0 && page < n_pages;
+  if (!ok && threadIdx.x == 0 && status) atomicExch(status, WPC_ERR_BAD_ARGUMENT);
+  const float* ct = cosv ? cosv + (size_t)t * R : nullptr;
+  const float* st = sinv ? sinv + (size_t)t * R : nullptr;
+  // queries
+  for (int i = threadIdx.x; i < nh * R; i += blockDim.x) {
+    const int h = i / R, r = i - h * R;
+    float o1, o2;
+    rotate_pair(row + h * hd, r, half, ct[r], st[r], o1, o2);
+    row[h * hd + r] = from_float<T>(o1);
+    row[h * hd + r + half] = from_float<T>(o2);
+  }
+  if (!ok) return;
+  // keys: rotated where r < R, copied elsewhere
+  const T* krow = row + (size_t)nh * hd;
+  const T* vrow = krow + (size_t)nkv * hd;
+  const int in_page = pos % WPC_PAGE;
+  for (int i = threadIdx.x; i < nkv * half; i += blockDim.x) {
+    const int h = i / half, r = i - h * half;
+    T* dst = k_pages + (((size_t)page * nkv + h) * WPC_PAGE + in_page) * hd;
+    if (r < R) {
+      float o1, o2;
+      rotate_pair(krow + h * hd, r, half, ct[r], st[r], o1, o2);
+      dst[r] = from_float<T>(o1);
+      dst[r + half] = from_float<T>(o2);
+    } else {
+      dst[r] = krow[h * hd + r];
+      dst[r + half] = krow[h * hd + r + half];
+    }
+  }
+  for (int i = threadIdx.x; i < nkv * hd; i += blockDim.x) {
+    const int h = i / hd, d = i - h * hd;
+    v_pages[(((size_t)page * nkv + h) * WPC_PAGE + in_page) * hd + d] = vrow[i];
+  }
+}
+
+// ---- N(mean, std) fill from a counter-based generator: element i of a tensor with key k
+//      draws from mix64(k ^ mix64(i)); Box-Muller on two 24-bit uniforms
+template <typename T>
+__global__ void fill_normal_kernel(T* __restrict__ out, size_t n, uint64_t key, float mean, float std) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const uint64_t z = mix64(key ^ mix64((uint64_t)i));
+    const float u1 = ((float)((z >> 40) & 0xFFFFFF) + 1.0f) * (1.0f / 16777216.0f);   // (0, 1]
+    const float u2 = (float)((z >> 16) & 0xFFFFFF) * (1.0f / 16777216.0f);            // [0, 1)
+    const float r = sqrtf(-2.0f * logf(u1));
+    out[i] = from_float<T>(mean + std * r * cospif(2.0f * u2));
+  }
+}
+
+static inline int grid_for(size_t n, int block) {
+  size_t g = (n + block - 1) / block;
+  return (int)(g < 1 ? 1 : (g > 148 * 16 ? 148 * 16 : g));
+}
+
+}  // namespace wpc
+
+using namespace wpc;
+
+extern "C" {
+
+int wpc_embed(const int* tokens, const void* table, int table_dtype, float* out, int T, int H, int V,
+              cudaStream_t stream) {
+  if (T <= 0) return 0;
+  WPC_DISPATCH_DTYPE(table_dtype, Tw,
+                     (embed_kernel<Tw><<<T, 256, 0, stream>>>(tokens, (const Tw*)table, out, H, V)));
+  return launch_status();
+}
+
+int wpc_rmsnorm(const float* x, const float* gain, float eps, void* out, int out_dtype, int T, int H,
+                cudaStream_t stream) {
+  if (T <= 0) return 0;
+  const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+  WPC_DISPATCH_DTYPE(out_dtype, To, (rmsnorm_kernel<To><<<T, threads, 0, stream>>>(x, gain, eps, (To*)out, H)));
+  return launch_status();
+}
+
+int wpc_silu_mul(const void* gu, void* out, int dtype, int T, int I, cudaStream_t stream) {
+  const size_t n = (size_t)T * I;
+  if (n == 0) return 0;
+  WPC_DISPATCH_DTYPE(dtype, Tt,
+                     (silu_mul_kernel<Tt><<<grid_for(n, 256), 256, 0, stream>>>((const Tt*)gu, (Tt*)out, I, n)));
+  return launch_status();
+}
+
+int wpc_add(float* x, const void* y, int y_dtype, size_t n, cudaStream_t stream) {
+  if (n == 0) return 0;
+  WPC_DISPATCH_DTYPE(y_dtype, Tt, (add_kernel<Tt><<<grid_for(n, 256), 256, 0, stream>>>(x, (const Tt*)y, n)));
+  return launch_status();
+}
+
+int wpc_gather_rows(const float* x, const int* idx, float* out, int n_rows, int H, int T, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  gather_rows_kernel<<<n_rows, 256, 0, stream>>>(x, idx, out, H, T);
+  return launch_status();
+}
+
+int wpc_convert(const void* in, int in_dtype, void* out, int out_dtype, size_t n, cudaStream_t stream) {
+  if (n == 0) return 0;
+  const int g = grid_for(n, 256);
+  if (in_dtype == WPC_DTYPE_F32 && out_dtype == WPC_DTYPE_BF16)
+    convert_kernel<float, __nv_bfloat16><<<g, 256, 0, stream>>>((const float*)in, (__nv_bfloat16*)out, n);
+  else if (in_dtype == WPC_DTYPE_BF16 && out_dtype == WPC_DTYPE_F32)
+    convert_kernel<__nv_bfloat16, float><<<g, 256, 0, stream>>>((const __nv_bfloat16*)in, (float*)out, n);
+  else
+    return WPC_ERR_BAD_ARGUMENT;
+  return launch_status();
+}
+
+int wpc_rope_angles(const int* positions, const double* inv_freq, float* cosv, float* sinv, int T, int R,
+                    cudaStream_t stream) {
+  const int n = T * R;
+  if (n <= 0) return 0;
+  rope_angles_kernel<<<(n + 127) / 128, 128, 0, stream>>>(positions, inv_freq, cosv, sinv, R, n);
+  return launch_status();
+}
+
+int wpc_rope_inplace(void* x, int dtype, int row_stride, int T, int n_heads, int hd, int R, const float* cosv,
+                     const float* sinv, cudaStream_t stream) {
+  if (T <= 0 || R <= 0) return 0;
+  if (hd % 2 || R > hd / 2) return WPC_ERR_BAD_ARGUMENT;
+  WPC_DISPATCH_DTYPE(dtype, Tt, (rope_inplace_kernel<Tt><<<T, 256, 0, stream>>>((Tt*)x, row_stride, n_heads, hd,
+                                                                               R, cosv, sinv)));
+  return launch_status();
+}
+
+int wpc_qk_rope_kv_store(void* qkv, int dtype, int row_stride, int T, int nh, int nkv, int hd, int R,
+                         const float* cosv, const float* sinv, void* k_pages, void* v_pages,
+                         const int* page_table, int table_width, const int* seq_of_token, const int* positions,
+                         int n_pages, int* status, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (hd % 2 || R > hd / 2 || (R > 0 && (!cosv || !sinv))) return WPC_ERR_BAD_ARGUMENT;
+  WPC_DISPATCH_DTYPE(dtype, Tt,
+                     (qk_rope_kv_store_kernel<Tt><<<T, 256, 0, stream>>>(
+                         (Tt*)qkv, row_stride, nh, nkv, hd, R, cosv, sinv, (Tt*)k_pages, (Tt*)v_pages, page_table,
+                         table_width, seq_of_token, positions, n_pages, status)));
+  return launch_status();
+}
+
+int wpc_fill_normal(void* out, int dtype, size_t n, uint64_t key, float mean, float std, cudaStream_t stream) {
+  if (n == 0) return 0;
+  WPC_DISPATCH_DTYPE(dtype, Tt, (fill_normal_kernel<Tt><<<grid_for(n, 256), 256, 0, stream>>>((Tt*)out, n, key,
+                                                                                             mean, std)));
+  return launch_status();
+}
+
+}  // extern "C"

@@ -1,0 +1,207 @@
+"""The engine: a model, its cache, and the one step function that everything above uses.
+
+`step` takes a batch of sequences, each with the tokens it brings now (a whole prompt, a
+chunk of one, or a single decoded token), runs exactly those tokens as one packed batch
+against the cache, and returns the float32 logits at the wanted places.  The reference's
+counterpart is `forward_token` (wpc-runtime/src/model.rs:419), one token of one sequence at a
+time; batches, chunks and wanted places have no counterpart there.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..cache import PAGE, CacheError, SequenceCache
+from ..registry import config_from_folder, resolve
+from ..weights import load_weights, random_weights_on_device
+from .batch import SequenceStep, StepLayout, context_from, plan_step
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
+
+
+def parse_dtype(dtype) -> torch.dtype:
+    if isinstance(dtype, torch.dtype):
+        if dtype not in (torch.bfloat16, torch.float32):
+            raise ValueError(f"dtype must be bfloat16 or float32, got {dtype}")
+        return dtype
+    try:
+        return _DTYPES[str(dtype)]
+    except KeyError:
+        raise ValueError(f"dtype must be bfloat16 or float32, got {dtype!r}") from None
+
+
+def _bucket(n: int, floor: int = 4) -> int:
+    b = floor
+    while b < n:
+        b *= 2
+    return b
+
+
+class _MetaRing:
+    """Pinned host buffers for step metadata, reused in turn; a buffer is rewritten only after
+    the copy that last read it has finished."""
+
+    def __init__(self, device, depth: int = 4):
+        self.device = torch.device(device)
+        self.depth = depth
+        self.bufs: List[Optional[torch.Tensor]] = [None] * depth
+        self.events: List[Optional[object]] = [None] * depth
+        self.i = 0
+        self.pinned = self.device.type == "cuda"
+
+    def next(self, n: int) -> torch.Tensor:
+        self.i = (self.i + 1) % self.depth
+        if self.events[self.i] is not None:
+            self.events[self.i].synchronize()
+        buf = self.bufs[self.i]
+        if buf is None or buf.numel() < n:
+            buf = torch.empty(max(n, 1024), dtype=torch.int32, pin_memory=self.pinned)
+            self.bufs[self.i] = buf
+        return buf
+
+    def sent(self) -> None:
+        if self.pinned:
+            ev = torch.cuda.Event()
+            ev.record()
+            self.events[self.i] = ev
+
+
+class Engine:
+    """max_tokens: the most positions that live sequences hold at any time, each sequence
+    rounded up to whole pages of 64; it sizes the cache.  use_graphs: replay single-token
+    steps from CUDA graphs (one per batch size and page-table width)."""
+
+    def __init__(self, model, dtype, device="cuda", max_tokens: int = 4096,
+                 max_sequences: Optional[int] = None, use_graphs: bool = True):
+        self.model = model
+        self.config = model.config
+        self.dtype = parse_dtype(dtype)
+        self.device = torch.device(device)
+        self.cache = SequenceCache(model.cache_specs(), max_tokens, self.dtype, self.device, max_sequences)
+        self._ring = _MetaRing(self.device)
+        self.use_graphs = bool(use_graphs) and self.device.type == "cuda"
+        self._graphs: Dict[tuple, object] = {}
+        self.vocab_size = model.embedding.vocab_size
+        self.max_positions = getattr(model.config, "max_position_embeddings", None)
+        self.steps_run = 0
+
+    # -- construction ------------------------------------------------------------------------
+    @classmethod
+    def from_folder(cls, folder: str, dtype="bfloat16", device="cuda", **kw) -> "Engine":
+        """A model folder: config.json names the architecture, model.safetensors holds the
+        tensors."""
+        ops.require_device(device)
+        arch, config = config_from_folder(folder)
+        model = arch.build(config)
+        load_weights(model, folder, parse_dtype(dtype), torch.device(device))
+        return cls(model, dtype, device, **kw)
+
+    @classmethod
+    def from_random(cls, config, seed: int = 0, dtype="bfloat16", device="cuda", **kw) -> "Engine":
+        """Random weights drawn on the device (no folder); `config` is a configuration object
+        of a registered architecture."""
+        ops.require_device(device)
+        model = resolve(config.to_dict()).build(config)
+        random_weights_on_device(model, seed, parse_dtype(dtype), torch.device(device))
+        return cls(model, dtype, device, **kw)
+
+    # -- sequences ---------------------------------------------------------------------------
+    def open_sequence(self) -> int:
+        return self.cache.open()
+
+    def close_sequence(self, slot: int) -> None:
+        self.cache.close(slot)
+
+    def sequence_length(self, slot: int) -> int:
+        return self.cache.length(slot)
+
+    # -- the step ----------------------------------------------------------------------------
+    def _check(self, entries: Sequence[SequenceStep]) -> None:
+        seen = set()
+        for e in entries:
+            if e.slot in seen:
+                raise ValueError(f"slot {e.slot} appears twice in one step")
+            seen.add(e.slot)
+            if e.slot not in self.cache.lengths:
+                raise CacheError(f"slot {e.slot} is not open")
+            toks = np.asarray(e.tokens)
+            if toks.size == 0:
+                raise ValueError("every sequence of a step brings at least one token")
+            if toks.min() < 0 or toks.max() >= self.vocab_size:
+                raise ValueError(f"token id outside 0..{self.vocab_size - 1} in slot {e.slot}")
+            end = self.cache.length(e.slot) + toks.size
+            if self.max_positions is not None and end > self.max_positions:
+                raise ValueError(f"slot {e.slot} would reach {end} positions; "
+                                 f"max_position_embeddings is {self.max_positions}")
+
+    def step(self, entries: Sequence[SequenceStep]) -> Optional[torch.Tensor]:
+        """Runs the tokens that each entry brings, from the cache that earlier steps left;
+        returns float32 logits [wanted places, vocab] in the order of the entries and of their
+        `want` lists, or None if nothing is wanted."""
+        self._check(entries)
+        slots = [e.slot for e in entries]
+        starts = [self.cache.reserve(e.slot, len(e.tokens)) for e in entries]
+        width = _bucket(self.cache.table_width(slots))
+        kv_groups = self.cache.kv_groups()
+        rows = [self.cache.page_table_rows(g, slots, width) for g in kv_groups]
+        n_tokens = sum(len(e.tokens) for e in entries)
+        n_want = sum(len(e.want) for e in entries)
+        lay = StepLayout(n_tokens, len(entries), n_want, width, len(kv_groups))
+        host = self._ring.next(lay.total)
+        plan = plan_step(entries, starts, rows, width, out=host.numpy())
+        logits = None
+        ran = False
+        if plan.is_decode and self.use_graphs:
+            ran, logits = self._graph_step(plan, host)
+        if not ran:
+            meta = host[: lay.total].to(self.device, non_blocking=True)
+            self._ring.sent()
+            ctx = context_from(meta, lay, self.dtype, plan.max_new_tokens, plan.max_ctx_len, plan.is_decode)
+            logits = self.model.forward(ctx, self.cache)
+        for e in entries:
+            self.cache.commit(e.slot, len(e.tokens))
+        self.steps_run += 1
+        return logits
+
+    def _graph_step(self, plan, host: torch.Tensor):
+        """Single-token steps of a shape seen before are replayed from a CUDA graph.  The first
+        step of a shape runs directly (returns ran=False); the second is captured, which runs
+        nothing, and then replayed, so that no step ever runs twice."""
+        lay = plan.layout
+        key = (lay.n_seqs, lay.table_width, lay.n_want)
+        entry = self._graphs.get(key)
+        if entry is None:
+            self._graphs[key] = "seen"
+            return False, None
+        if entry == "seen":
+            meta = torch.zeros(lay.total, dtype=torch.int32, device=self.device)
+            ctx = context_from(meta, lay, self.dtype, 1, lay.table_width * PAGE, True)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                logits = self.model.forward(ctx, self.cache)
+            entry = (graph, meta, logits)
+            self._graphs[key] = entry
+        graph, meta, logits = entry
+        meta.copy_(host[: lay.total], non_blocking=True)
+        self._ring.sent()
+        graph.replay()
+        return True, logits
+
+    # -- sampling ----------------------------------------------------------------------------
+    def set_sampler_state(self, slots: Sequence[int], seed: int, request_ids: Sequence[int]) -> None:
+        """Writes (seed, request number, 0 tokens drawn) into the slots' state rows."""
+        rows = torch.tensor([[0, seed, r, 0] for r in request_ids], dtype=torch.int64)
+        idx = torch.tensor(list(slots), dtype=torch.int64)
+        self.cache.seq_state[idx.to(self.device)] = rows.to(self.device)
+
+    def sample(self, logits: torch.Tensor, slots: Sequence[int], temperature: float,
+               banned: Sequence[int] = ()) -> torch.Tensor:
+        """One token per row of `logits`, int32 on the device; row i belongs to slots[i]."""
+        slot_t = torch.tensor(list(slots), dtype=torch.int32).to(self.device, non_blocking=True)
+        banned_t = None
+        if len(banned):
+            banned_t = torch.tensor(sorted(set(int(b) for b in banned)), dtype=torch.int32).to(self.device)
+        return ops.sample(logits, slot_t, self.cache.seq_state, float(temperature), banned_t)

@@ -1,0 +1,105 @@
+"""The generation loop above the step function: batches of unequal prompts, stop tokens,
+sequences that end earlier, and as many batches one after another as there are requests.
+
+The order within a sequence is the reference's (wpc-runtime/src/main.rs:284-312): pick a
+token from the last logits, append it, stop if it is a stop token (it stays in the output and
+is never fed), else feed it.  The forward pass that the reference spends after the last
+token (main.rs:307) is not run.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence
+
+from ..cache import pages_for
+from .batch import SequenceStep
+
+
+@dataclass
+class GenerationOptions:
+    max_tokens: int = 40                    # main.rs:61-62
+    temperature: float = 0.0                # 0: greedy (sampling.rs:3-13)
+    seed: int = 0
+    stop_token_ids: Sequence[int] = ()
+    banned_token_ids: Sequence[int] = ()    # sampling.rs:23-51 (WPC_BAN_TOKENS)
+    max_batch: Optional[int] = None         # most sequences in one batch
+
+
+def plan_batches(prompt_lens: Sequence[int], max_tokens: int, n_pages: int, n_slots: int,
+                 max_batch: Optional[int] = None) -> List[List[int]]:
+    """Request numbers grouped into batches, in order.  A batch takes requests while every one
+    of them can reach prompt + max_tokens positions within the cache's pages and slots."""
+    batches: List[List[int]] = []
+    cur: List[int] = []
+    cur_pages = 0
+    limit = min(n_slots, max_batch) if max_batch else n_slots
+    for r, n in enumerate(prompt_lens):
+        if n < 1:
+            raise ValueError(f"request {r} has an empty prompt")
+        need = pages_for(n + max_tokens)
+        if need > n_pages:
+            raise ValueError(f"request {r} needs {need} pages of 64 positions ({n} prompt + {max_tokens} new); "
+                             f"the cache has {n_pages}")
+        if cur and (cur_pages + need > n_pages or len(cur) >= limit):
+            batches.append(cur)
+            cur, cur_pages = [], 0
+        cur.append(r)
+        cur_pages += need
+    if cur:
+        batches.append(cur)
+    return batches
+
+
+@dataclass
+class _Live:
+    request: int
+    slot: int
+    output: List[int] = field(default_factory=list)
+
+
+def advance(live: List[_Live], picked: Sequence[int], opts: GenerationOptions, stop: frozenset):
+    """Appends each picked token to its sequence and decides who goes on: returns (still
+    live, finished).  A sequence ends on a stop token or when it has max_tokens tokens."""
+    go_on, done = [], []
+    for seq, tok in zip(live, picked):
+        tok = int(tok)
+        seq.output.append(tok)
+        if tok in stop or len(seq.output) >= opts.max_tokens:
+            done.append(seq)
+        else:
+            go_on.append(seq)
+    return go_on, done
+
+
+def generate(engine, prompts: Sequence[Sequence[int]], opts: GenerationOptions) -> List[List[int]]:
+    """Generated token ids for each prompt.  `engine` offers open_sequence, close_sequence,
+    step, sample, set_sampler_state and a `cache` with n_pages and n_slots."""
+    if opts.max_tokens < 1:
+        return [[] for _ in prompts]
+    stop = frozenset(int(s) for s in opts.stop_token_ids)
+    outputs: List[Optional[List[int]]] = [None] * len(prompts)
+    batches = plan_batches([len(p) for p in prompts], opts.max_tokens, engine.cache.n_pages,
+                           engine.cache.n_slots, opts.max_batch)
+    for batch in batches:
+        live = [_Live(r, engine.open_sequence()) for r in batch]
+        try:
+            engine.set_sampler_state([s.slot for s in live], opts.seed, [s.request for s in live])
+            entries = [SequenceStep(s.slot, list(prompts[s.request]), want=[len(prompts[s.request]) - 1])
+                       for s in live]
+            while live:
+                logits = engine.step(entries)
+                picked = engine.sample(logits, [s.slot for s in live], opts.temperature,
+                                       opts.banned_token_ids).tolist()
+                live, done = advance(live, picked, opts, stop)
+                for seq in done:
+                    outputs[seq.request] = seq.output
+                    engine.close_sequence(seq.slot)
+                entries = [SequenceStep(s.slot, [s.output[-1]], want=[0]) for s in live]
+        except BaseException:
+            for seq in live:
+                try:
+                    engine.close_sequence(seq.slot)
+                except Exception:
+                    pass
+            raise
+    return [o if o is not None else [] for o in outputs]

@@ -1,0 +1,274 @@
+"""The device operations that the parts call: each checks its arguments and launches one
+hand-written kernel of the in-tree CUDA library on the current stream.
+
+There is no fallback: without a CUDA device, or if the library cannot be built or loaded,
+every operation raises `KernelError`.  Tensors are passed by address through the library's C
+interface (csrc/api.h); outputs are allocated here with torch's allocator, which is all that
+torch does on this path.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+from typing import Optional, Tuple
+
+import torch
+
+from .constants import PAGE
+
+_F32, _BF16 = 0, 1
+_ERRORS = {1001: "bad argument", 1002: "unsupported size", 1003: "size beyond the stated maximum",
+           1004: "a device-side wait ran out"}
+
+
+class KernelError(RuntimeError):
+    """A kernel could not be launched, or the kernel library is missing."""
+
+
+_lib = None
+_lib_lock = threading.Lock()
+
+
+def library():
+    """The loaded kernel library (built on first use)."""
+    global _lib
+    if _lib is None:
+        with _lib_lock:
+            if _lib is None:
+                from .csrc.build import BuildError, library_path
+                try:
+                    path = library_path()
+                    _lib = ctypes.CDLL(path)
+                except (BuildError, OSError) as e:
+                    raise KernelError(f"the CUDA kernel library is not available: {e}") from None
+    return _lib
+
+
+def require_device(device="cuda") -> None:
+    """Raises unless `device` is a CUDA device and the kernel library loads."""
+    dev = torch.device(device)
+    if dev.type != "cuda":
+        raise KernelError(f"this engine runs on CUDA devices only, not on {dev}")
+    if not torch.cuda.is_available():
+        raise KernelError("no CUDA device is available; there is no CPU path")
+    library()
+
+
+def _code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return _F32
+    if dtype == torch.bfloat16:
+        return _BF16
+    raise KernelError(f"unsupported element type {dtype}")
+
+
+def _p(t: Optional[torch.Tensor]):
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(name: str, rc: int) -> None:
+    if rc == 0:
+        return
+    if rc in _ERRORS:
+        raise KernelError(f"{name}: {_ERRORS[rc]}")
+    raise KernelError(f"{name}: CUDA error {rc}")
+
+
+def _need(cond: bool, msg: str) -> None:
+    if not cond:
+        raise KernelError(msg)
+
+
+def _rows(t: torch.Tensor, name: str) -> None:
+    _need(t.is_cuda, f"{name} must be on a CUDA device")
+    _need(t.dim() == 2 and t.stride(1) == 1, f"{name} must be a matrix with unit column stride")
+
+
+# ---------------------------------------------------------------------------------------------
+def embed(tokens: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+    """float32 [T, width] = table[tokens]."""
+    _need(tokens.dtype == torch.int32 and tokens.is_contiguous(), "tokens must be contiguous int32")
+    _need(table.is_contiguous(), "the embedding table must be contiguous")
+    T, (V, H) = tokens.numel(), table.shape
+    out = torch.empty((T, H), dtype=torch.float32, device=table.device)
+    _check("embed", library().wpc_embed(_p(tokens), _p(table), _code(table.dtype), _p(out), T, H, V, _stream()))
+    return out
+
+
+def rmsnorm(x: torch.Tensor, gain: torch.Tensor, eps: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """x * rsqrt(mean(x^2) + eps) * gain per row; x and gain float32."""
+    _need(x.dtype == torch.float32 and x.is_contiguous() and x.dim() == 2, "x must be contiguous float32 [T, width]")
+    _need(gain.dtype == torch.float32 and gain.numel() == x.shape[1], "gain must be float32 [width]")
+    out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    _check("rmsnorm", library().wpc_rmsnorm(_p(x), _p(gain), ctypes.c_float(eps), _p(out), _code(out_dtype),
+                                            x.shape[0], x.shape[1], _stream()))
+    return out
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
+           out_dtype: Optional[torch.dtype] = None, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x [T, K] times w [N, K] transposed, plus bias (float32 [N]).  With `residual` (float32
+    [T, N], contiguous) the result is added to it in place in float32 and it is returned."""
+    _rows(x, "x")
+    _rows(w, "w")
+    M, K = x.shape
+    N = w.shape[0]
+    _need(w.shape[1] == K, f"x has {K} columns, w has {w.shape[1]}")
+    if bias is not None:
+        _need(bias.dtype == torch.float32 and bias.numel() == N and bias.is_contiguous(), "bias must be float32 [N]")
+    if residual is not None:
+        _need(residual.dtype == torch.float32 and residual.shape == (M, N) and residual.is_contiguous(),
+              "residual must be contiguous float32 [T, N]")
+        out, accumulate = residual, 1
+    else:
+        out = torch.empty((M, N), dtype=out_dtype or x.dtype, device=x.device)
+        accumulate = 0
+    if M == 0:
+        return out
+    if _fast_linear(x, w, bias, out, accumulate):
+        return out
+    _check("gemm_simt", library().wpc_gemm_simt(
+        _p(x), _code(x.dtype), x.stride(0), _p(w), _code(w.dtype), w.stride(0), _p(bias), _p(out),
+        _code(out.dtype), out.stride(0), accumulate, M, N, K, _stream()))
+    return out
+
+
+def _fast_linear(x, w, bias, out, accumulate) -> bool:
+    """The tensor-core product, where it applies; returns False to leave it to the plain one."""
+    return False
+
+
+def linear_plain(x, w, bias=None, out_dtype=None, residual=None) -> torch.Tensor:
+    """The same product on the CUDA cores only (the plain twin of `linear`)."""
+    global _fast_linear
+    saved = _fast_linear
+    _fast_linear = lambda *a: False
+    try:
+        return linear(x, w, bias, out_dtype, residual)
+    finally:
+        _fast_linear = saved
+
+
+def silu_mul(gu: torch.Tensor, inner: int) -> torch.Tensor:
+    """silu(gu[:, :inner]) * gu[:, inner:]."""
+    _need(gu.is_contiguous() and gu.dim() == 2 and gu.shape[1] == 2 * inner, "gu must be contiguous [T, 2*inner]")
+    out = torch.empty((gu.shape[0], inner), dtype=gu.dtype, device=gu.device)
+    _check("silu_mul", library().wpc_silu_mul(_p(gu), _p(out), _code(gu.dtype), gu.shape[0], inner, _stream()))
+    return out
+
+
+def add_(x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+    """x += y in float32, in place (x float32)."""
+    _need(x.dtype == torch.float32 and x.is_contiguous() and y.is_contiguous() and x.shape == y.shape,
+          "x must be contiguous float32 and y of the same shape")
+    _check("add", library().wpc_add(_p(x), _p(y), _code(y.dtype), ctypes.c_size_t(x.numel()), _stream()))
+    return x
+
+
+def gather_rows(x: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
+    _need(x.dtype == torch.float32 and x.is_contiguous() and idx.dtype == torch.int32, "x float32, idx int32")
+    out = torch.empty((idx.numel(), x.shape[1]), dtype=torch.float32, device=x.device)
+    _check("gather_rows", library().wpc_gather_rows(_p(x), _p(idx), _p(out), idx.numel(), x.shape[1], x.shape[0],
+                                                    _stream()))
+    return out
+
+
+def convert(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    if x.dtype == dtype:
+        return x
+    _need(x.is_contiguous(), "x must be contiguous")
+    out = torch.empty(x.shape, dtype=dtype, device=x.device)
+    _check("convert", library().wpc_convert(_p(x), _code(x.dtype), _p(out), _code(dtype),
+                                            ctypes.c_size_t(x.numel()), _stream()))
+    return out
+
+
+def rope_angles(positions: torch.Tensor, inv_freq: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """cos and sin, float32 [T, R], of positions[t] * inv_freq[r] computed in float64."""
+    _need(positions.dtype == torch.int32 and inv_freq.dtype == torch.float64, "positions int32, inv_freq float64")
+    T, R = positions.numel(), inv_freq.numel()
+    cos = torch.empty((T, R), dtype=torch.float32, device=positions.device)
+    sin = torch.empty_like(cos)
+    _check("rope_angles", library().wpc_rope_angles(_p(positions), _p(inv_freq), _p(cos), _p(sin), T, R, _stream()))
+    return cos, sin
+
+
+def rope_inplace(x: torch.Tensor, n_heads: int, head_dim: int, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """Rotates the first n_heads heads of every row of x in place."""
+    _rows(x, "x")
+    _need(x.shape[1] >= n_heads * head_dim and cos.shape == sin.shape and cos.shape[0] == x.shape[0],
+          "x too narrow or tables of the wrong length")
+    _check("rope_inplace", library().wpc_rope_inplace(_p(x), _code(x.dtype), x.stride(0), x.shape[0], n_heads,
+                                                      head_dim, cos.shape[1], _p(cos), _p(sin), _stream()))
+    return x
+
+
+def qk_rope_kv_store(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
+                     cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
+                     k_pages: torch.Tensor, v_pages: torch.Tensor, page_table: torch.Tensor,
+                     seq_of_token: torch.Tensor, positions: torch.Tensor) -> None:
+    """Rotates q and k of qkv [T, (n_heads + 2 n_kv_heads) head_dim] (q in place) and appends
+    the rotated k and the v of every token to the pages of its sequence."""
+    _rows(qkv, "qkv")
+    _need(qkv.shape[1] == (n_heads + 2 * n_kv_heads) * head_dim, "qkv has the wrong width")
+    _need(k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.dtype == qkv.dtype
+          and tuple(k_pages.shape[1:]) == (n_kv_heads, PAGE, head_dim) and k_pages.shape == v_pages.shape,
+          "pages must be contiguous [n_pages, n_kv_heads, PAGE, head_dim] of qkv's type")
+    _need(page_table.dtype == torch.int32 and page_table.is_contiguous(), "page_table must be contiguous int32")
+    R = 0 if cos is None else cos.shape[1]
+    _check("qk_rope_kv_store", library().wpc_qk_rope_kv_store(
+        _p(qkv), _code(qkv.dtype), qkv.stride(0), qkv.shape[0], n_heads, n_kv_heads, head_dim, R, _p(cos), _p(sin),
+        _p(k_pages), _p(v_pages), _p(page_table), page_table.shape[1], _p(seq_of_token), _p(positions),
+        k_pages.shape[0], _p(None), _stream()))
+
+
+def attention(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, k_pages: torch.Tensor,
+              v_pages: torch.Tensor, page_table: torch.Tensor, cu_seqlens: torch.Tensor, ctx_lens: torch.Tensor,
+              seq_of_token: torch.Tensor, positions: torch.Tensor, scale: float, window: Optional[int],
+              max_new_tokens: int, max_ctx_len: int) -> torch.Tensor:
+    """softmax(q . k * scale) . v over the cached positions that each query sees: 0..its own,
+    or the last `window` of them.  q: the first n_heads*head_dim columns of each row."""
+    return attention_plain(q, n_heads, n_kv_heads, head_dim, k_pages, v_pages, page_table, seq_of_token,
+                           positions, scale, window)
+
+
+def attention_plain(q, n_heads, n_kv_heads, head_dim, k_pages, v_pages, page_table, seq_of_token, positions,
+                    scale, window) -> torch.Tensor:
+    _rows(q, "q")
+    _need(q.shape[1] >= n_heads * head_dim, "q is too narrow")
+    _need(k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.dtype == q.dtype, "pages: wrong type")
+    T = q.shape[0]
+    out = torch.empty((T, n_heads * head_dim), dtype=q.dtype, device=q.device)
+    _check("attention_plain", library().wpc_attention_plain(
+        _p(q), q.stride(0), _p(out), out.stride(0), _code(q.dtype), _p(k_pages), _p(v_pages), _p(page_table),
+        page_table.shape[1], _p(seq_of_token), _p(positions), T, n_heads, n_kv_heads, head_dim,
+        ctypes.c_float(scale), int(window or 0), _stream()))
+    return out
+
+
+def sample(logits: torch.Tensor, slots: torch.Tensor, seq_state: torch.Tensor, temperature: float,
+           banned: Optional[torch.Tensor]) -> torch.Tensor:
+    """One token per row (int32).  temperature 0: the first greatest logit; else a draw from
+    softmax(logits / temperature) with the uniform number that the row's state names
+    (seq_state[slot] = position, seed, request number, tokens drawn; the last is advanced)."""
+    _need(logits.dtype == torch.float32 and logits.is_contiguous() and logits.dim() == 2, "logits: float32 [B, V]")
+    _need(slots.dtype == torch.int32 and slots.numel() == logits.shape[0], "slots: int32 [B]")
+    _need(seq_state.dtype == torch.int64 and seq_state.is_contiguous() and seq_state.shape[1] == 4,
+          "seq_state: int64 [n_slots, 4]")
+    out = torch.empty((logits.shape[0],), dtype=torch.int32, device=logits.device)
+    nb = 0 if banned is None else banned.numel()
+    _check("sample", library().wpc_sample(_p(logits), logits.shape[0], logits.shape[1], _p(slots), _p(seq_state),
+                                          ctypes.c_float(temperature), _p(banned), nb, _p(out), _stream()))
+    return out
+
+
+def fill_normal(t: torch.Tensor, key: int, mean: float, std: float) -> None:
+    _need(t.is_contiguous(), "t must be contiguous")
+    _check("fill_normal", library().wpc_fill_normal(_p(t), _code(t.dtype), ctypes.c_size_t(t.numel()),
+                                                    ctypes.c_uint64(key), ctypes.c_float(mean), ctypes.c_float(std),
+                                                    _stream()))

@@ -1,0 +1,14 @@
+"""Parts that layers are put together from; see base.py for the interfaces."""
+from .attention import GQAAttention
+from .base import (Block, FeedForward, KVSpec, Mixer, Norm, ParamSpec, Part, PositionEncoding,
+                   StateSpec, collect_params)
+from .block import PreNormBlock
+from .embedding import Embedding, OutputHead
+from .linear import Linear, fuse_rows
+from .mlp import SwiGLU
+from .norm import RMSNorm
+from .rope import RotaryEncoding
+
+__all__ = ["Block", "Embedding", "FeedForward", "GQAAttention", "KVSpec", "Linear", "Mixer", "Norm",
+           "OutputHead", "ParamSpec", "Part", "PositionEncoding", "PreNormBlock", "RMSNorm",
+           "RotaryEncoding", "StateSpec", "SwiGLU", "collect_params", "fuse_rows"]
