@@ -1,0 +1,93 @@
+"""The engine on the GPU against the plain implementation, in 32-bit and in bfloat16: each
+request alone and whole, with its last 32 tokens one by one, and in batches of unequal
+lengths whose shorter requests end earlier, one batch after another so that slots and pages
+are used again."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import (assert_close_to_plain, random_tokens, run_batch, run_tail_one_by_one, run_whole)
+from plain import qwen2_plain as P
+from wpc_engine_b200 import Engine, GenerationOptions, generate
+
+pytestmark = pytest.mark.gpu
+CASES = [(n, d) for n in ("A", "B", "C") for d in ("float32", "bfloat16")]
+
+
+@pytest.fixture(scope="module")
+def engines(folders):
+    made = {}
+
+    def get(name, dtype, **kw):
+        key = (name, dtype, tuple(sorted(kw.items())))
+        if key not in made:
+            made[key] = (Engine.from_folder(folders[(name, dtype)], dtype=dtype, max_tokens=4096, **kw),
+                         folders[(name, dtype)])
+        return made[key]
+    return get
+
+
+def requests_for(engine, lens, seed=100):
+    return [random_tokens(engine.config.vocab_size, n, seed + i) for i, n in enumerate(lens)]
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_whole(engines, name, dtype):
+    eng, folder = engines(name, dtype)
+    for r in requests_for(eng, [1, 2, 63, 64, 65, 120]):
+        assert_close_to_plain(run_whole(eng, r), folder, r, dtype, f"whole, {len(r)} tokens")
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_last_32_one_by_one(engines, name, dtype):
+    eng, folder = engines(name, dtype)
+    for r in requests_for(eng, [5, 33, 100, 127], seed=200):
+        assert_close_to_plain(run_tail_one_by_one(eng, r), folder, r, dtype, f"tail, {len(r)} tokens")
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_unequal_batches_reuse_slots(engines, name, dtype):
+    eng, folder = engines(name, dtype)
+    for round_, (lens, prompts) in enumerate([([70, 5, 33, 100], [20, 5, 1, 64]),
+                                              ([9, 128, 64], [9, 100, 3]),
+                                              ([100, 100, 31, 2, 77], [64, 65, 30, 1, 77])]):
+        reqs = requests_for(eng, lens, seed=300 + 10 * round_)
+        outs = run_batch(eng, reqs, prompts)
+        for r, o in zip(reqs, outs):
+            assert_close_to_plain(o, folder, r, dtype, f"batch {round_}, {len(r)} tokens")
+        eng.cache.check()
+        assert eng.cache.slots.n_held == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_chunking_and_batching_change_only_rounding(engines, dtype):
+    """The same request whole, tail by tail and inside a batch: the three differ from one
+    another far less than the type's distance from the plain implementation."""
+    eng, _ = engines("C", dtype)
+    r = requests_for(eng, [120], seed=400)[0]
+    whole = run_whole(eng, r)
+    tail = run_tail_one_by_one(eng, r)
+    batch = run_batch(eng, [r, r[:50], r[:7]], [60, 50, 7])[0]
+    tol = 2e-5 if dtype == "float32" else 6e-2
+    scale = np.abs(whole).max()
+    assert np.abs(tail - whole).max() <= tol * scale
+    assert np.abs(batch - whole).max() <= tol * scale
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding(engines, folders, dtype):
+    """300 tokens decoded one by one after a short prompt (graphs replayed, pages crossed)."""
+    eng, folder = engines("C", dtype)
+    r = requests_for(eng, [330], seed=500)[0]
+    got = run_tail_one_by_one(eng, r, tail=300)
+    assert_close_to_plain(got, folder, r, dtype, "long decoding")
+
+
+def test_greedy_generation_matches_plain(engines):
+    eng, folder = engines("A", "float32")
+    cfg, tensors = P.read_model_folder(folder)
+    prompts = [random_tokens(256, n, 40 + n) for n in (5, 11, 17)]
+    got = generate(eng, prompts, GenerationOptions(max_tokens=8))
+    for p, g in zip(prompts, got):
+        assert g == P.generate_greedy(cfg, tensors, p, 8)
+    eng.cache.check()

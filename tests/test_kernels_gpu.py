@@ -1,0 +1,204 @@
+"""Each kernel alone against its plain torch reference (tests/torch_ops.py), at sizes other
+than the engine's: widths that are no power of two, head sizes in steps of 16, odd counts."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import torch_ops as ref
+from wpc_engine_b200 import ops
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def rnd(shape, dtype=torch.float32, seed=0, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+def close(got, want, dtype, scale=1.0):
+    tol = 2e-5 if dtype == torch.float32 else 1.2e-2
+    err = (got.float() - want.float()).abs().max().item()
+    ref_mag = max(want.float().abs().max().item(), 1e-6)
+    assert err <= tol * max(ref_mag, scale), f"max error {err} against magnitude {ref_mag}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embed(dtype):
+    table = rnd((301, 72), dtype, 1)
+    tokens = torch.tensor([0, 300, 7, 7, 150], dtype=torch.int32, device=DEV)
+    assert torch.equal(ops.embed(tokens, table), ref.embed(tokens, table))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("width", [4, 72, 1000, 3584])
+def test_rmsnorm(dtype, width):
+    x = rnd((5, width), seed=2, scale=3.0)
+    gain = 1 + rnd((width,), seed=3, scale=0.1)
+    close(ops.rmsnorm(x, gain, 1e-5, dtype), ref.rmsnorm(x, gain, 1e-5, dtype), dtype)
+
+
+def test_rmsnorm_anchor():
+    # wpc-runtime/src/norm.rs:49-60
+    x = torch.tensor([[3.0, 4.0, 0.0, 0.0]], device=DEV)
+    out = ops.rmsnorm(x, torch.ones(4, device=DEV), 1e-6, torch.float32)
+    want = x.cpu() / math.sqrt(6.25 + 1e-6)
+    assert torch.allclose(out.cpu(), want, atol=1e-6)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(1, 40, 24), (7, 200, 96), (130, 72, 200), (33, 300, 80)])
+@pytest.mark.parametrize("mode", ["plain", "bias", "residual"])
+def test_linear(dtype, shape, mode):
+    M, N, K = shape
+    x, w = rnd((M, K), dtype, 4), rnd((N, K), dtype, 5, 0.1)
+    bias = rnd((N,), seed=6) if mode != "plain" else None
+    if mode == "residual":
+        r0 = rnd((M, N), seed=7)
+        got = ops.linear(x, w, bias, residual=r0.clone())
+        want = ref.linear(x, w, bias, residual=r0.clone())
+        close(got, want, torch.float32, scale=1.0)
+    else:
+        close(ops.linear(x, w, bias), ref.linear(x, w, bias), dtype)
+
+
+def test_linear_keeps_32_bit_weights_with_16_bit_rows():
+    x, w = rnd((9, 48), torch.bfloat16, 8), rnd((20, 48), torch.float32, 9)
+    close(ops.linear(x, w), ref.linear(x, w), torch.bfloat16)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_silu_mul_add_gather_convert(dtype):
+    gu = rnd((6, 2 * 77), dtype, 10, 2.0)
+    close(ops.silu_mul(gu, 77), ref.silu_mul(gu, 77), dtype)
+    x, y = rnd((6, 77), seed=11), rnd((6, 77), dtype, 12)
+    close(ops.add_(x.clone(), y), ref.add_(x.clone(), y), torch.float32)
+    idx = torch.tensor([5, 0, 5], dtype=torch.int32, device=DEV)
+    assert torch.equal(ops.gather_rows(x, idx), x[idx.long()])
+    assert torch.equal(ops.convert(x, torch.bfloat16), x.to(torch.bfloat16))
+
+
+def test_rope_angles_and_anchor():
+    # float64 angles; position 0 is the identity, pair norms are kept (wpc-runtime/src/rope.rs:46-72)
+    hd, theta = 48, 1e6
+    inv = torch.tensor(np.power(theta, -2.0 * np.arange(hd // 2) / hd), dtype=torch.float64, device=DEV)
+    pos = torch.tensor([0, 5, 1000, 131071], dtype=torch.int32, device=DEV)
+    cos, sin = ops.rope_angles(pos, inv)
+    rc, rs = ref.rope_angles(pos.cpu(), inv.cpu())
+    assert (cos.cpu() - rc).abs().max() <= 1e-7 and (sin.cpu() - rs).abs().max() <= 1e-7
+    x = rnd((4, 3 * hd), seed=13)
+    y = ops.rope_inplace(x.clone(), 3, hd, cos, sin)
+    assert torch.equal(y[0], x[0])
+    xv, yv = x.view(4, 3, 2, hd // 2), y.view(4, 3, 2, hd // 2)
+    assert torch.allclose((xv ** 2).sum(2), (yv ** 2).sum(2), rtol=1e-5)
+    close(y, ref.rope_inplace(x.clone(), 3, hd, cos, sin), torch.float32)
+
+
+def paged_case(dtype, nh, nkv, hd, lens, new, window=None, seed=0):
+    """A batch of sequences with `lens[b]` positions after the step, the last `new[b]` of which
+    are this step's tokens; pages are handed out in a scrambled order."""
+    B = len(lens)
+    width = max((n + 63) // 64 for n in lens) + 1
+    n_pages = sum((n + 63) // 64 for n in lens) + 3
+    perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(seed)).tolist()
+    table = torch.full((B, width), -1, dtype=torch.int32)
+    for b, n in enumerate(lens):
+        for i in range((n + 63) // 64):
+            table[b, i] = perm.pop()
+    T = sum(new)
+    seq = torch.tensor([b for b in range(B) for _ in range(new[b])], dtype=torch.int32)
+    pos = torch.tensor([lens[b] - new[b] + i for b in range(B) for i in range(new[b])], dtype=torch.int32)
+    k_pages = rnd((n_pages, nkv, 64, hd), dtype, seed + 1)
+    v_pages = rnd((n_pages, nkv, 64, hd), dtype, seed + 2)
+    qkv = rnd((T, (nh + 2 * nkv) * hd), dtype, seed + 3)
+    return qkv, k_pages, v_pages, table.to(DEV), seq.to(DEV), pos.to(DEV)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 16), (3, 1, 32), (6, 3, 48), (7, 1, 128), (2, 2, 80)])
+def test_qk_rope_kv_store(dtype, nh, nkv, hd):
+    lens, new = [70, 5, 130], [6, 5, 1]
+    qkv, kp, vp, table, seq, pos = paged_case(dtype, nh, nkv, hd, lens, new)
+    inv = torch.tensor(np.power(1e4, -2.0 * np.arange(hd // 2) / hd), dtype=torch.float64, device=DEV)
+    cos, sin = ops.rope_angles(pos, inv)
+    q1, k1, v1 = qkv.clone(), kp.clone(), vp.clone()
+    ops.qk_rope_kv_store(q1, nh, nkv, hd, cos, sin, k1, v1, table, seq, pos)
+    q2, k2, v2 = qkv.cpu().clone(), kp.cpu().clone(), vp.cpu().clone()
+    ref.qk_rope_kv_store(q2, nh, nkv, hd, cos.cpu(), sin.cpu(), k2, v2, table.cpu(), seq.cpu(), pos.cpu())
+    close(q1[:, :nh * hd].cpu(), q2[:, :nh * hd], dtype)
+    close(k1.cpu(), k2, dtype)
+    assert torch.equal(v1.cpu(), v2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 16), (3, 1, 32), (6, 3, 48), (7, 1, 128), (28, 4, 128), (2, 2, 80)])
+@pytest.mark.parametrize("window", [None, 40])
+def test_attention(dtype, nh, nkv, hd, window):
+    lens, new = [200, 5, 131, 64], [37, 5, 1, 1]
+    qkv, kp, vp, table, seq, pos = paged_case(dtype, nh, nkv, hd, lens, new, seed=5)
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(new)]), dtype=torch.int32, device=DEV)
+    ctx = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(hd)
+    got = ops.attention(qkv, nh, nkv, hd, kp, vp, table, cu, ctx, seq, pos, scale, window, max(new), max(lens))
+    want = ref.attention_plain(qkv.cpu(), nh, nkv, hd, kp.cpu(), vp.cpu(), table.cpu(), seq.cpu(), pos.cpu(),
+                               scale, window)
+    close(got.cpu(), want, dtype)
+    plain = ops.attention_plain(qkv, nh, nkv, hd, kp, vp, table, seq, pos, scale, window)
+    close(plain.cpu(), want, dtype)
+
+
+def test_attention_finds_one_far_key():
+    """One key among hundreds is made to dominate a query's scores; the output must be that
+    key's value, wherever the key lies (first page, a page edge, far back)."""
+    nh, nkv, hd = 4, 2, 32
+    lens, new = [600], [1]
+    for far in (0, 63, 64, 300, 599):
+        qkv, kp, vp, table, seq, pos = paged_case(torch.float32, nh, nkv, hd, lens, new, seed=far)
+        kp.mul_(0.01)
+        page = int(table[0, far // 64])
+        q = qkv[0, :hd]
+        kp[page, 0, far % 64, :] = q * 50.0 / (q.norm() ** 2) * math.sqrt(hd)
+        got = ops.attention(qkv, nh, nkv, hd, kp, vp, table, torch.tensor([0, 1], dtype=torch.int32, device=DEV),
+                            torch.tensor(lens, dtype=torch.int32, device=DEV), seq, pos, 1 / math.sqrt(hd), None, 1, 600)
+        assert torch.allclose(got[0, :hd], vp[page, 0, far % 64, :], atol=1e-3), far
+
+
+def test_sample_greedy_ties_and_banned():
+    # wpc-runtime/src/sampling.rs:57-74
+    logits = torch.tensor([[0.1, 5.0, -2.0, 4.9], [2.0, 2.0, 1.0, 2.0]], device=DEV)
+    state = torch.zeros((4, 4), dtype=torch.int64, device=DEV)
+    slots = torch.tensor([1, 3], dtype=torch.int32, device=DEV)
+    assert ops.sample(logits, slots, state, 0.0, None).tolist() == [1, 0]
+    ban = torch.tensor([1], dtype=torch.int32, device=DEV)
+    assert ops.sample(logits, slots, state, 0.0, ban).tolist() == [3, 0]
+    ban = torch.tensor([1, 3], dtype=torch.int32, device=DEV)
+    assert ops.sample(logits, slots, state, 0.0, ban).tolist() == [0, 0]
+    assert state[:, 3].tolist() == [0, 3, 0, 3]
+
+
+@pytest.mark.parametrize("V", [300, 1000, 152064])
+def test_sample_temperature_picks_the_cdf_index(V):
+    from plain import qwen2_plain as P
+    logits = rnd((3, V), seed=V, scale=2.0)
+    state = torch.tensor([[0, 7, r, 5] for r in range(3)], dtype=torch.int64, device=DEV)
+    slots = torch.arange(3, dtype=torch.int32, device=DEV)
+    got = ops.sample(logits, slots, state, 0.8, None).tolist()
+    for r in range(3):
+        u = P.uniform_for(7, r, 5)
+        idx, cdf, target = P.sample_temperature(logits[r].cpu().numpy(), 0.8, u)
+        lo = cdf[got[r] - 1] if got[r] > 0 else 0.0
+        slack = 1e-5 * cdf[-1]
+        assert lo - slack <= target <= cdf[got[r]] + slack, (got[r], idx)
+    assert state[:, 3].tolist() == [6, 6, 6]
+
+
+def test_fill_normal_moments():
+    t = torch.empty(1 << 20, dtype=torch.float32, device=DEV)
+    ops.fill_normal(t, 1234, 1.0, 0.02)
+    assert abs(t.mean().item() - 1.0) < 2e-4 and abs(t.std().item() - 0.02) < 2e-4
+    t2 = torch.empty_like(t)
+    ops.fill_normal(t2, 1235, 1.0, 0.02)
+    assert not torch.equal(t, t2)
