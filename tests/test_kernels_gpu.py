@@ -202,3 +202,57 @@ def test_fill_normal_moments():
     t2 = torch.empty_like(t)
     ops.fill_normal(t2, 1235, 1.0, 0.02)
     assert not torch.equal(t, t2)
+
+
+# ---- the tensor-core product against its plain twin and the torch reference ----------------------
+TC_SHAPES = [(1, 128, 64), (8, 256, 128), (8, 4608, 3584), (8, 3584, 18944), (64, 1000, 520), (100, 384, 96),
+             (129, 200, 72), (256, 256, 256), (300, 1000, 520), (2048, 512, 256), (513, 4608, 3584), (16, 37888, 3584)]
+
+
+@pytest.mark.parametrize("shape", TC_SHAPES)
+@pytest.mark.parametrize("mode", ["plain", "bias_f32out", "residual"])
+def test_tensor_core_linear(shape, mode):
+    M, N, K = shape
+    x, w = rnd((M, K), torch.bfloat16, 21), rnd((N, K), torch.bfloat16, 22, 0.05)
+    swap, bn, splits = ops.plan_tensor_core_linear(M, N, K)
+    if mode == "plain":
+        got, want = ops.linear(x, w), ops.linear_plain(x, w)
+        tol = 1.2e-2
+    elif mode == "bias_f32out":
+        bias = rnd((N,), seed=23)
+        got = ops.linear(x, w, bias, out_dtype=torch.float32)
+        want = ops.linear_plain(x, w, bias, out_dtype=torch.float32)
+        tol = 2e-3
+    else:
+        r0 = rnd((M, N), seed=24)
+        got, want = ops.linear(x, w, residual=r0.clone()), ops.linear_plain(x, w, residual=r0.clone())
+        tol = 2e-3
+    assert ops.device_status() == 0
+    err = (got.float() - want.float()).abs().max().item()
+    mag = want.float().abs().max().item()
+    assert err <= tol * mag, f"{shape} swap={swap} bn={bn} splits={splits}: error {err} against {mag}"
+    if M <= 300 and N <= 1000:
+        ref_out = ref.linear(x.cpu(), w.cpu(), None if mode == "plain" else (bias.cpu() if mode == "bias_f32out" else None),
+                             out_dtype=got.dtype) if mode != "residual" else None
+        if ref_out is not None:
+            assert (got.cpu().float() - ref_out.float()).abs().max().item() <= tol * mag
+
+
+def test_tensor_core_linear_finds_one_element():
+    """Every (row, k) position reaches the right output: a single one in x picks one column of w."""
+    M, N, K = 40, 300, 200
+    w = rnd((N, K), torch.bfloat16, 31)
+    for (m, k) in [(0, 0), (39, 199), (17, 63), (17, 64), (5, 127), (5, 128)]:
+        x = torch.zeros((M, K), dtype=torch.bfloat16, device=DEV)
+        x[m, k] = 1.0
+        got = ops.linear(x, w, out_dtype=torch.float32)
+        want = torch.zeros((M, N), device=DEV)
+        want[m] = w[:, k].float()
+        assert torch.equal(got, want), (m, k)
+
+
+def test_tensor_core_linear_repeated_calls_share_scratch():
+    x, w = rnd((8, 3584), torch.bfloat16, 41), rnd((4608, 3584), torch.bfloat16, 42, 0.05)
+    first = ops.linear(x, w)
+    for _ in range(3):
+        assert torch.equal(ops.linear(x, w), first)

@@ -31,6 +31,11 @@ int wpc_fill_normal(void* out, int dtype, size_t n, uint64_t key, float mean, fl
 int wpc_gemm_simt(const void* A, int a_dtype, int lda, const void* W, int w_dtype, int ldw, const float* bias,
                   void* C, int out_dtype, int ldc, int accumulate, int M, int N, int K, cudaStream_t stream);
 
+int wpc_gemm_tc_workspace(int rows_a, int rows_b, int bn, int splits, size_t* scratch_floats, int* n_counters);
+int wpc_gemm_tc(const void* a, int lda, int rows_a, const void* b, int ldb, int rows_b, int K, const float* bias,
+                void* out, int out_dtype, int ldc, int accumulate, int swap, int bn, int splits, float* scratch,
+                size_t scratch_floats, int* counters, int n_counters, int* status, cudaStream_t stream);
+
 int wpc_attention_plain(const void* q, int q_stride, void* out, int out_stride, int dtype, const void* k_pages,
                         const void* v_pages, const int* page_table, int table_width, const int* seq_of_token,
                         const int* positions, int T, int nh, int nkv, int hd, float scale, int window,

@@ -1,0 +1,527 @@
+// bfloat16 matrix product on the 5th-generation tensor cores of sm_100a:
+//
+//     D[M, N] = A[M, K] . B[N, K]^T        (both operands row-major with K contiguous)
+//
+// One CTA computes one 128 x BN tile of D (optionally only a slice of K: split-K).  Operand
+// tiles of 64 K-elements (one 128-byte swizzle row) travel from global to shared memory by TMA
+// through a ring of stages; a single thread issues tcgen05.mma into a float32 accumulator in
+// tensor memory; four warps read the accumulator back with tcgen05.ld and write the result.
+//
+//   warp 0      producer: arms a stage's "full" barrier and starts the two TMA loads
+//   warp 1      allocates tensor memory, issues the MMAs, frees tensor memory at the end
+//   warps 2..5  epilogue: TMEM -> registers -> (+bias, +residual, type) -> global
+//
+// Two output arrangements:
+//   normal   A = activations [tokens, K], B = weights [features, K]; out[token, feature]
+//   swapped  A = weights [features, K], B = activations [tokens <= 128, K]; the tile is
+//            D^T and the epilogue writes out[token, feature].  This keeps the 128-row MMA
+//            full when there are only a few tokens (decode), so the weights stream once at
+//            full width.
+// With split-K every CTA of a tile writes its partial sums to scratch memory and takes a
+// ticket; the CTA that draws the last ticket adds the partial sums in slice order (so the
+// result does not depend on which CTA came last) and runs the epilogue.  Nobody waits for
+// anybody.  Every wait on an mbarrier is bounded: when it runs out the kernel records
+// WPC_ERR_DEVICE_WAIT in `status`, lets its copies land, frees its tensor memory and returns.
+//
+// The math is the reference's y = W x + b (wpc-runtime/src/weights.rs:59-78) in bfloat16
+// inputs with float32 accumulation.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "api.h"
+#include "common.cuh"
+
+namespace wpc {
+namespace tc {
+
+constexpr int BM = 128;            // rows of A per tile = MMA M
+constexpr int BK = 64;             // K elements per stage: 128 bytes of bfloat16, one swizzle row
+constexpr int UMMA_K = 16;         // K of one tcgen05.mma for 16-bit inputs
+constexpr int THREADS = 192;
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // 2 s
+
+struct Params {
+  int M, N, K;                 // rows of A, rows of B, shared dimension
+  int k_blocks;                // ceil(K / BK)
+  int splits;                  // CTAs along K per tile
+  const float* bias;           // [features] or null
+  void* out;
+  int ldc;                     // row stride of out, in elements
+  int out_bf16;                // 1: bfloat16, 0: float32
+  int accumulate;              // 1: out (float32) += result
+  float* scratch;              // split-K partial sums: [tile][split][BN][BM] float32
+  int* counters;               // one ticket counter per tile, zero between launches
+  int* status;                 // device error word (may be null)
+};
+
+// ---- PTX wrappers -----------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait: false if the barrier did not flip within WAIT_LIMIT_NS.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_ns();
+  for (;;) {
+    for (int i = 0; i < 256; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (global_ns() - t0 > WAIT_LIMIT_NS) return false;
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* holder, int cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(holder)), "r"(cols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, int cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// The barrier gets one arrival when all MMAs issued so far by this thread have finished.
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+// 32 lanes x 32 columns of 32 bits: thread i of the warp gets lane (base lane + i), columns c..c+31.
+__device__ __forceinline__ void tmem_ld32(uint32_t addr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(addr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t addr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(addr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, swizzled in
+// 1024-byte groups of 8 rows (what TMA writes with CU_TENSOR_MAP_SWIZZLE_128B): start address,
+// 1024 bytes from one group of 8 rows to the next, descriptor version 1, 128-byte swizzle.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFF) >> 4);            // bits 0..13: start address / 16
+  d |= (uint64_t)1 << 16;                            // bits 16..29: leading byte offset / 16 (unused with swizzle)
+  d |= (uint64_t)(1024 >> 4) << 32;                  // bits 32..45: stride byte offset / 16
+  d |= (uint64_t)1 << 46;                            // bits 46..47: version 1 (sm_100)
+  d |= (uint64_t)2 << 61;                            // bits 61..63: SWIZZLE_128B
+  return d;
+}
+// Instruction descriptor: float32 accumulator, bfloat16 A and B, both K-major, M = 128, N = n.
+__host__ __device__ constexpr uint32_t instr_desc(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+template <int BN>
+struct Smem {
+  static constexpr int STAGES = BN >= 256 ? 4 : (BN >= 128 ? 6 : 6);
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int TILES_BYTES = STAGES * STAGE_BYTES;
+  static constexpr int TOTAL = TILES_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+  static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+};
+
+__device__ __forceinline__ void store_row32(const Params& p, int row, int col0, int n_cols, const float (&v)[32]) {
+  // out[row, col0 .. col0 + n_cols) from v (normal arrangement: this thread owns a row)
+  if (p.accumulate) {
+    float* dst = (float*)p.out + (size_t)row * p.ldc + col0;
+    if (n_cols == 32 && (((uintptr_t)dst) & 15) == 0) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        float4 o = *(float4*)(dst + j);
+        o.x += v[j]; o.y += v[j + 1]; o.z += v[j + 2]; o.w += v[j + 3];
+        *(float4*)(dst + j) = o;
+      }
+    } else {
+      for (int j = 0; j < n_cols; ++j) dst[j] += v[j];
+    }
+  } else if (p.out_bf16) {
+    __nv_bfloat16* dst = (__nv_bfloat16*)p.out + (size_t)row * p.ldc + col0;
+    if (n_cols == 32 && (((uintptr_t)dst) & 15) == 0) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 8) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(v[j], v[j + 1]), b = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+        __nv_bfloat162 c = __floats2bfloat162_rn(v[j + 4], v[j + 5]), d = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+        uint4 o;
+        o.x = *(uint32_t*)&a; o.y = *(uint32_t*)&b; o.z = *(uint32_t*)&c; o.w = *(uint32_t*)&d;
+        *(uint4*)(dst + j) = o;
+      }
+    } else {
+      for (int j = 0; j < n_cols; ++j) dst[j] = __float2bfloat16_rn(v[j]);
+    }
+  } else {
+    float* dst = (float*)p.out + (size_t)row * p.ldc + col0;
+    if (n_cols == 32 && (((uintptr_t)dst) & 15) == 0) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) *(float4*)(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+    } else {
+      for (int j = 0; j < n_cols; ++j) dst[j] = v[j];
+    }
+  }
+}
+
+template <int BN, bool SWAP>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
+  using S = Smem<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = (uint64_t*)(tiles + S::TILES_BYTES);
+  uint64_t* empty = full + S::STAGES;
+  uint64_t* accum_full = empty + S::STAGES;
+  uint32_t* tmem_holder = (uint32_t*)(accum_full + 1);
+  int* flags = (int*)(tmem_holder + 1);          // [0]: a wait ran out, [1]: this CTA drew the last ticket
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
+  const int split = blockIdx.z;
+  const int kb_per = (p.k_blocks + p.splits - 1) / p.splits;
+  const int kb0 = split * kb_per;
+  const int kb1 = min(p.k_blocks, kb0 + kb_per);
+  const int n_kb = max(kb1 - kb0, 0);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S::STAGES; ++s) {
+      mbar_init(full + s, 1);
+      mbar_init(empty + s, 1);
+    }
+    mbar_init(accum_full, 1);
+    flags[0] = 0;
+    flags[1] = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(tmem_holder, S::TMEM_COLS);
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int i = 0; i < n_kb; ++i) {
+        const int s = i % S::STAGES;
+        const uint32_t ph = (i / S::STAGES) & 1;
+        if (!mbar_wait(empty + s, ph ^ 1)) { atomicExch(flags, 1); break; }
+        mbar_expect_tx(full + s, S::STAGE_BYTES);
+        uint8_t* a_dst = tiles + s * S::STAGE_BYTES;
+        tma_load_2d(a_dst, &map_a, (kb0 + i) * BK, m0, full + s);
+        tma_load_2d(a_dst + S::A_BYTES, &map_b, (kb0 + i) * BK, n0, full + s);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc(BN);
+      bool ok = true;
+      for (int i = 0; i < n_kb && ok; ++i) {
+        const int s = i % S::STAGES;
+        const uint32_t ph = (i / S::STAGES) & 1;
+        if (!mbar_wait(full + s, ph)) { atomicExch(flags, 1); ok = false; break; }
+        fence_after_sync();
+        const uint32_t a_addr = smem_u32(tiles + s * S::STAGE_BYTES);
+        const uint64_t da = smem_desc_sw128(a_addr), db = smem_desc_sw128(a_addr + S::A_BYTES);
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k) {
+          // 32 bytes further along K inside the swizzled row: + 2 in the (address / 16) field
+          umma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(empty + s);       // the stage is free again once these MMAs have read it
+      }
+      umma_commit(accum_full);        // arrives when everything issued above has finished
+    }
+  } else {
+    // ---- epilogue: warps 2..5 read lanes 32*(warp % 4) .. +31 of the accumulator ----
+    const int q = warp & 3;
+    const int r = q * 32 + lane;                        // row of the tile = TMEM lane
+    const int et = threadIdx.x - 64;                    // 0..127 among the epilogue threads
+    bool ok = mbar_wait(accum_full, 0);
+    ok = __all_sync(0xffffffffu, ok);              // tcgen05.ld needs the whole warp on one path
+    if (!ok) atomicExch(flags, 1);
+    fence_after_sync();
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+    const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
+    const int n_valid = min(BN, p.N - n0);              // columns of the tile that exist
+    const bool have_acc = n_kb > 0 && ok;
+
+    bool run_epilogue = ok;
+    if (p.splits > 1) {
+      // partial sums to scratch: [tile][split][column][row], rows contiguous
+      float* part = p.scratch + ((size_t)tile_id * p.splits + split) * (size_t)(BN * BM);
+      for (int c = 0; c < n_valid; c += 32) {
+        uint32_t v[32];
+        if (have_acc) {
+          if (BN >= 32) tmem_ld32(lane_addr + c, v); else tmem_ld16(lane_addr + c, v);
+          tmem_ld_wait();
+        }
+        const int nc = min(32, n_valid - c);
+        for (int j = 0; j < nc; ++j) part[(size_t)(c + j) * BM + r] = have_acc ? __uint_as_float(v[j]) : 0.f;
+      }
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (et == 0) {
+        const int ticket = atomicAdd(p.counters + tile_id, 1);
+        flags[1] = (ticket == p.splits - 1);
+        if (ticket == p.splits - 1) p.counters[tile_id] = 0;      // ready for the next launch
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      run_epilogue = ok && flags[1];
+      if (run_epilogue) __threadfence();
+    }
+
+    if (run_epilogue) {
+      const float* part0 = p.scratch ? p.scratch + (size_t)tile_id * p.splits * (size_t)(BN * BM) : nullptr;
+      for (int c = 0; c < n_valid; c += 32) {
+        const int nc = min(32, n_valid - c);
+        float v[32];
+        if (p.splits > 1) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = 0.f;
+          for (int z = 0; z < p.splits; ++z) {
+            const float* pz = part0 + (size_t)z * (BN * BM);
+            for (int j = 0; j < nc; ++j) v[j] += __ldcg(pz + (size_t)(c + j) * BM + r);
+          }
+        } else {
+          uint32_t u[32];
+          if (have_acc) {
+            if (BN >= 32) tmem_ld32(lane_addr + c, u); else tmem_ld16(lane_addr + c, u);
+            tmem_ld_wait();
+          }
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = have_acc ? __uint_as_float(u[j]) : 0.f;
+        }
+        if (!SWAP) {
+          // this thread owns token row m0 + r and features n0 + c ..
+          const int row = m0 + r;
+          if (p.bias) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (j < nc) v[j] += p.bias[n0 + c + j];
+          }
+          if (row < p.M) store_row32(p, row, n0 + c, nc, v);
+        } else {
+          // this thread owns feature m0 + r, the columns are tokens n0 + c ..
+          const int feat = m0 + r;
+          if (feat < p.M) {
+            const float b = p.bias ? p.bias[feat] : 0.f;
+            for (int j = 0; j < nc; ++j) {
+              const size_t o = (size_t)(n0 + c + j) * p.ldc + feat;
+              const float val = v[j] + b;
+              if (p.accumulate) ((float*)p.out)[o] += val;
+              else if (p.out_bf16) ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(val);
+              else ((float*)p.out)[o] = val;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  fence_before_sync();
+  __syncthreads();
+  if (flags[0]) {
+    // a wait ran out: give copies in flight time to land before shared memory goes away
+    if (threadIdx.x == 0 && p.status) atomicExch(p.status, WPC_ERR_DEVICE_WAIT);
+    const unsigned long long t0 = global_ns();
+    while (global_ns() - t0 < 2000000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    fence_after_sync();
+    tmem_dealloc(tmem_base, S::TMEM_COLS);
+  }
+}
+
+// ---- host side --------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  });
+  return fn;
+}
+
+struct MapKey {
+  const void* ptr;
+  int rows, cols, ld, box_rows;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = (size_t)k.ptr;
+    h = h * 1000003u ^ (size_t)k.rows;
+    h = h * 1000003u ^ (size_t)k.cols;
+    h = h * 1000003u ^ (size_t)k.ld;
+    h = h * 1000003u ^ (size_t)k.box_rows;
+    return h;
+  }
+};
+
+// A tensor map for a row-major bfloat16 matrix [rows, cols] with row stride ld elements,
+// copied in boxes of box_rows x 64 with the 128-byte swizzle.  Encoded maps are kept: the
+// same weights are multiplied step after step.
+static int tensor_map(const void* ptr, int rows, int cols, int ld, int box_rows, CUtensorMap* out) {
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  static std::mutex mu;
+  const MapKey key{ptr, rows, cols, ld, box_rows};
+  {
+    std::lock_guard<std::mutex> g(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return 0; }
+  }
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return WPC_ERR_UNSUPPORTED;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return WPC_ERR_UNSUPPORTED;
+  std::lock_guard<std::mutex> g(mu);
+  if (cache.size() > 8192) cache.clear();
+  cache[key] = *out;
+  return 0;
+}
+
+template <int BN, bool SWAP>
+static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, cudaStream_t stream) {
+  using S = Smem<BN>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, SWAP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         S::TOTAL);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid((p.M + BM - 1) / BM, (p.N + BN - 1) / BN, p.splits);
+  gemm_tc_kernel<BN, SWAP><<<grid, THREADS, S::TOTAL, stream>>>(ma, mb, p);
+  return launch_status();
+}
+
+}  // namespace tc
+}  // namespace wpc
+
+using namespace wpc;
+using namespace wpc::tc;
+
+extern "C" {
+
+// How many float32 of scratch and how many counters a call with these sizes needs.
+int wpc_gemm_tc_workspace(int rows_a, int rows_b, int bn, int splits, size_t* scratch_floats, int* n_counters) {
+  const int tiles = ((rows_a + BM - 1) / BM) * ((rows_b + bn - 1) / bn);
+  *scratch_floats = splits > 1 ? (size_t)tiles * splits * bn * BM : 0;
+  *n_counters = splits > 1 ? tiles : 0;
+  return 0;
+}
+
+// a: [rows_a, K] bfloat16, row stride lda; b: [rows_b, K] bfloat16, row stride ldb.
+// swap = 0: out[rows_a, rows_b] (bias over rows_b);  swap = 1: out[rows_b, rows_a] (bias over
+// rows_a).  bn: the tile's extent along rows_b (16, 32, 64, 128; 256 without swap).
+int wpc_gemm_tc(const void* a, int lda, int rows_a, const void* b, int ldb, int rows_b, int K, const float* bias,
+                void* out, int out_dtype, int ldc, int accumulate, int swap, int bn, int splits, float* scratch,
+                size_t scratch_floats, int* counters, int n_counters, int* status, cudaStream_t stream) {
+  if (rows_a <= 0 || rows_b <= 0) return 0;
+  if (K <= 0 || (lda % 8) || (ldb % 8) || (((uintptr_t)a) & 15) || (((uintptr_t)b) & 15)) return WPC_ERR_UNSUPPORTED;
+  if (accumulate && out_dtype != WPC_DTYPE_F32) return WPC_ERR_BAD_ARGUMENT;
+  Params p;
+  p.M = rows_a; p.N = rows_b; p.K = K;
+  p.k_blocks = (K + BK - 1) / BK;
+  p.splits = splits < 1 ? 1 : (splits > p.k_blocks ? p.k_blocks : splits);
+  p.bias = bias; p.out = out; p.ldc = ldc;
+  p.out_bf16 = out_dtype == WPC_DTYPE_BF16; p.accumulate = accumulate;
+  p.scratch = scratch; p.counters = counters; p.status = status;
+  if (p.splits > 1) {
+    size_t need_f; int need_c;
+    wpc_gemm_tc_workspace(rows_a, rows_b, bn, p.splits, &need_f, &need_c);
+    if (!scratch || !counters || need_f > scratch_floats || need_c > n_counters) return WPC_ERR_TOO_LARGE;
+  }
+  CUtensorMap ma, mb;
+  int rc = tensor_map(a, rows_a, K, lda, BM, &ma);
+  if (rc) return rc;
+  rc = tensor_map(b, rows_b, K, ldb, bn, &mb);
+  if (rc) return rc;
+  if (!swap) {
+    switch (bn) {
+      case 64: return launch<64, false>(ma, mb, p, stream);
+      case 128: return launch<128, false>(ma, mb, p, stream);
+      case 256: return launch<256, false>(ma, mb, p, stream);
+    }
+  } else {
+    switch (bn) {
+      case 16: return launch<16, true>(ma, mb, p, stream);
+      case 32: return launch<32, true>(ma, mb, p, stream);
+      case 64: return launch<64, true>(ma, mb, p, stream);
+      case 128: return launch<128, true>(ma, mb, p, stream);
+    }
+  }
+  return WPC_ERR_UNSUPPORTED;
+}
+
+}  // extern "C"

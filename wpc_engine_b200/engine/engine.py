@@ -87,6 +87,7 @@ class Engine:
         self.vocab_size = model.embedding.vocab_size
         self.max_positions = getattr(model.config, "max_position_embeddings", None)
         self.steps_run = 0
+        self.graph_launches = 0      # kernels that graph replays have launched so far
 
     # -- construction ------------------------------------------------------------------------
     @classmethod
@@ -180,14 +181,16 @@ class Engine:
             meta = torch.zeros(lay.total, dtype=torch.int32, device=self.device)
             ctx = context_from(meta, lay, self.dtype, 1, lay.table_width * PAGE, True)
             graph = torch.cuda.CUDAGraph()
+            before = ops.launch_count
             with torch.cuda.graph(graph):
                 logits = self.model.forward(ctx, self.cache)
-            entry = (graph, meta, logits)
+            entry = (graph, meta, logits, ops.launch_count - before)
             self._graphs[key] = entry
-        graph, meta, logits = entry
+        graph, meta, logits, n_kernels = entry
         meta.copy_(host[: lay.total], non_blocking=True)
         self._ring.sent()
         graph.replay()
+        self.graph_launches += n_kernels
         return True, logits
 
     # -- sampling ----------------------------------------------------------------------------

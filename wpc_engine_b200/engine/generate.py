@@ -8,6 +8,7 @@ token (main.rs:307) is not run.
 """
 from __future__ import annotations
 
+import time
 from dataclasses import dataclass, field
 from typing import List, Optional, Sequence
 
@@ -71,11 +72,18 @@ def advance(live: List[_Live], picked: Sequence[int], opts: GenerationOptions, s
     return go_on, done
 
 
-def generate(engine, prompts: Sequence[Sequence[int]], opts: GenerationOptions) -> List[List[int]]:
+def generate(engine, prompts: Sequence[Sequence[int]], opts: GenerationOptions,
+             stats: Optional[dict] = None) -> List[List[int]]:
     """Generated token ids for each prompt.  `engine` offers open_sequence, close_sequence,
-    step, sample, set_sampler_state and a `cache` with n_pages and n_slots."""
+    step, sample, set_sampler_state and a `cache` with n_pages and n_slots.
+
+    With `stats` (a dict) the loop records what the reference prints to standard error
+    (wpc-runtime/src/main.rs:294, 309): seconds and tokens of the prompt steps and of the
+    single-token steps, summed over the batches."""
     if opts.max_tokens < 1:
         return [[] for _ in prompts]
+    if stats is not None:
+        stats.update(prefill_s=0.0, prefill_tokens=0, decode_s=0.0, decode_tokens=0, decode_steps=0)
     stop = frozenset(int(s) for s in opts.stop_token_ids)
     outputs: List[Optional[List[int]]] = [None] * len(prompts)
     batches = plan_batches([len(p) for p in prompts], opts.max_tokens, engine.cache.n_pages,
@@ -86,10 +94,22 @@ def generate(engine, prompts: Sequence[Sequence[int]], opts: GenerationOptions) 
             engine.set_sampler_state([s.slot for s in live], opts.seed, [s.request for s in live])
             entries = [SequenceStep(s.slot, list(prompts[s.request]), want=[len(prompts[s.request]) - 1])
                        for s in live]
+            first = True
             while live:
+                t0 = time.perf_counter()
                 logits = engine.step(entries)
                 picked = engine.sample(logits, [s.slot for s in live], opts.temperature,
-                                       opts.banned_token_ids).tolist()
+                                       opts.banned_token_ids).tolist()      # the step's one device-to-host read
+                if stats is not None:
+                    dt = time.perf_counter() - t0
+                    if first:
+                        stats["prefill_s"] += dt
+                        stats["prefill_tokens"] += sum(len(e.tokens) for e in entries)
+                    else:
+                        stats["decode_s"] += dt
+                        stats["decode_tokens"] += len(entries)
+                        stats["decode_steps"] += 1
+                first = False
                 live, done = advance(live, picked, opts, stop)
                 for seq in done:
                     outputs[seq.request] = seq.output

@@ -71,7 +71,12 @@ def _stream():
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+launch_count = 0          # kernels launched through this module (graph replays are counted by the engine)
+
+
 def _check(name: str, rc: int) -> None:
+    global launch_count
+    launch_count += 1
     if rc == 0:
         return
     if rc in _ERRORS:
@@ -111,9 +116,14 @@ def rmsnorm(x: torch.Tensor, gain: torch.Tensor, eps: float, out_dtype: torch.dt
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
-           out_dtype: Optional[torch.dtype] = None, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+           out_dtype: Optional[torch.dtype] = None, residual: Optional[torch.Tensor] = None,
+           plain: bool = False) -> torch.Tensor:
     """x [T, K] times w [N, K] transposed, plus bias (float32 [N]).  With `residual` (float32
-    [T, N], contiguous) the result is added to it in place in float32 and it is returned."""
+    [T, N], contiguous) the result is added to it in place in float32 and it is returned.
+
+    bfloat16 x and w go to the tensor-core kernel (csrc/gemm_tc.cu) when their layout allows
+    TMA (16-byte aligned rows); everything else, and everything with `plain`, runs on the
+    CUDA cores in float32 (csrc/gemm_simt.cu)."""
     _rows(x, "x")
     _rows(w, "w")
     M, K = x.shape
@@ -130,7 +140,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
         accumulate = 0
     if M == 0:
         return out
-    if _fast_linear(x, w, bias, out, accumulate):
+    if not plain and _tensor_core_linear(x, w, bias, out, accumulate):
         return out
     _check("gemm_simt", library().wpc_gemm_simt(
         _p(x), _code(x.dtype), x.stride(0), _p(w), _code(w.dtype), w.stride(0), _p(bias), _p(out),
@@ -138,20 +148,76 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
     return out
 
 
-def _fast_linear(x, w, bias, out, accumulate) -> bool:
-    """The tensor-core product, where it applies; returns False to leave it to the plain one."""
-    return False
-
-
 def linear_plain(x, w, bias=None, out_dtype=None, residual=None) -> torch.Tensor:
     """The same product on the CUDA cores only (the plain twin of `linear`)."""
-    global _fast_linear
-    saved = _fast_linear
-    _fast_linear = lambda *a: False
-    try:
-        return linear(x, w, bias, out_dtype, residual)
-    finally:
-        _fast_linear = saved
+    return linear(x, w, bias, out_dtype, residual, plain=True)
+
+
+_SMS = 148
+_WORKSPACE_FLOATS = 8 << 20        # 32 MiB of split-K partial sums
+_WORKSPACE_COUNTERS = 4096
+_workspaces = {}
+
+
+def workspace(device):
+    """(scratch float32, ticket counters int32, status int32) of a device, allocated once.
+    Kernels that use them run one after another on a stream; calls on several streams at
+    once would share them and race."""
+    key = torch.device(device).index or 0
+    ws = _workspaces.get(key)
+    if ws is None:
+        ws = (torch.empty(_WORKSPACE_FLOATS, dtype=torch.float32, device=device),
+              torch.zeros(_WORKSPACE_COUNTERS, dtype=torch.int32, device=device),
+              torch.zeros(1, dtype=torch.int32, device=device))
+        _workspaces[key] = ws
+    return ws
+
+
+def device_status(device="cuda") -> int:
+    """The device error word (0: none): set when a bounded wait inside a kernel ran out."""
+    ws = _workspaces.get(torch.device(device).index or 0)
+    return 0 if ws is None else int(ws[2].item())
+
+
+def plan_tensor_core_linear(M: int, N: int, K: int):
+    """(swap, bn, splits) for x [M, K] . w [N, K]^T.  Few tokens: the weights take the MMA's
+    128 rows and the tokens its columns (swap).  Few tiles: K is split over CTAs so that
+    about all SMs stream weights."""
+    k_blocks = (K + 63) // 64
+    if M <= 128:
+        swap, bn = True, (16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128)
+        tiles = (N + 127) // 128
+    else:
+        swap, bn = False, (256 if N >= 256 else 128 if N > 64 else 64)
+        tiles = ((M + 127) // 128) * ((N + bn - 1) // bn)
+    splits = 1
+    if tiles * 2 <= _SMS:
+        splits = max(1, min(_SMS // tiles, k_blocks // 4, 16))
+        while splits > 1 and tiles * splits * bn * 128 > _WORKSPACE_FLOATS:
+            splits -= 1
+        if tiles > _WORKSPACE_COUNTERS:
+            splits = 1
+    return swap, bn, splits
+
+
+def _tensor_core_linear(x, w, bias, out, accumulate) -> bool:
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        return False
+    M, K = x.shape
+    N = w.shape[0]
+    if K % 8 or x.stride(0) % 8 or w.stride(0) % 8 or x.data_ptr() % 16 or w.data_ptr() % 16:
+        return False
+    swap, bn, splits = plan_tensor_core_linear(M, N, K)
+    scratch, counters, status = workspace(x.device)
+    if swap:
+        a, b = w, x
+    else:
+        a, b = x, w
+    _check("gemm_tc", library().wpc_gemm_tc(
+        _p(a), a.stride(0), a.shape[0], _p(b), b.stride(0), b.shape[0], K, _p(bias), _p(out), _code(out.dtype),
+        out.stride(0), accumulate, int(swap), bn, splits, _p(scratch), ctypes.c_size_t(scratch.numel()),
+        _p(counters), counters.numel(), _p(status), _stream()))
+    return True
 
 
 def silu_mul(gu: torch.Tensor, inner: int) -> torch.Tensor:
