@@ -525,3 +525,103 @@ int wpc_gemm_tc(const void* a, int lda, int rows_a, const void* b, int ldb, int 
 }
 
 }  // extern "C"
+
+// ---- the variant that allocates nothing (see no_alloc.h) ------------------------------------------
+#include "no_alloc.h"
+
+// Scratch of the static variant: partial sums, then the tickets, then a status word.  In host
+// code this name is only a handle for cudaGetSymbolAddress, never a device address.
+static __device__ __align__(256) unsigned char wpc_static_scratch[WPC_STATIC_SCRATCH_BYTES];
+
+namespace wpc {
+namespace tc {
+
+constexpr int MAX_DEVICES = 64;
+
+// The device address of the scratch array on the current device, looked up once per device.
+static int static_scratch_address(unsigned char** out) {
+  static unsigned char* addr[MAX_DEVICES] = {nullptr};
+  static std::mutex mu;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= MAX_DEVICES) return WPC_ERR_UNSUPPORTED;
+  std::lock_guard<std::mutex> g(mu);
+  if (!addr[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, wpc_static_scratch);
+    if (e != cudaSuccess) return (int)e;
+    addr[dev] = (unsigned char*)p;
+  }
+  *out = addr[dev];
+  return 0;
+}
+
+// A tensor map built on the caller's stack: the static variant keeps no cache, so that it
+// touches no heap either.
+static int tensor_map_uncached(const void* ptr, int rows, int cols, int ld, int box_rows, CUtensorMap* out) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return WPC_ERR_UNSUPPORTED;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : WPC_ERR_UNSUPPORTED;
+}
+
+}  // namespace tc
+}  // namespace wpc
+
+extern "C" int wpc_linear_few_tokens_static(const void* x, int ldx, int tokens, const void* w, int ldw, int features,
+                                            int K, const float* bias, void* out, int out_dtype, int ldc, int splits,
+                                            cudaStream_t stream) {
+  if (tokens < 1 || tokens > 128 || features < 1 || K < 1) return WPC_ERR_BAD_ARGUMENT;
+  if ((ldx % 8) || (ldw % 8) || (((uintptr_t)x) & 15) || (((uintptr_t)w) & 15)) return WPC_ERR_UNSUPPORTED;
+  if (out_dtype != WPC_DTYPE_BF16 && out_dtype != WPC_DTYPE_F32) return WPC_ERR_BAD_ARGUMENT;
+  const int bn = tokens <= 16 ? 16 : tokens <= 32 ? 32 : tokens <= 64 ? 64 : 128;
+  const int tiles = (features + BM - 1) / BM;
+  const int k_blocks = (K + BK - 1) / BK;
+  if (tiles > WPC_STATIC_MAX_TILES) return WPC_ERR_TOO_LARGE;
+  const size_t per_split = (size_t)tiles * bn * BM;
+  if (splits == 0) {
+    splits = 148 / tiles;
+    if (splits > k_blocks / 4) splits = k_blocks / 4;
+    if (splits > 16) splits = 16;
+    while (splits > 1 && per_split * splits > WPC_STATIC_SCRATCH_FLOATS) --splits;
+    if (splits < 1) splits = 1;
+  }
+  if (splits > k_blocks) splits = k_blocks;
+  if (splits > 1 && per_split * splits > WPC_STATIC_SCRATCH_FLOATS) return WPC_ERR_TOO_LARGE;
+
+  unsigned char* base = nullptr;
+  int rc = static_scratch_address(&base);
+  if (rc) return rc;
+  float* scratch = (float*)base;
+  int* counters = (int*)(base + (size_t)WPC_STATIC_SCRATCH_FLOATS * 4);
+  int* status = counters + WPC_STATIC_MAX_TILES;
+  // the tickets must start at zero whatever an earlier call left behind
+  cudaError_t e = cudaMemsetAsync(counters, 0, 8192, stream);
+  if (e != cudaSuccess) return (int)e;
+
+  Params p;
+  p.M = features; p.N = tokens; p.K = K;
+  p.k_blocks = k_blocks;
+  p.splits = splits;
+  p.bias = bias; p.out = out; p.ldc = ldc;
+  p.out_bf16 = out_dtype == WPC_DTYPE_BF16; p.accumulate = 0;
+  p.scratch = scratch; p.counters = counters; p.status = status;
+  CUtensorMap ma, mb;
+  rc = tensor_map_uncached(w, features, K, ldw, BM, &ma);
+  if (rc) return rc;
+  rc = tensor_map_uncached(x, tokens, K, ldx, bn, &mb);
+  if (rc) return rc;
+  switch (bn) {
+    case 16: return launch<16, true>(ma, mb, p, stream);
+    case 32: return launch<32, true>(ma, mb, p, stream);
+    case 64: return launch<64, true>(ma, mb, p, stream);
+    default: return launch<128, true>(ma, mb, p, stream);
+  }
+}
