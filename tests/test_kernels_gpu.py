@@ -256,3 +256,32 @@ def test_tensor_core_linear_repeated_calls_share_scratch():
     first = ops.linear(x, w)
     for _ in range(3):
         assert torch.equal(ops.linear(x, w), first)
+
+
+# ---- decode attention (split over CTAs) -----------------------------------------------------------
+@pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 16), (3, 1, 32), (4, 2, 48), (14, 2, 64), (28, 4, 128), (16, 1, 128), (2, 2, 80)])
+@pytest.mark.parametrize("window", [None, 100])
+@pytest.mark.parametrize("splits", [None, 1, 3, 16])
+def test_attention_decode_splits(nh, nkv, hd, window, splits):
+    lens, new = [1, 64, 65, 700, 333, 128], [1] * 6
+    qkv, kp, vp, table, seq, pos = paged_case(torch.bfloat16, nh, nkv, hd, lens, new, seed=9)
+    cu = torch.arange(7, dtype=torch.int32, device=DEV)
+    ctx = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(hd)
+    got = ops.attention(qkv, nh, nkv, hd, kp, vp, table, cu, ctx, seq, pos, scale, window, 1, max(lens), splits=splits)
+    want = ref.attention_plain(qkv.cpu(), nh, nkv, hd, kp.cpu(), vp.cpu(), table.cpu(), seq.cpu(), pos.cpu(),
+                               scale, window)
+    close(got.cpu(), want, torch.bfloat16)
+
+
+def test_attention_prefill_window_edges():
+    """A window's edge: the key just outside the window is made huge; it must not be seen, and
+    the key just inside must."""
+    nh, nkv, hd, W = 2, 1, 32, 40
+    lens, new = [200], [150]
+    qkv, kp, vp, table, seq, pos = paged_case(torch.bfloat16, nh, nkv, hd, lens, new, seed=3)
+    cu = torch.tensor([0, 150], dtype=torch.int32, device=DEV)
+    ctx = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    got = ops.attention(qkv, nh, nkv, hd, kp, vp, table, cu, ctx, seq, pos, 0.2, W, 150, 200)
+    want = ref.attention_plain(qkv.cpu(), nh, nkv, hd, kp.cpu(), vp.cpu(), table.cpu(), seq.cpu(), pos.cpu(), 0.2, W)
+    close(got.cpu(), want, torch.bfloat16)

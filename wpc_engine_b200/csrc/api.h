@@ -41,6 +41,16 @@ int wpc_attention_plain(const void* q, int q_stride, void* out, int out_stride, 
                         const int* positions, int T, int nh, int nkv, int hd, float scale, int window,
                         cudaStream_t stream);
 
+int wpc_attention_mma_supports(int nh, int nkv, int hd);
+int wpc_attention_decode(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+                         const void* v_pages, const int* page_table, int table_width, const int* ctx_lens, int B,
+                         int nh, int nkv, int hd, float scale, int window, int splits, float* part_o, float* part_ml,
+                         cudaStream_t stream);
+int wpc_attention_prefill(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+                          const void* v_pages, const int* page_table, int table_width, const int* cu_seqlens,
+                          const int* ctx_lens, int B, int max_new, int nh, int nkv, int hd, float scale, int window,
+                          cudaStream_t stream);
+
 int wpc_sample(const float* logits, int n_rows, int V, const int* slots, long long* seq_state, float temperature,
                const int* banned, int n_banned, int* out, cudaStream_t stream);
 

@@ -1,0 +1,528 @@
+// bfloat16 attention over the paged cache on the tensor cores, with an online softmax in
+// float32 (wpc-runtime/src/model.rs:476-510 is the arithmetic: scaled scores of a query
+// against the visible keys, softmax, weighted values).
+//
+// The query heads that share a KV head are stacked along the MMA's row dimension, so a page
+// of keys and values is read once for the whole group.
+//
+//   decode   one query token per sequence.  grid = (splits, kv heads, sequences); the 16 MMA
+//            rows hold the group's query heads; the four warps of a CTA take the four
+//            16-key quarters of each 64-key page and are merged at the end; a sequence's
+//            pages are divided over `splits` CTAs whose partial results (unnormalised
+//            output, running maximum, running sum) a second kernel combines.
+//   prefill  any number of new tokens per sequence.  grid = (row tiles, kv heads,
+//            sequences); a tile is 64 rows of (token, head-in-group), 16 per warp; every warp
+//            walks the pages up to the tile's last visible key.
+//
+// Keys and values of a page ([64, head_dim], contiguous) are copied to shared memory with
+// cp.async, two pages in flight, rows padded by 16 bytes so that ldmatrix is free of bank
+// conflicts.  head_dim: multiples of 16 up to 128 (other sizes take the plain kernel).
+#include "api.h"
+#include "common.cuh"
+
+namespace wpc {
+namespace fa {
+
+constexpr int PAGE = WPC_PAGE;
+constexpr int THREADS = 128;
+constexpr float LOG2E = 1.4426950408889634f;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_u32(p)));
+}
+// D(16x8, f32) += A(16x16, bf16, row) * B(16x8, bf16, col)
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *(uint32_t*)&v;
+}
+
+template <int HD>
+struct Cfg {
+  static constexpr int STRIDE = HD + 8;                   // elements per padded row
+  static constexpr int PAGE_ELEMS = PAGE * STRIDE;
+  static constexpr int SMEM_BYTES = 4 * PAGE_ELEMS * 2;   // K and V, two buffers each
+};
+
+// Copies one page ([64, HD], contiguous) into padded shared memory rows.
+template <int HD>
+__device__ __forceinline__ void load_page(__nv_bfloat16* dst, const __nv_bfloat16* src, int tid) {
+  constexpr int CPR = HD / 8;                    // 16-byte chunks per row
+  for (int c = tid; c < PAGE * CPR; c += THREADS) {
+    const int row = c / CPR, col = c - row * CPR;
+    cp_async16(dst + row * Cfg<HD>::STRIDE + col * 8, src + row * HD + col * 8);
+  }
+}
+
+// s[nt] (16 rows x 8 keys each) = q (16 x HD) . K[key0 + 8 nt + .., :]^T for NT key tiles.
+template <int HD, int NT>
+__device__ __forceinline__ void scores(const uint32_t (&qf)[HD / 16][4], const __nv_bfloat16* ks, int key0,
+                                       float (&s)[NT][4], int lane) {
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) s[nt][i] = 0.f;
+  const int mat = lane >> 3, r = lane & 7;
+#pragma unroll
+  for (int kk = 0; kk < HD / 16; ++kk) {
+#pragma unroll
+    for (int np = 0; np < NT / 2; ++np) {
+      uint32_t b[4];
+      const int key = key0 + np * 16 + (mat >> 1) * 8 + r;
+      const int dim = kk * 16 + (mat & 1) * 8;
+      ldmatrix_x4(b, ks + key * Cfg<HD>::STRIDE + dim);
+      mma_bf16(s[2 * np], qf[kk], b[0], b[1]);
+      mma_bf16(s[2 * np + 1], qf[kk], b[2], b[3]);
+    }
+  }
+}
+
+// o (16 x HD) += p (16 x 8 NT keys, bf16 fragments) . V[key0 .., :]
+template <int HD, int NT>
+__device__ __forceinline__ void weighted_values(const uint32_t (&pf)[NT / 2][4], const __nv_bfloat16* vs, int key0,
+                                                float (&o)[HD / 8][4], int lane) {
+  const int mat = lane >> 3, r = lane & 7;
+#pragma unroll
+  for (int kc = 0; kc < NT / 2; ++kc) {
+#pragma unroll
+    for (int dp = 0; dp < HD / 16; ++dp) {
+      uint32_t b[4];
+      const int key = key0 + kc * 16 + (mat & 1) * 8 + r;
+      const int dim = dp * 16 + (mat >> 1) * 8;
+      ldmatrix_x4_trans(b, vs + key * Cfg<HD>::STRIDE + dim);
+      mma_bf16(o[2 * dp], pf[kc], b[0], b[1]);
+      mma_bf16(o[2 * dp + 1], pf[kc], b[2], b[3]);
+    }
+  }
+}
+
+// One online-softmax step for the two rows that a thread holds (lane/4 and lane/4 + 8).
+// `s` holds scaled scores (log2 domain) with -inf where masked; on return it holds the
+// probabilities' numerators; m, l, o are updated (l is a per-thread partial sum).
+template <int HD, int NT>
+__device__ __forceinline__ void softmax_step(float (&s)[NT][4], float (&m)[2], float (&l)[2], float (&o)[HD / 8][4]) {
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    float mx = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) mx = fmaxf(mx, fmaxf(s[nt][2 * h], s[nt][2 * h + 1]));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float m_new = fmaxf(m[h], mx);
+    const bool none = m_new == -INFINITY;
+    const float alpha = none ? 1.f : exp2f(m[h] - m_new);
+    float sum = 0.f;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const float p0 = none ? 0.f : exp2f(s[nt][2 * h] - m_new);
+      const float p1 = none ? 0.f : exp2f(s[nt][2 * h + 1] - m_new);
+      s[nt][2 * h] = p0;
+      s[nt][2 * h + 1] = p1;
+      sum += p0 + p1;
+    }
+    l[h] = l[h] * alpha + sum;
+    m[h] = m_new;
+#pragma unroll
+    for (int d = 0; d < HD / 8; ++d) {
+      o[d][2 * h] *= alpha;
+      o[d][2 * h + 1] *= alpha;
+    }
+  }
+}
+
+template <int NT>
+__device__ __forceinline__ void to_fragments(const float (&s)[NT][4], uint32_t (&pf)[NT / 2][4]) {
+#pragma unroll
+  for (int kc = 0; kc < NT / 2; ++kc) {
+    pf[kc][0] = pack_bf16(s[2 * kc][0], s[2 * kc][1]);
+    pf[kc][1] = pack_bf16(s[2 * kc][2], s[2 * kc][3]);
+    pf[kc][2] = pack_bf16(s[2 * kc + 1][0], s[2 * kc + 1][1]);
+    pf[kc][3] = pack_bf16(s[2 * kc + 1][2], s[2 * kc + 1][3]);
+  }
+}
+
+// Query fragments of the two rows (row_lo, row_hi) of this thread, straight from global memory;
+// a null pointer gives a zero row.
+template <int HD>
+__device__ __forceinline__ void load_q(uint32_t (&qf)[HD / 16][4], const __nv_bfloat16* row_lo,
+                                       const __nv_bfloat16* row_hi, int lane) {
+  const int c = (lane & 3) * 2;
+#pragma unroll
+  for (int kk = 0; kk < HD / 16; ++kk) {
+    qf[kk][0] = row_lo ? *(const uint32_t*)(row_lo + kk * 16 + c) : 0u;
+    qf[kk][1] = row_hi ? *(const uint32_t*)(row_hi + kk * 16 + c) : 0u;
+    qf[kk][2] = row_lo ? *(const uint32_t*)(row_lo + kk * 16 + c + 8) : 0u;
+    qf[kk][3] = row_hi ? *(const uint32_t*)(row_hi + kk * 16 + c + 8) : 0u;
+  }
+}
+
+// ---- decode -------------------------------------------------------------------------------------
+// part_o: [T, nh, splits, HD] float32 (unnormalised), part_ml: [T, nh, splits, 2] (max, sum)
+template <int HD>
+__global__ void __launch_bounds__(THREADS)
+decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* __restrict__ out, int out_stride,
+              const __nv_bfloat16* __restrict__ k_pages, const __nv_bfloat16* __restrict__ v_pages,
+              const int* __restrict__ page_table, int table_width, const int* __restrict__ ctx_lens,
+              int nh, int nkv, float scale_log2, int window, int splits, float* __restrict__ part_o,
+              float* __restrict__ part_ml) {
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  __nv_bfloat16* ks = (__nv_bfloat16*)smem_raw;                       // [2][PAGE][STRIDE]
+  __nv_bfloat16* vs = ks + 2 * Cfg<HD>::PAGE_ELEMS;
+  const int split = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n_rep = nh / nkv;
+  const int L = ctx_lens[b];
+  const int pos = L - 1;
+  const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const int first_block = lo / PAGE, last_block = pos / PAGE;
+  const int n_blocks = last_block - first_block + 1;
+  const int per = (n_blocks + splits - 1) / splits;
+  const int blk0 = first_block + split * per;
+  const int blk1 = min(last_block + 1, blk0 + per);
+  const int* table = page_table + (size_t)b * table_width;
+  const size_t page_elems = (size_t)nkv * PAGE * HD;
+
+  const int r_lo = lane >> 2, r_hi = r_lo + 8;                        // rows = heads of the group
+  const __nv_bfloat16* qtok = q + (size_t)b * q_stride + (size_t)g * n_rep * HD;
+  uint32_t qf[HD / 16][4];
+  load_q<HD>(qf, r_lo < n_rep ? qtok + r_lo * HD : nullptr, r_hi < n_rep ? qtok + r_hi * HD : nullptr, lane);
+
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float o[HD / 8][4];
+#pragma unroll
+  for (int d = 0; d < HD / 8; ++d)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[d][i] = 0.f;
+
+  if (blk0 < blk1) {
+    const size_t src0 = (size_t)max(table[blk0], 0) * page_elems + (size_t)g * PAGE * HD;
+    load_page<HD>(ks, k_pages + src0, tid);
+    load_page<HD>(vs, v_pages + src0, tid);
+  }
+  cp_async_commit();
+  for (int blk = blk0; blk < blk1; ++blk) {
+    const int buf = (blk - blk0) & 1;
+    if (blk + 1 < blk1) {
+      const size_t src = (size_t)max(table[blk + 1], 0) * page_elems + (size_t)g * PAGE * HD;
+      load_page<HD>(ks + (buf ^ 1) * Cfg<HD>::PAGE_ELEMS, k_pages + src, tid);
+      load_page<HD>(vs + (buf ^ 1) * Cfg<HD>::PAGE_ELEMS, v_pages + src, tid);
+    }
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    const int key0 = warp * 16;                                       // this warp's quarter of the page
+    const int abs0 = blk * PAGE + key0;
+    if (abs0 <= pos && abs0 + 15 >= lo) {
+      float s[2][4];
+      scores<HD, 2>(qf, ks + buf * Cfg<HD>::PAGE_ELEMS, key0, s, lane);
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int kabs = abs0 + nt * 8 + (lane & 3) * 2 + (i & 1);
+          s[nt][i] = (kabs >= lo && kabs <= pos) ? s[nt][i] * scale_log2 : -INFINITY;
+        }
+      softmax_step<HD, 2>(s, m, l, o);
+      uint32_t pf[1][4];
+      to_fragments<2>(s, pf);
+      weighted_values<HD, 2>(pf, vs + buf * Cfg<HD>::PAGE_ELEMS, key0, o, lane);
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+
+  // ---- merge the four warps (each saw a quarter of every page) through shared memory ----
+  float* so = (float*)smem_raw;                         // [4][16][HD]
+  float* sm = so + 4 * 16 * HD;                         // [4][16]
+  float* sl = sm + 4 * 16;                              // [4][16]
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+    l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+  }
+#pragma unroll
+  for (int d = 0; d < HD / 8; ++d) {
+    const int c = d * 8 + (lane & 3) * 2;
+    so[(warp * 16 + r_lo) * HD + c] = o[d][0];
+    so[(warp * 16 + r_lo) * HD + c + 1] = o[d][1];
+    so[(warp * 16 + r_hi) * HD + c] = o[d][2];
+    so[(warp * 16 + r_hi) * HD + c + 1] = o[d][3];
+  }
+  if ((lane & 3) == 0) {
+    sm[warp * 16 + r_lo] = m[0];
+    sm[warp * 16 + r_hi] = m[1];
+    sl[warp * 16 + r_lo] = l[0];
+    sl[warp * 16 + r_hi] = l[1];
+  }
+  __syncthreads();
+  for (int e = tid; e < n_rep * HD; e += THREADS) {
+    const int row = e / HD, d = e - row * HD;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, sm[w * 16 + row]);
+    float acc = 0.f, Lsum = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = sm[w * 16 + row];
+      const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
+      acc += f * so[(w * 16 + row) * HD + d];
+      Lsum += f * sl[w * 16 + row];
+    }
+    const int head = g * n_rep + row;
+    if (splits == 1) {
+      out[(size_t)b * out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(Lsum > 0.f ? acc / Lsum : 0.f);
+    } else {
+      const size_t pi = ((size_t)b * nh + head) * splits + split;
+      part_o[pi * HD + d] = acc;
+      if (d == 0) {
+        part_ml[pi * 2] = M;
+        part_ml[pi * 2 + 1] = Lsum;
+      }
+    }
+  }
+}
+
+template <int HD>
+__global__ void combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                               __nv_bfloat16* __restrict__ out, int out_stride, int nh, int splits) {
+  const int b = blockIdx.x, head = blockIdx.y;
+  const size_t base = ((size_t)b * nh + head) * splits;
+  float M = -INFINITY;
+  for (int s = 0; s < splits; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
+  for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+    float acc = 0.f, Lsum = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const float ms = part_ml[(base + s) * 2];
+      const float f = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
+      acc += f * part_o[(base + s) * HD + d];
+      Lsum += f * part_ml[(base + s) * 2 + 1];
+    }
+    out[(size_t)b * out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(Lsum > 0.f ? acc / Lsum : 0.f);
+  }
+}
+
+// ---- prefill ------------------------------------------------------------------------------------
+template <int HD>
+__global__ void __launch_bounds__(THREADS)
+prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* __restrict__ out, int out_stride,
+               const __nv_bfloat16* __restrict__ k_pages, const __nv_bfloat16* __restrict__ v_pages,
+               const int* __restrict__ page_table, int table_width, const int* __restrict__ cu_seqlens,
+               const int* __restrict__ ctx_lens, int nh, int nkv, float scale_log2, int window) {
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  __nv_bfloat16* ks = (__nv_bfloat16*)smem_raw;
+  __nv_bfloat16* vs = ks + 2 * Cfg<HD>::PAGE_ELEMS;
+  const int tile = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n_rep = nh / nkv;
+  const int tok0 = cu_seqlens[b];
+  const int n_new = cu_seqlens[b + 1] - tok0;
+  const int n_rows = n_new * n_rep;
+  const int row0 = tile * 64;
+  if (row0 >= n_rows) return;                         // whole CTA: no barrier has been used yet
+  const int L = ctx_lens[b];
+  const int start = L - n_new;                        // position of the sequence's first new token
+  const int* table = page_table + (size_t)b * table_width;
+  const size_t page_elems = (size_t)nkv * PAGE * HD;
+
+  // rows of this thread: (token, head in group)
+  const int r_lo = row0 + warp * 16 + (lane >> 2), r_hi = r_lo + 8;
+  const bool v_lo = r_lo < n_rows, v_hi = r_hi < n_rows;
+  const int t_lo = v_lo ? r_lo / n_rep : 0, t_hi = v_hi ? r_hi / n_rep : 0;
+  const int h_lo = g * n_rep + (v_lo ? r_lo % n_rep : 0), h_hi = g * n_rep + (v_hi ? r_hi % n_rep : 0);
+  const int p_lo = start + t_lo, p_hi = start + t_hi;                // positions of the two rows
+  uint32_t qf[HD / 16][4];
+  load_q<HD>(qf, v_lo ? q + (size_t)(tok0 + t_lo) * q_stride + (size_t)h_lo * HD : nullptr,
+             v_hi ? q + (size_t)(tok0 + t_hi) * q_stride + (size_t)h_hi * HD : nullptr, lane);
+
+  // key range of the tile: from the first key its first row sees to the position of its last row
+  const int last_row = min(row0 + 63, n_rows - 1);
+  const int tile_pos_hi = start + last_row / n_rep;
+  const int tile_pos_lo = start + row0 / n_rep;
+  const int tile_lo = (window > 0 && tile_pos_lo - window + 1 > 0) ? tile_pos_lo - window + 1 : 0;
+  const int blk0 = tile_lo / PAGE, blk1 = tile_pos_hi / PAGE + 1;
+  const int lo_lo = (window > 0 && p_lo - window + 1 > 0) ? p_lo - window + 1 : 0;
+  const int lo_hi = (window > 0 && p_hi - window + 1 > 0) ? p_hi - window + 1 : 0;
+  // this warp's rows see keys in [warp_lo, warp_hi]
+  const int wr0 = min(row0 + warp * 16, n_rows - 1), wr1 = min(row0 + warp * 16 + 15, n_rows - 1);
+  const int warp_hi = start + wr1 / n_rep;
+  const int warp_pos0 = start + wr0 / n_rep;
+  const int warp_lo = (window > 0 && warp_pos0 - window + 1 > 0) ? warp_pos0 - window + 1 : 0;
+  const bool warp_active = row0 + warp * 16 < n_rows;
+
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float o[HD / 8][4];
+#pragma unroll
+  for (int d = 0; d < HD / 8; ++d)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[d][i] = 0.f;
+
+  {
+    const size_t src0 = (size_t)max(table[blk0], 0) * page_elems + (size_t)g * PAGE * HD;
+    load_page<HD>(ks, k_pages + src0, tid);
+    load_page<HD>(vs, v_pages + src0, tid);
+  }
+  cp_async_commit();
+  for (int blk = blk0; blk < blk1; ++blk) {
+    const int buf = (blk - blk0) & 1;
+    if (blk + 1 < blk1) {
+      const size_t src = (size_t)max(table[blk + 1], 0) * page_elems + (size_t)g * PAGE * HD;
+      load_page<HD>(ks + (buf ^ 1) * Cfg<HD>::PAGE_ELEMS, k_pages + src, tid);
+      load_page<HD>(vs + (buf ^ 1) * Cfg<HD>::PAGE_ELEMS, v_pages + src, tid);
+    }
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    const int abs0 = blk * PAGE;
+    if (warp_active && abs0 <= warp_hi && abs0 + PAGE - 1 >= warp_lo) {
+      float s[8][4];
+      scores<HD, 8>(qf, ks + buf * Cfg<HD>::PAGE_ELEMS, 0, s, lane);
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int kabs = abs0 + nt * 8 + (lane & 3) * 2 + (i & 1);
+          const bool vis = (i < 2) ? (v_lo && kabs >= lo_lo && kabs <= p_lo) : (v_hi && kabs >= lo_hi && kabs <= p_hi);
+          s[nt][i] = vis ? s[nt][i] * scale_log2 : -INFINITY;
+        }
+      softmax_step<HD, 8>(s, m, l, o);
+      uint32_t pf[4][4];
+      to_fragments<8>(s, pf);
+      weighted_values<HD, 8>(pf, vs + buf * Cfg<HD>::PAGE_ELEMS, 0, o, lane);
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+    l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+  }
+  const float inv_lo = l[0] > 0.f ? 1.f / l[0] : 0.f, inv_hi = l[1] > 0.f ? 1.f / l[1] : 0.f;
+  __nv_bfloat16* o_lo = out + (size_t)(tok0 + t_lo) * out_stride + (size_t)h_lo * HD;
+  __nv_bfloat16* o_hi = out + (size_t)(tok0 + t_hi) * out_stride + (size_t)h_hi * HD;
+#pragma unroll
+  for (int d = 0; d < HD / 8; ++d) {
+    const int c = d * 8 + (lane & 3) * 2;
+    if (v_lo) *(uint32_t*)(o_lo + c) = pack_bf16(o[d][0] * inv_lo, o[d][1] * inv_lo);
+    if (v_hi) *(uint32_t*)(o_hi + c) = pack_bf16(o[d][2] * inv_hi, o[d][3] * inv_hi);
+  }
+}
+
+template <int HD>
+static int launch_decode(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+                         const void* v_pages, const int* page_table, int table_width, const int* ctx_lens, int B,
+                         int nh, int nkv, float scale, int window, int splits, float* part_o, float* part_ml,
+                         cudaStream_t stream) {
+  const int merge_bytes = (4 * 16 * HD + 2 * 4 * 16) * (int)sizeof(float);
+  const int smem = Cfg<HD>::SMEM_BYTES > merge_bytes ? Cfg<HD>::SMEM_BYTES : merge_bytes;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid(splits, nkv, B);
+  decode_kernel<HD><<<grid, THREADS, smem, stream>>>(
+      (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pages,
+      (const __nv_bfloat16*)v_pages, page_table, table_width, ctx_lens, nh, nkv, scale * LOG2E, window, splits,
+      part_o, part_ml);
+  int rc = launch_status();
+  if (rc || splits == 1) return rc;
+  combine_kernel<HD><<<dim3(B, nh), HD < 32 ? 32 : HD, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, out_stride,
+                                                                   nh, splits);
+  return launch_status();
+}
+
+template <int HD>
+static int launch_prefill(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+                          const void* v_pages, const int* page_table, int table_width, const int* cu_seqlens,
+                          const int* ctx_lens, int B, int max_new, int nh, int nkv, float scale, int window,
+                          cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg<HD>::SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int n_rep = nh / nkv;
+  dim3 grid((max_new * n_rep + 63) / 64, nkv, B);
+  prefill_kernel<HD><<<grid, THREADS, Cfg<HD>::SMEM_BYTES, stream>>>(
+      (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pages,
+      (const __nv_bfloat16*)v_pages, page_table, table_width, cu_seqlens, ctx_lens, nh, nkv, scale * LOG2E, window);
+  return launch_status();
+}
+
+}  // namespace fa
+}  // namespace wpc
+
+using namespace wpc;
+
+#define WPC_DISPATCH_HD(hd, ...)                              \
+  switch (hd) {                                               \
+    case 16: { constexpr int HD = 16; return __VA_ARGS__; }   \
+    case 32: { constexpr int HD = 32; return __VA_ARGS__; }   \
+    case 48: { constexpr int HD = 48; return __VA_ARGS__; }   \
+    case 64: { constexpr int HD = 64; return __VA_ARGS__; }   \
+    case 80: { constexpr int HD = 80; return __VA_ARGS__; }   \
+    case 96: { constexpr int HD = 96; return __VA_ARGS__; }   \
+    case 112: { constexpr int HD = 112; return __VA_ARGS__; } \
+    case 128: { constexpr int HD = 128; return __VA_ARGS__; } \
+    default: return WPC_ERR_UNSUPPORTED;                      \
+  }
+
+extern "C" {
+
+// 1 if these sizes can take the tensor-core kernels, else 0 (the plain kernel takes them).
+int wpc_attention_mma_supports(int nh, int nkv, int hd) {
+  return hd >= 16 && hd <= 128 && hd % 16 == 0 && nkv >= 1 && nh % nkv == 0 && nh / nkv <= 16;
+}
+
+// One query token per sequence: q row b belongs to sequence b.  part_o: float32
+// [B * nh * splits * hd], part_ml: float32 [B * nh * splits * 2]; unused when splits == 1.
+int wpc_attention_decode(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+                         const void* v_pages, const int* page_table, int table_width, const int* ctx_lens, int B,
+                         int nh, int nkv, int hd, float scale, int window, int splits, float* part_o,
+                         float* part_ml, cudaStream_t stream) {
+  if (B <= 0) return 0;
+  if (!wpc_attention_mma_supports(nh, nkv, hd) || splits < 1 || (q_stride % 2) || (out_stride % 2))
+    return WPC_ERR_UNSUPPORTED;
+  if (splits > 1 && (!part_o || !part_ml)) return WPC_ERR_BAD_ARGUMENT;
+  WPC_DISPATCH_HD(hd, fa::launch_decode<HD>(q, q_stride, out, out_stride, k_pages, v_pages, page_table, table_width,
+                                           ctx_lens, B, nh, nkv, scale, window, splits, part_o, part_ml, stream));
+}
+
+int wpc_attention_prefill(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+                          const void* v_pages, const int* page_table, int table_width, const int* cu_seqlens,
+                          const int* ctx_lens, int B, int max_new, int nh, int nkv, int hd, float scale, int window,
+                          cudaStream_t stream) {
+  if (B <= 0 || max_new <= 0) return 0;
+  if (!wpc_attention_mma_supports(nh, nkv, hd) || (q_stride % 2) || (out_stride % 2)) return WPC_ERR_UNSUPPORTED;
+  WPC_DISPATCH_HD(hd, fa::launch_prefill<HD>(q, q_stride, out, out_stride, k_pages, v_pages, page_table, table_width,
+                                            cu_seqlens, ctx_lens, B, max_new, nh, nkv, scale, window, stream));
+}
+
+}  // extern "C"

@@ -296,11 +296,50 @@ def qk_rope_kv_store(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim:
 def attention(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, k_pages: torch.Tensor,
               v_pages: torch.Tensor, page_table: torch.Tensor, cu_seqlens: torch.Tensor, ctx_lens: torch.Tensor,
               seq_of_token: torch.Tensor, positions: torch.Tensor, scale: float, window: Optional[int],
-              max_new_tokens: int, max_ctx_len: int) -> torch.Tensor:
+              max_new_tokens: int, max_ctx_len: int, splits: Optional[int] = None) -> torch.Tensor:
     """softmax(q . k * scale) . v over the cached positions that each query sees: 0..its own,
-    or the last `window` of them.  q: the first n_heads*head_dim columns of each row."""
-    return attention_plain(q, n_heads, n_kv_heads, head_dim, k_pages, v_pages, page_table, seq_of_token,
-                           positions, scale, window)
+    or the last `window` of them.  q: the first n_heads*head_dim columns of each row.
+
+    bfloat16 with a head size that is a multiple of 16 up to 128 runs on the tensor cores
+    (csrc/attention_mma.cu): the split-KV kernel when every sequence brings one token, the
+    tiled kernel otherwise.  Everything else runs the plain kernel."""
+    if q.dtype != torch.bfloat16 or not library().wpc_attention_mma_supports(n_heads, n_kv_heads, head_dim):
+        return attention_plain(q, n_heads, n_kv_heads, head_dim, k_pages, v_pages, page_table, seq_of_token,
+                               positions, scale, window)
+    _rows(q, "q")
+    _need(q.shape[1] >= n_heads * head_dim, "q is too narrow")
+    _need(k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.dtype == q.dtype, "pages: wrong type")
+    T, B = q.shape[0], ctx_lens.numel()
+    out = torch.empty((T, n_heads * head_dim), dtype=q.dtype, device=q.device)
+    if max_new_tokens == 1:
+        _need(T == B, "one token per sequence expected")
+        if splits is None:
+            splits = plan_decode_splits(B, n_kv_heads, max_ctx_len, window)
+        part_o = part_ml = None
+        if splits > 1:
+            part_o = torch.empty((B * n_heads * splits * head_dim,), dtype=torch.float32, device=q.device)
+            part_ml = torch.empty((B * n_heads * splits * 2,), dtype=torch.float32, device=q.device)
+        _check("attention_decode", library().wpc_attention_decode(
+            _p(q), q.stride(0), _p(out), out.stride(0), _p(k_pages), _p(v_pages), _p(page_table),
+            page_table.shape[1], _p(ctx_lens), B, n_heads, n_kv_heads, head_dim, ctypes.c_float(scale),
+            int(window or 0), splits, _p(part_o), _p(part_ml), _stream()))
+    else:
+        _check("attention_prefill", library().wpc_attention_prefill(
+            _p(q), q.stride(0), _p(out), out.stride(0), _p(k_pages), _p(v_pages), _p(page_table),
+            page_table.shape[1], _p(cu_seqlens), _p(ctx_lens), B, max_new_tokens, n_heads, n_kv_heads, head_dim,
+            ctypes.c_float(scale), int(window or 0), _stream()))
+    return out
+
+
+def plan_decode_splits(n_seqs: int, n_kv_heads: int, max_ctx_len: int, window: Optional[int]) -> int:
+    """How many CTAs share one sequence's pages in decode attention: enough that about two
+    waves of CTAs are in flight, and at least two pages each."""
+    blocks = (max_ctx_len + PAGE - 1) // PAGE
+    if window:
+        blocks = min(blocks, (window + PAGE - 1) // PAGE + 1)
+    ctas = max(n_seqs * n_kv_heads, 1)
+    want = (2 * _SMS + ctas - 1) // ctas
+    return max(1, min(want, blocks // 2, 64))
 
 
 def attention_plain(q, n_heads, n_kv_heads, head_dim, k_pages, v_pages, page_table, seq_of_token, positions,
