@@ -91,3 +91,52 @@ def test_greedy_generation_matches_plain(engines):
     for p, g in zip(prompts, got):
         assert g == P.generate_greedy(cfg, tensors, p, 8)
     eng.cache.check()
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_first_tokens_of_a_sequence(engines, name, dtype):
+    """Position 0, the first decoded token after a one-token prompt, and a prompt's end."""
+    eng, folder = engines(name, dtype)
+    r = requests_for(eng, [6], seed=700)[0]
+    slot = eng.open_sequence()
+    try:
+        from wpc_engine_b200 import SequenceStep
+        rows = [eng.step([SequenceStep(slot, [t], want=[0])]).float().cpu().numpy() for t in r]
+    finally:
+        eng.close_sequence(slot)
+    assert_close_to_plain(np.concatenate(rows), folder, r, dtype, "one token at a time from the start")
+
+
+def test_temperature_generation_follows_the_plain_sampler(engines):
+    """Tiny-B, temperature 0.8, seed 7: every drawn token is what the plain sampler draws from
+    the engine's own logits with the same uniform number; batching changes no draw."""
+    eng, folder = engines("B", "float32")
+    prompts = [random_tokens(384, n, 50 + n) for n in (1, 7, 23, 40)]
+    opts = GenerationOptions(max_tokens=12, temperature=0.8, seed=7)
+    got = generate(eng, prompts, opts)
+    assert [len(g) for g in got] == [12] * 4
+    for r, (p, g) in enumerate(zip(prompts, got)):
+        logits = run_whole(eng, p + g[:-1])[len(p) - 1:]
+        for step, tok in enumerate(g):
+            u = P.uniform_for(7, r, step)
+            idx, cdf, target = P.sample_temperature(logits[step], 0.8, u)
+            lo = cdf[tok - 1] if tok > 0 else 0.0
+            slack = 1e-4 * cdf[-1]
+            assert lo - slack <= target <= cdf[tok] + slack, (r, step, tok, idx)
+    alone = generate(eng, [prompts[2]], opts)
+    # request numbers are positions in the call, so the same prompt alone is request 0: other draws
+    again = generate(eng, prompts, opts)
+    assert again == got and len(alone[0]) == 12
+
+
+def test_stop_tokens_end_one_sequence_while_others_go_on(engines):
+    eng, folder = engines("A", "float32")
+    prompts = [random_tokens(256, n, 40 + n) for n in (5, 11, 17)]
+    free = generate(eng, prompts, GenerationOptions(max_tokens=8))
+    stop = free[1][2]
+    got = generate(eng, prompts, GenerationOptions(max_tokens=8, stop_token_ids=[stop]))
+    for f, g in zip(free, got):
+        cut = f.index(stop) + 1 if stop in f else len(f)
+        assert g == f[:cut]
+    eng.cache.check()
+    assert eng.cache.slots.n_held == 0

@@ -1,0 +1,241 @@
+"""Each part of a layer alone on the GPU against the plain implementation's function for it,
+at sizes of its own, and a toy architecture with a mixer that keeps a state of fixed size per
+sequence: registered, built, loaded and stepped from the test, without a change to the
+library's files."""
+import dataclasses
+import json
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from plain import qwen2_plain as P
+import wpc_engine_b200 as wpc
+from wpc_engine_b200.cache import SequenceCache
+from wpc_engine_b200.engine.batch import SequenceStep, context_from, plan_step
+from wpc_engine_b200.models.decoder import DecoderModel, Run
+from wpc_engine_b200.parts import (Embedding, GQAAttention, Linear, Mixer, OutputHead, ParamSpec, PreNormBlock,
+                                   RMSNorm, RotaryEncoding, StateSpec, SwiGLU)
+from wpc_engine_b200.weights.loader import bind_model, finalize_parts
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def rnd(shape, seed, scale=1.0):
+    return (torch.randn(shape, generator=torch.Generator().manual_seed(seed)) * scale)
+
+
+def make_ctx(dtype, lens_new, starts, cache=None, slots=None):
+    """A step context for sequences that bring lens_new[b] tokens after starts[b] cached ones."""
+    entries = [SequenceStep(slots[b] if slots else b, [1] * n, want=[n - 1]) for b, n in enumerate(lens_new)]
+    rows, width = [], 1
+    if cache is not None:
+        width = cache.table_width([e.slot for e in entries])
+        rows = [cache.page_table_rows(g, [e.slot for e in entries], width) for g in cache.kv_groups()]
+    plan = plan_step(entries, starts, rows, width)
+    meta = torch.from_numpy(plan.host).to(DEV)
+    return context_from(meta, plan.layout, dtype, plan.max_new_tokens, plan.max_ctx_len, plan.is_decode, list(lens_new))
+
+
+def bind(part, tensors, dtype):
+    from wpc_engine_b200.parts.base import collect_params
+    from wpc_engine_b200.weights.loader import device_dtype
+    wanted = collect_params(part)
+    per = {}
+    for name, (owner, local, spec) in wanted.items():
+        t = tensors[name]
+        per.setdefault(id(owner), (owner, {}))[1][local] = t.to(DEV, device_dtype(t.dtype, spec.kind, dtype)).contiguous()
+    for owner, d in per.values():
+        owner.bind(d)
+    finalize_parts(part)
+
+
+def tol(dtype):
+    return 3e-5 if dtype == torch.float32 else 2e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norm_part(dtype):
+    part = RMSNorm(88, 3e-5)
+    g = 1 + rnd((88,), 1, 0.1)
+    bind(part, {"weight": g}, dtype)
+    x = rnd((7, 88), 2, 2.0)
+    got = part.forward(make_ctx(dtype, [7], [0]), x.to(DEV))
+    want = P.rms_norm(x.numpy().astype(np.float64), g.numpy().astype(np.float64), 3e-5)
+    assert np.abs(got.float().cpu().numpy() - want).max() <= tol(dtype) * np.abs(want).max()
+
+
+def test_rotary_part_shares_tables_and_handles_partial_rotation():
+    rot = RotaryEncoding(32, 1e4, rotary_pairs=10)
+    ctx = make_ctx(torch.float32, [3, 2], [5, 0])
+    cos, sin = rot.tables(ctx)
+    assert rot.tables(ctx)[0] is cos and cos.shape == (5, 10)          # computed once per step
+    x = rnd((5, 2 * 32), 3).to(DEV)
+    y = wpc.ops.rope_inplace(x.clone(), 2, 32, cos, sin)
+    pos = [5, 6, 7, 0, 1]
+    xv = x.cpu().numpy().astype(np.float64).reshape(5, 2, 32)
+    i = np.arange(10)
+    ang = np.asarray(pos)[:, None] * np.power(1e4, -2.0 * i / 32)[None, :]
+    want = xv.copy()
+    want[..., :10] = xv[..., :10] * np.cos(ang)[:, None] - xv[..., 16:26] * np.sin(ang)[:, None]
+    want[..., 16:26] = xv[..., 16:26] * np.cos(ang)[:, None] + xv[..., :10] * np.sin(ang)[:, None]
+    assert np.abs(y.cpu().numpy().reshape(5, 2, 32) - want).max() < 1e-5
+    assert torch.equal(y[3], x[3])                                      # position 0 is the identity
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_feed_forward_part(dtype):
+    part = SwiGLU(72, 200)
+    ts = {"gate_proj.weight": rnd((200, 72), 4, 0.1), "up_proj.weight": rnd((200, 72), 5, 0.1),
+          "down_proj.weight": rnd((72, 200), 6, 0.1)}
+    ts = {k: v.to(dtype) for k, v in ts.items()}
+    bind(part, ts, dtype)
+    h = rnd((9, 72), 7).to(dtype)
+    residual = rnd((9, 72), 8).to(DEV)
+    r0 = residual.clone()
+    assert part.forward(make_ctx(dtype, [9], [0]), h.to(DEV), residual) is None
+    f = lambda t: t.float().numpy().astype(np.float64)
+    want = f(r0.cpu()) + P.swiglu(f(h), f(ts["gate_proj.weight"]), f(ts["up_proj.weight"]), f(ts["down_proj.weight"]))
+    assert np.abs(residual.cpu().numpy() - want).max() <= tol(dtype) * np.abs(want).max()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window", [None, 20])
+def test_attention_part_over_two_steps(dtype, window):
+    """The mixer alone with a cache of its own: a prompt step, then a second step that brings
+    more tokens; both against the plain attention over the whole sequence."""
+    W, nh, nkv, hd = 56, 6, 2, 16
+    rot = RotaryEncoding(hd, 1e4)
+    part = GQAAttention(W, nh, nkv, hd, position=rot, qkv_bias=True, window=window)
+    ts = {f"{n}_proj.weight": rnd((o, W), 10 + i, 0.2) for i, (n, o) in enumerate([("q", nh * hd), ("k", nkv * hd), ("v", nkv * hd)])}
+    ts.update({f"{n}_proj.bias": rnd((o,), 20 + i, 0.2) for i, (n, o) in enumerate([("q", nh * hd), ("k", nkv * hd), ("v", nkv * hd)])})
+    ts["o_proj.weight"] = rnd((W, nh * hd), 30, 0.2)
+    ts = {k: v.to(dtype) for k, v in ts.items()}
+    bind(part, ts, dtype)
+    cache = SequenceCache([part.cache_spec()], 512, dtype, DEV)
+    slot = cache.open()
+    T1, T2 = 70, 9
+    h = rnd((T1 + T2, W), 40).to(dtype)
+    outs = []
+    for lo, n in ((0, T1), (T1, T2)):
+        cache.reserve(slot, n)
+        ctx = make_ctx(dtype, [n], [lo], cache, [slot])
+        model_stub = DecoderModel(None, Embedding(2, W), [PreNormBlock(RMSNorm(W, 1e-6), part, RMSNorm(W, 1e-6), SwiGLU(W, 8))],
+                                  RMSNorm(W, 1e-6), OutputHead(2, W))
+        view = model_stub.cache_views(cache, ctx)[0]
+        residual = torch.zeros((n, W), dtype=torch.float32, device=DEV)
+        part.forward(ctx, h[lo:lo + n].to(DEV), view, residual)
+        outs.append(residual.cpu().numpy())
+        cache.commit(slot, n)
+    f = lambda t: t.float().numpy().astype(np.float64)
+    hh = f(h)
+    q = P.rope(P.linear(hh, f(ts["q_proj.weight"]), f(ts["q_proj.bias"])).reshape(-1, nh, hd), np.arange(T1 + T2), 1e4)
+    k = P.rope(P.linear(hh, f(ts["k_proj.weight"]), f(ts["k_proj.bias"])).reshape(-1, nkv, hd), np.arange(T1 + T2), 1e4)
+    v = P.linear(hh, f(ts["v_proj.weight"]), f(ts["v_proj.bias"])).reshape(-1, nkv, hd)
+    want = P.linear(P.attention(q, k, v, window).reshape(-1, nh * hd), f(ts["o_proj.weight"]))
+    got = np.concatenate(outs)
+    assert np.abs(got - want).max() <= tol(dtype) * np.abs(want).max()
+
+
+def test_embedding_and_heads():
+    emb = Embedding(50, 24)
+    table = rnd((50, 24), 50)
+    bind(emb, {"weight": table}, torch.float32)
+    ctx = make_ctx(torch.float32, [3], [0])
+    ctx.tokens.copy_(torch.tensor([4, 49, 0], dtype=torch.int32))
+    assert torch.equal(emb.forward(ctx).cpu(), table[[4, 49, 0]])
+    tied = OutputHead(50, 24, tied_to=emb)
+    assert tied.param_specs() == {}
+    h = rnd((3, 24), 51).to(DEV)
+    assert torch.allclose(tied.forward(ctx, h).cpu(), h.cpu() @ table.t(), atol=1e-5)
+    own = OutputHead(50, 24)
+    w = rnd((50, 24), 52)
+    bind(own, {"weight": w}, torch.float32)
+    assert torch.allclose(own.forward(ctx, h).cpu(), h.cpu() @ w.t(), atol=1e-5)
+
+
+# ---- a toy architecture defined here: a mixer with a running state per sequence --------------------
+class RunningMeanMixer(Mixer):
+    """state <- decay * state + (1 - decay) * h_t for each token in order; out_t = W state.
+    Keeps one [width] record per sequence; written with torch calls, since it is only a toy,
+    and not capturable into a graph because it reads the slots on the host."""
+    graph_safe = False
+
+    def __init__(self, width, decay):
+        self.width, self.decay = width, decay
+        self.proj = Linear(width, width)
+
+    def subparts(self):
+        return {"proj": self.proj}
+
+    def cache_spec(self):
+        return StateSpec((self.width,), "float32")
+
+    def forward(self, ctx, h, cache, residual):
+        outs = []
+        t = 0
+        slots = cache.slots.long()
+        for b, n in enumerate(ctx.new_tokens_host):
+            s = cache.state[slots[b]].clone()
+            for i in range(n):
+                s = self.decay * s + (1 - self.decay) * h[t + i].float()
+                outs.append(s)
+            cache.state[slots[b]] = s
+            t += n
+        return self.proj.forward(torch.stack(outs).to(h.dtype))          # the block adds it to the residual
+
+
+@dataclasses.dataclass(frozen=True)
+class ToyConfig:
+    vocab_size: int
+    width: int
+    n_layers: int
+    decay: float
+    eps: float
+
+    @classmethod
+    def from_dict(cls, raw):
+        return cls(**{f.name: raw[f.name] for f in dataclasses.fields(cls)})
+
+    def to_dict(self):
+        return dict(dataclasses.asdict(self), architectures=["ToyRunningMeanLM"])
+
+
+def build_toy(c: ToyConfig):
+    blocks = [PreNormBlock(RMSNorm(c.width, c.eps), RunningMeanMixer(c.width, c.decay), RMSNorm(c.width, c.eps),
+                           SwiGLU(c.width, 2 * c.width), names=("norm1", "mixer", "norm2", "ffn")) for _ in range(c.n_layers)]
+    emb = Embedding(c.vocab_size, c.width)
+    # the schedule runs layer 0 twice: a layer may be named twice and then keeps two states
+    schedule = [Run(0)] + [Run(i) for i in range(c.n_layers)]
+    return DecoderModel(c, emb, blocks, RMSNorm(c.width, c.eps), OutputHead(c.vocab_size, c.width, tied_to=emb),
+                        schedule=schedule, names={"embedding": "tok", "blocks": "layer.{}", "final_norm": "out_norm"})
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path, dtype):
+    wpc.register_architecture("ToyRunningMeanLM", ToyConfig, build_toy)
+    try:
+        cfg = ToyConfig(vocab_size=90, width=40, n_layers=2, decay=0.8, eps=1e-5)
+        folder = wpc.write_random_model(str(tmp_path / "toy"), cfg, 3, getattr(torch, dtype))
+        with open(os.path.join(folder, "config.json")) as f:
+            assert json.load(f)["architectures"] == ["ToyRunningMeanLM"]
+        eng = wpc.Engine.from_folder(folder, dtype=dtype, max_tokens=1024, max_sequences=4)
+        assert len(eng.cache.groups) == 1 and eng.cache.groups[0].state.shape == (3, 4, 40)   # three scheduled runs
+        toks = np.random.default_rng(0).integers(0, 90, size=30).tolist()
+        from helpers import run_batch, run_tail_one_by_one, run_whole
+        whole = run_whole(eng, toks)
+        tail = run_tail_one_by_one(eng, toks, tail=12)       # the state carries over steps; slots are reused
+        batch = run_batch(eng, [toks, toks[:11]], [20, 3])
+        t = 1e-5 if dtype == "float32" else 4e-2
+        scale = np.abs(whole).max()
+        assert np.abs(tail - whole).max() <= t * scale
+        assert np.abs(batch[0] - whole).max() <= t * scale and np.abs(batch[1] - whole[:11]).max() <= t * scale
+        assert np.abs(whole[5] - whole[6]).max() > 1e-3
+        out = wpc.generate(eng, [toks[:4], toks[:9]], wpc.GenerationOptions(max_tokens=5))
+        assert [len(o) for o in out] == [5, 5]
+        eng.cache.check()
+    finally:
+        wpc.unregister_architecture("ToyRunningMeanLM")

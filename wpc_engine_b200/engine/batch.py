@@ -121,11 +121,12 @@ class StepContext:
     max_new_tokens: int
     max_ctx_len: int
     is_decode: bool
+    new_tokens_host: Optional[List[int]] = None   # tokens that each sequence brings, on the host (all 1 in a graph)
     shared: Dict[object, object] = field(default_factory=dict)   # per-step tables of the parts
 
 
 def context_from(meta: torch.Tensor, lay: StepLayout, act_dtype: torch.dtype, max_new_tokens: int,
-                 max_ctx_len: int, is_decode: bool) -> StepContext:
+                 max_ctx_len: int, is_decode: bool, new_tokens_host: Optional[List[int]] = None) -> StepContext:
     def view(off, n):
         return meta[off: off + n]
     tables = []
@@ -138,4 +139,5 @@ def context_from(meta: torch.Tensor, lay: StepLayout, act_dtype: torch.dtype, ma
         seq_of_token=view(lay.seq_of_token, lay.n_tokens),
         cu_seqlens=view(lay.cu_seqlens, lay.n_seqs + 1), ctx_lens=view(lay.ctx_lens, lay.n_seqs),
         slots=view(lay.slots, lay.n_seqs), want_rows=view(lay.want_rows, lay.n_want),
-        page_tables=tables, max_new_tokens=max_new_tokens, max_ctx_len=max_ctx_len, is_decode=is_decode)
+        page_tables=tables, max_new_tokens=max_new_tokens, max_ctx_len=max_ctx_len, is_decode=is_decode,
+        new_tokens_host=new_tokens_host if new_tokens_host is not None else ([1] * lay.n_seqs if is_decode else None))

@@ -82,7 +82,7 @@ class Engine:
         self.device = torch.device(device)
         self.cache = SequenceCache(model.cache_specs(), max_tokens, self.dtype, self.device, max_sequences)
         self._ring = _MetaRing(self.device)
-        self.use_graphs = bool(use_graphs) and self.device.type == "cuda"
+        self.use_graphs = bool(use_graphs) and self.device.type == "cuda" and model.graph_safe()
         self._graphs: Dict[tuple, object] = {}
         self.vocab_size = model.embedding.vocab_size
         self.max_positions = getattr(model.config, "max_position_embeddings", None)
@@ -160,7 +160,8 @@ class Engine:
         if not ran:
             meta = host[: lay.total].to(self.device, non_blocking=True)
             self._ring.sent()
-            ctx = context_from(meta, lay, self.dtype, plan.max_new_tokens, plan.max_ctx_len, plan.is_decode)
+            ctx = context_from(meta, lay, self.dtype, plan.max_new_tokens, plan.max_ctx_len, plan.is_decode,
+                               [len(e.tokens) for e in entries])
             logits = self.model.forward(ctx, self.cache)
         for e in entries:
             self.cache.commit(e.slot, len(e.tokens))

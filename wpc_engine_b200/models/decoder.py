@@ -12,7 +12,7 @@ import torch
 
 from .. import ops
 from ..cache import KVGroup, KVView, SequenceCache, StateGroup, StateView
-from ..parts.base import Block, Norm, Part, collect_params
+from ..parts.base import Block, Norm, Part, all_graph_safe, collect_params
 from ..parts.embedding import Embedding, OutputHead
 
 
@@ -66,6 +66,9 @@ class DecoderModel:
         for prefix, part in self.roots():
             wanted.update(collect_params(part, prefix + "."))
         return wanted
+
+    def graph_safe(self) -> bool:
+        return all(all_graph_safe(part) for _, part in self.roots())
 
     # -- cache -------------------------------------------------------------------------------
     def cache_specs(self) -> List[object]:

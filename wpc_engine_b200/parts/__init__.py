@@ -1,7 +1,7 @@
 """Parts that layers are put together from; see base.py for the interfaces."""
 from .attention import GQAAttention
 from .base import (Block, FeedForward, KVSpec, Mixer, Norm, ParamSpec, Part, PositionEncoding,
-                   StateSpec, collect_params)
+                   StateSpec, all_graph_safe, collect_params)
 from .block import PreNormBlock
 from .embedding import Embedding, OutputHead
 from .linear import Linear, fuse_rows
@@ -11,4 +11,4 @@ from .rope import RotaryEncoding
 
 __all__ = ["Block", "Embedding", "FeedForward", "GQAAttention", "KVSpec", "Linear", "Mixer", "Norm",
            "OutputHead", "ParamSpec", "Part", "PositionEncoding", "PreNormBlock", "RMSNorm",
-           "RotaryEncoding", "StateSpec", "SwiGLU", "collect_params", "fuse_rows"]
+           "RotaryEncoding", "StateSpec", "SwiGLU", "all_graph_safe", "collect_params", "fuse_rows"]

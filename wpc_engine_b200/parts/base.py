@@ -62,6 +62,11 @@ class StateSpec:
 
 
 class Part:
+    # False for a part whose forward pass cannot be captured into a CUDA graph (it synchronises
+    # with the host, or its launches depend on values that change from step to step); the
+    # engine then runs the model's single-token steps directly.
+    graph_safe = True
+
     def param_specs(self) -> Dict[str, ParamSpec]:
         return {}
 
@@ -103,6 +108,10 @@ class Block(Part):
 
     def forward(self, ctx, x: torch.Tensor, cache) -> None:
         raise NotImplementedError
+
+
+def all_graph_safe(part: Part) -> bool:
+    return bool(part.graph_safe) and all(all_graph_safe(sub) for sub in part.subparts().values())
 
 
 def collect_params(part: Part, prefix: str = "") -> Dict[str, Tuple[Part, str, ParamSpec]]:
