@@ -285,3 +285,25 @@ def test_attention_prefill_window_edges():
     got = ops.attention(qkv, nh, nkv, hd, kp, vp, table, cu, ctx, seq, pos, 0.2, W, 150, 200)
     want = ref.attention_plain(qkv.cpu(), nh, nkv, hd, kp.cpu(), vp.cpu(), table.cpu(), seq.cpu(), pos.cpu(), 0.2, W)
     close(got.cpu(), want, torch.bfloat16)
+
+
+@pytest.mark.parametrize("T,inner,K", [(8, 256, 96), (200, 256, 96), (300, 384, 520), (2048, 1024, 256)])
+def test_gated_linear_fused_epilogue(T, inner, K):
+    """silu(gate) * up applied by the product's epilogue (more than 128 tokens) against the
+    product followed by the activation kernel, and against torch."""
+    x = rnd((T, K), torch.bfloat16, 51)
+    w = rnd((2 * inner, K), torch.bfloat16, 52, 0.1)
+    got = ops.gated_linear(x, w, inner, 128)
+    two = ops.silu_mul(ops.linear_plain(x, w, out_dtype=torch.float32).to(torch.bfloat16), inner, 128)
+    want = ref.gated_linear(x.cpu(), w.cpu(), inner, 128)
+    mag = want.float().abs().max().item()
+    assert (got.cpu().float() - want.float()).abs().max().item() <= 1.5e-2 * mag
+    assert (two.cpu().float() - want.float()).abs().max().item() <= 2e-2 * mag
+    assert ops.device_status() == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("inner,group", [(77, 77), (256, 128), (48, 8), (40, 4)])
+def test_silu_mul_groups(dtype, inner, group):
+    gu = rnd((5, 2 * inner), dtype, 53, 2.0)
+    close(ops.silu_mul(gu, inner, group), ref.silu_mul(gu.cpu(), inner, group).to(DEV), dtype)

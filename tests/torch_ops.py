@@ -10,7 +10,7 @@ import math
 import torch
 
 PAGE = 64
-__all__ = ["require_device", "embed", "rmsnorm", "linear", "silu_mul", "add_", "gather_rows", "convert",
+__all__ = ["require_device", "embed", "rmsnorm", "linear", "silu_mul", "gated_linear", "add_", "gather_rows", "convert",
            "rope_angles", "rope_inplace", "qk_rope_kv_store", "attention", "sample", "fill_normal"]
 
 _M64 = (1 << 64) - 1
@@ -39,9 +39,18 @@ def linear(x, w, bias=None, out_dtype=None, residual=None):
     return y.to(out_dtype or x.dtype)
 
 
-def silu_mul(gu, inner):
-    g, u = gu[:, :inner].float(), gu[:, inner:].float()
+GATED_GROUP = 128
+
+
+def silu_mul(gu, inner, group=None):
+    group = inner if group is None else group
+    v = gu.float().reshape(gu.shape[0], inner // group, 2, group)
+    g, u = v[:, :, 0].reshape(gu.shape[0], inner), v[:, :, 1].reshape(gu.shape[0], inner)
     return (g / (1.0 + torch.exp(-g)) * u).to(gu.dtype)
+
+
+def gated_linear(x, w, inner, group, plain=False):
+    return silu_mul(linear(x, w), inner, group)
 
 
 def add_(x, y):

@@ -14,7 +14,7 @@ int wpc_embed(const int* tokens, const void* table, int table_dtype, float* out,
               cudaStream_t stream);
 int wpc_rmsnorm(const float* x, const float* gain, float eps, void* out, int out_dtype, int T, int H,
                 cudaStream_t stream);
-int wpc_silu_mul(const void* gu, void* out, int dtype, int T, int I, cudaStream_t stream);
+int wpc_silu_mul(const void* gu, void* out, int dtype, int T, int I, int group, cudaStream_t stream);
 int wpc_add(float* x, const void* y, int y_dtype, size_t n, cudaStream_t stream);
 int wpc_gather_rows(const float* x, const int* idx, float* out, int n_rows, int H, int T, cudaStream_t stream);
 int wpc_convert(const void* in, int in_dtype, void* out, int out_dtype, size_t n, cudaStream_t stream);
@@ -33,8 +33,9 @@ int wpc_gemm_simt(const void* A, int a_dtype, int lda, const void* W, int w_dtyp
 
 int wpc_gemm_tc_workspace(int rows_a, int rows_b, int bn, int splits, size_t* scratch_floats, int* n_counters);
 int wpc_gemm_tc(const void* a, int lda, int rows_a, const void* b, int ldb, int rows_b, int K, const float* bias,
-                void* out, int out_dtype, int ldc, int accumulate, int swap, int bn, int splits, float* scratch,
-                size_t scratch_floats, int* counters, int n_counters, int* status, cudaStream_t stream);
+                void* out, int out_dtype, int ldc, int accumulate, int gated, int swap, int bn, int splits,
+                float* scratch, size_t scratch_floats, int* counters, int n_counters, int* status,
+                cudaStream_t stream);
 
 int wpc_attention_plain(const void* q, int q_stride, void* out, int out_stride, int dtype, const void* k_pages,
                         const void* v_pages, const int* page_table, int table_width, const int* seq_of_token,

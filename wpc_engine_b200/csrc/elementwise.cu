@@ -35,15 +35,80 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
   for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_float<To>(row[i] * scale * gain[i]);
 }
 
-// ---- SiLU(gate) * up; gate = gu[:, 0:I], up = gu[:, I:2I] (wpc-runtime/src/model.rs:527-531)
+__device__ __forceinline__ void store4(float* o, float4 v) { *(float4*)o = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* o, float4 v) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 u;
+  u.x = *(uint32_t*)&a;
+  u.y = *(uint32_t*)&b;
+  *(uint2*)o = u;
+}
+
+// The same for widths that are multiples of 4 and at most 4 * VPT * blockDim: the row is read
+// once, 16 bytes at a time, and stays in registers between the sum and the scaling.
+template <typename To, int VPT>
+__global__ void rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ gain,
+                                   float eps, To* __restrict__ out, int H) {
+  __shared__ float red[32];
+  const float4* row = (const float4*)(x + (size_t)blockIdx.x * H);
+  const float4* g4 = (const float4*)gain;
+  To* o = out + (size_t)blockIdx.x * H;
+  const int n4 = H / 4;
+  float4 v[VPT], g[VPT];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int i = threadIdx.x + k * blockDim.x;
+    if (i < n4) {
+      v[k] = row[i];
+      g[k] = g4[i];
+      ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+    }
+  }
+  ss = block_sum(ss, red);
+  const float scale = 1.0f / sqrtf(ss / (float)H + eps);
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int i = threadIdx.x + k * blockDim.x;
+    if (i < n4)
+      store4(o + 4 * i, make_float4(v[k].x * scale * g[k].x, v[k].y * scale * g[k].y, v[k].z * scale * g[k].z,
+                                    v[k].w * scale * g[k].w));
+  }
+}
+
+// ---- SiLU(gate) * up (wpc-runtime/src/model.rs:527-531).  gu rows hold gate and up interleaved
+//      in blocks of G features: [G gate | G up | G gate | ...]; G = I is "all gates, then all ups".
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t n) {
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, int G, size_t n) {
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
     const size_t t = i / I;
     const int c = (int)(i - t * I);
-    const float g = to_float(gu[t * 2 * I + c]);
-    const float u = to_float(gu[t * 2 * I + I + c]);
+    const size_t base = t * 2 * I + (size_t)(c / G) * 2 * G + c % G;
+    const float g = to_float(gu[base]);
+    const float u = to_float(gu[base + G]);
     out[i] = from_float<T>(g / (1.0f + expf(-g)) * u);
+  }
+}
+
+// bfloat16, 8 features a thread (G a multiple of 8, rows 16-byte aligned)
+__global__ void silu_mul_vec_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int I,
+                                    int G, size_t n8) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t e = i * 8;
+    const size_t t = e / I;
+    const int c = (int)(e - t * I);
+    const size_t base = t * 2 * I + (size_t)(c / G) * 2 * G + c % G;
+    const uint4 gv = *(const uint4*)(gu + base), uv = *(const uint4*)(gu + base + G);
+    const __nv_bfloat162* g2 = (const __nv_bfloat162*)&gv;
+    const __nv_bfloat162* u2 = (const __nv_bfloat162*)&uv;
+    uint4 ov;
+    __nv_bfloat162* o2 = (__nv_bfloat162*)&ov;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 g = __bfloat1622float2(g2[k]), u = __bfloat1622float2(u2[k]);
+      o2[k] = __floats2bfloat162_rn(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y);
+    }
+    *(uint4*)(out + e) = ov;
   }
 }
 
@@ -106,6 +171,7 @@ __global__ void rope_inplace_kernel(T* __restrict__ x, int row_stride, int n_hea
 // ---- q and k rotated (q in place), k and v appended to the pages of their sequence
 //      (wpc-runtime/src/model.rs:464-475: keys are stored after rotation, values as they are).
 //      Row layout of qkv: nh query heads, then nkv key heads, then nkv value heads.
+//      One block per (token, head of the row).
 template <typename T>
 __global__ void qk_rope_kv_store_kernel(T* __restrict__ qkv, int row_stride, int nh, int nkv, int hd, int R,
                                         const float* __restrict__ cosv, const float* __restrict__ sinv,
@@ -113,45 +179,46 @@ __global__ void qk_rope_kv_store_kernel(T* __restrict__ qkv, int row_stride, int
                                         const int* __restrict__ page_table, int table_width,
                                         const int* __restrict__ seq_of_token, const int* __restrict__ positions,
                                         int n_pages, int* __restrict__ status) {
-  const int t = blockIdx.x, half = hd / 2;
-  T* row = qkv + (size_t)t * row_stride;
+  const int t = blockIdx.x, head = blockIdx.y, half = hd / 2;
+  T* src = qkv + (size_t)t * row_stride + (size_t)head * hd;
+  const float* ct = cosv ? cosv + (size_t)t * R : nullptr;
+  const float* st = sinv ? sinv + (size_t)t * R : nullptr;
+  if (head < nh) {
+    for (int r = threadIdx.x; r < R; r += blockDim.x) {
+      float o1, o2;
+      rotate_pair(src, r, half, ct[r], st[r], o1, o2);
+      src[r] = from_float<T>(o1);
+      src[r + half] = from_float<T>(o2);
+    }
+    return;
+  }
   const int pos = positions[t];
   const int b = seq_of_token[t];
   const int block = pos / WPC_PAGE;
   const int page = (block < table_width) ? page_table[(size_t)b * table_width + block] : -1;
-  const bool ok = page >= 0 && page < n_pages;
-  if (!ok && threadIdx.x == 0 && status) atomicExch(status, WPC_ERR_BAD_ARGUMENT);
-  const float* ct = cosv ? cosv + (size_t)t * R : nullptr;
-  const float* st = sinv ? sinv + (size_t)t * R : nullptr;
-  // queries
-  for (int i = threadIdx.x; i < nh * R; i += blockDim.x) {
-    const int h = i / R, r = i - h * R;
-    float o1, o2;
-    rotate_pair(row + h * hd, r, half, ct[r], st[r], o1, o2);
-    row[h * hd + r] = from_float<T>(o1);
-    row[h * hd + r + half] = from_float<T>(o2);
+  if (page < 0 || page >= n_pages) {
+    if (threadIdx.x == 0 && status) atomicExch(status, WPC_ERR_BAD_ARGUMENT);
+    return;
   }
-  if (!ok) return;
-  // keys: rotated where r < R, copied elsewhere
-  const T* krow = row + (size_t)nh * hd;
-  const T* vrow = krow + (size_t)nkv * hd;
   const int in_page = pos % WPC_PAGE;
-  for (int i = threadIdx.x; i < nkv * half; i += blockDim.x) {
-    const int h = i / half, r = i - h * half;
+  if (head < nh + nkv) {
+    const int h = head - nh;
     T* dst = k_pages + (((size_t)page * nkv + h) * WPC_PAGE + in_page) * hd;
-    if (r < R) {
-      float o1, o2;
-      rotate_pair(krow + h * hd, r, half, ct[r], st[r], o1, o2);
-      dst[r] = from_float<T>(o1);
-      dst[r + half] = from_float<T>(o2);
-    } else {
-      dst[r] = krow[h * hd + r];
-      dst[r + half] = krow[h * hd + r + half];
+    for (int r = threadIdx.x; r < half; r += blockDim.x) {
+      if (r < R) {
+        float o1, o2;
+        rotate_pair(src, r, half, ct[r], st[r], o1, o2);
+        dst[r] = from_float<T>(o1);
+        dst[r + half] = from_float<T>(o2);
+      } else {
+        dst[r] = src[r];
+        dst[r + half] = src[r + half];
+      }
     }
-  }
-  for (int i = threadIdx.x; i < nkv * hd; i += blockDim.x) {
-    const int h = i / hd, d = i - h * hd;
-    v_pages[(((size_t)page * nkv + h) * WPC_PAGE + in_page) * hd + d] = vrow[i];
+  } else {
+    const int h = head - nh - nkv;
+    T* dst = v_pages + (((size_t)page * nkv + h) * WPC_PAGE + in_page) * hd;
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) dst[d] = src[d];
   }
 }
 
@@ -190,16 +257,31 @@ int wpc_embed(const int* tokens, const void* table, int table_dtype, float* out,
 int wpc_rmsnorm(const float* x, const float* gain, float eps, void* out, int out_dtype, int T, int H,
                 cudaStream_t stream) {
   if (T <= 0) return 0;
-  const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
-  WPC_DISPATCH_DTYPE(out_dtype, To, (rmsnorm_kernel<To><<<T, threads, 0, stream>>>(x, gain, eps, (To*)out, H)));
+  const bool aligned = H % 4 == 0 && (((uintptr_t)x | (uintptr_t)gain | (uintptr_t)out) & 15) == 0;
+  if (aligned && H <= 1024) {
+    WPC_DISPATCH_DTYPE(out_dtype, To, (rmsnorm_vec_kernel<To, 2><<<T, 128, 0, stream>>>(x, gain, eps, (To*)out, H)));
+  } else if (aligned && H <= 4096) {
+    WPC_DISPATCH_DTYPE(out_dtype, To, (rmsnorm_vec_kernel<To, 4><<<T, 256, 0, stream>>>(x, gain, eps, (To*)out, H)));
+  } else if (aligned && H <= 16384) {
+    WPC_DISPATCH_DTYPE(out_dtype, To, (rmsnorm_vec_kernel<To, 8><<<T, 512, 0, stream>>>(x, gain, eps, (To*)out, H)));
+  } else {
+    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    WPC_DISPATCH_DTYPE(out_dtype, To, (rmsnorm_kernel<To><<<T, threads, 0, stream>>>(x, gain, eps, (To*)out, H)));
+  }
   return launch_status();
 }
 
-int wpc_silu_mul(const void* gu, void* out, int dtype, int T, int I, cudaStream_t stream) {
+int wpc_silu_mul(const void* gu, void* out, int dtype, int T, int I, int group, cudaStream_t stream) {
   const size_t n = (size_t)T * I;
   if (n == 0) return 0;
-  WPC_DISPATCH_DTYPE(dtype, Tt,
-                     (silu_mul_kernel<Tt><<<grid_for(n, 256), 256, 0, stream>>>((const Tt*)gu, (Tt*)out, I, n)));
+  if (group < 1 || I % group) return WPC_ERR_BAD_ARGUMENT;
+  if (dtype == WPC_DTYPE_BF16 && group % 8 == 0 && (((uintptr_t)gu | (uintptr_t)out) & 15) == 0) {
+    silu_mul_vec_kernel<<<grid_for(n / 8, 256), 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I,
+                                                                 group, n / 8);
+    return launch_status();
+  }
+  WPC_DISPATCH_DTYPE(dtype, Tt, (silu_mul_kernel<Tt><<<grid_for(n, 256), 256, 0, stream>>>((const Tt*)gu, (Tt*)out,
+                                                                                          I, group, n)));
   return launch_status();
 }
 
@@ -251,7 +333,7 @@ int wpc_qk_rope_kv_store(void* qkv, int dtype, int row_stride, int T, int nh, in
   if (T <= 0) return 0;
   if (hd % 2 || R > hd / 2 || (R > 0 && (!cosv || !sinv))) return WPC_ERR_BAD_ARGUMENT;
   WPC_DISPATCH_DTYPE(dtype, Tt,
-                     (qk_rope_kv_store_kernel<Tt><<<T, 256, 0, stream>>>(
+                     (qk_rope_kv_store_kernel<Tt><<<dim3(T, nh + 2 * nkv), hd >= 128 ? 64 : 32, 0, stream>>>(
                          (Tt*)qkv, row_stride, nh, nkv, hd, R, cosv, sinv, (Tt*)k_pages, (Tt*)v_pages, page_table,
                          table_width, seq_of_token, positions, n_pages, status)));
   return launch_status();

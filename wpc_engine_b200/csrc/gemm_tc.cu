@@ -51,6 +51,8 @@ struct Params {
   int ldc;                     // row stride of out, in elements
   int out_bf16;                // 1: bfloat16, 0: float32
   int accumulate;              // 1: out (float32) += result
+  int gated;                   // 1: columns c and c + BN/2 of a tile are gate and up of one feature;
+                               //    out[row, tile * BN/2 + c] = silu(gate) * up, bfloat16 (normal arrangement)
   float* scratch;              // split-K partial sums: [tile][split][BN][BM] float32
   int* counters;               // one ticket counter per tile, zero between launches
   int* status;                 // device error word (may be null)
@@ -323,7 +325,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       if (run_epilogue) __threadfence();
     }
 
-    if (run_epilogue) {
+    if (!SWAP && BN >= 64 && run_epilogue && p.gated) {
+      // gate in columns [0, BN/2), up in [BN/2, BN) of the tile (wpc-runtime/src/model.rs:527-531)
+      const int row = m0 + r;
+      for (int c = 0; c < BN / 2; c += 32) {
+        uint32_t ug[32], uu[32];
+        float v[32];
+        if (have_acc) {
+          tmem_ld32(lane_addr + c, ug);
+          tmem_ld32(lane_addr + BN / 2 + c, uu);
+          tmem_ld_wait();
+        }
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const float g = have_acc ? __uint_as_float(ug[j]) : 0.f, u = have_acc ? __uint_as_float(uu[j]) : 0.f;
+          v[j] = g / (1.0f + expf(-g)) * u;
+        }
+        if (row < p.M) store_row32(p, row, blockIdx.y * (BN / 2) + c, 32, v);
+      }
+    } else if (run_epilogue) {
       const float* part0 = p.scratch ? p.scratch + (size_t)tile_id * p.splits * (size_t)(BN * BM) : nullptr;
       for (int c = 0; c < n_valid; c += 32) {
         const int nc = min(32, n_valid - c);
@@ -484,9 +504,13 @@ int wpc_gemm_tc_workspace(int rows_a, int rows_b, int bn, int splits, size_t* sc
 // a: [rows_a, K] bfloat16, row stride lda; b: [rows_b, K] bfloat16, row stride ldb.
 // swap = 0: out[rows_a, rows_b] (bias over rows_b);  swap = 1: out[rows_b, rows_a] (bias over
 // rows_a).  bn: the tile's extent along rows_b (16, 32, 64, 128; 256 without swap).
+// gated = 1 (normal arrangement only): b holds gate and up rows interleaved in blocks of bn/2
+// (bn/2 gate rows, then the bn/2 up rows of the same features); out is [rows_a, rows_b / 2]
+// bfloat16 = silu(gate) * up.
 int wpc_gemm_tc(const void* a, int lda, int rows_a, const void* b, int ldb, int rows_b, int K, const float* bias,
-                void* out, int out_dtype, int ldc, int accumulate, int swap, int bn, int splits, float* scratch,
-                size_t scratch_floats, int* counters, int n_counters, int* status, cudaStream_t stream) {
+                void* out, int out_dtype, int ldc, int accumulate, int gated, int swap, int bn, int splits,
+                float* scratch, size_t scratch_floats, int* counters, int n_counters, int* status,
+                cudaStream_t stream) {
   if (rows_a <= 0 || rows_b <= 0) return 0;
   if (K <= 0 || (lda % 8) || (ldb % 8) || (((uintptr_t)a) & 15) || (((uintptr_t)b) & 15)) return WPC_ERR_UNSUPPORTED;
   if (accumulate && out_dtype != WPC_DTYPE_F32) return WPC_ERR_BAD_ARGUMENT;
@@ -496,7 +520,10 @@ int wpc_gemm_tc(const void* a, int lda, int rows_a, const void* b, int ldb, int 
   p.splits = splits < 1 ? 1 : (splits > p.k_blocks ? p.k_blocks : splits);
   p.bias = bias; p.out = out; p.ldc = ldc;
   p.out_bf16 = out_dtype == WPC_DTYPE_BF16; p.accumulate = accumulate;
+  p.gated = gated;
   p.scratch = scratch; p.counters = counters; p.status = status;
+  if (gated && (swap || bn < 64 || p.splits != 1 || accumulate || !p.out_bf16 || bias || rows_b % bn))
+    return WPC_ERR_UNSUPPORTED;
   if (p.splits > 1) {
     size_t need_f; int need_c;
     wpc_gemm_tc_workspace(rows_a, rows_b, bn, p.splits, &need_f, &need_c);
@@ -612,6 +639,7 @@ extern "C" int wpc_linear_few_tokens_static(const void* x, int ldx, int tokens, 
   p.splits = splits;
   p.bias = bias; p.out = out; p.ldc = ldc;
   p.out_bf16 = out_dtype == WPC_DTYPE_BF16; p.accumulate = 0;
+  p.gated = 0;
   p.scratch = scratch; p.counters = counters; p.status = status;
   CUtensorMap ma, mb;
   rc = tensor_map_uncached(w, features, K, ldw, BM, &ma);

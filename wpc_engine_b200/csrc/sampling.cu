@@ -1,14 +1,15 @@
 // Picking the next token from float32 logits: greedy (the first strictly greatest value,
 // banned ids skipped; wpc-runtime/src/sampling.rs:3-13, 35-51) or, with a temperature, a
 // draw from softmax(logits / T) by inverse CDF in index order with one counter-based uniform
-// number per draw.  One block per row; each thread owns a contiguous range of the
-// vocabulary, so that the cumulative sums run in index order whatever the block size.
+// number per draw.  One block per row.  The maximum is found with coalesced strided reads; for
+// a draw each thread then owns a contiguous range of the vocabulary, so that the cumulative
+// sums run in index order.
 #include "api.h"
 #include "common.cuh"
 
 namespace wpc {
 
-constexpr int SP_THREADS = 512;
+constexpr int SP_THREADS = 1024;
 
 __device__ __forceinline__ bool is_banned(int i, const int* banned, int n_banned) {
   for (int j = 0; j < n_banned; ++j)
@@ -31,10 +32,11 @@ sample_kernel(const float* __restrict__ logits, int V, const int* __restrict__ s
   const int chunk = (V + SP_THREADS - 1) / SP_THREADS;
   const int lo = min(V, tid * chunk), hi = min(V, lo + chunk);
 
-  // the first strictly greatest value of this thread's range
+  // the first strictly greatest value: threads stride over the row (coalesced); among equal
+  // values the lowest index wins, within a thread by order and between threads by comparison
   float best = -INFINITY;
   int best_i = -1;
-  for (int i = lo; i < hi; ++i) {
+  for (int i = tid; i < V; i += SP_THREADS) {
     const float v = z[i];
     if (v > best && !(n_banned && is_banned(i, banned, n_banned))) {
       best = v;
@@ -46,10 +48,12 @@ sample_kernel(const float* __restrict__ logits, int V, const int* __restrict__ s
   __syncthreads();
   for (int s = SP_THREADS / 2; s > 0; s >>= 1) {
     if (tid < s) {
-      // the lower thread holds lower indices: it keeps its value unless the other is greater
-      if (s_val[tid + s] > s_val[tid] || (s_idx[tid] < 0 && s_idx[tid + s] >= 0)) {
-        s_val[tid] = s_val[tid + s];
-        s_idx[tid] = s_idx[tid + s];
+      const float ov = s_val[tid + s];
+      const int oi = s_idx[tid + s];
+      const bool take = oi >= 0 && (s_idx[tid] < 0 || ov > s_val[tid] || (ov == s_val[tid] && oi < s_idx[tid]));
+      if (take) {
+        s_val[tid] = ov;
+        s_idx[tid] = oi;
       }
     }
     __syncthreads();

@@ -215,17 +215,45 @@ def _tensor_core_linear(x, w, bias, out, accumulate) -> bool:
         a, b = x, w
     _check("gemm_tc", library().wpc_gemm_tc(
         _p(a), a.stride(0), a.shape[0], _p(b), b.stride(0), b.shape[0], K, _p(bias), _p(out), _code(out.dtype),
-        out.stride(0), accumulate, int(swap), bn, splits, _p(scratch), ctypes.c_size_t(scratch.numel()),
+        out.stride(0), accumulate, 0, int(swap), bn, splits, _p(scratch), ctypes.c_size_t(scratch.numel()),
         _p(counters), counters.numel(), _p(status), _stream()))
     return True
 
 
-def silu_mul(gu: torch.Tensor, inner: int) -> torch.Tensor:
-    """silu(gu[:, :inner]) * gu[:, inner:]."""
+def silu_mul(gu: torch.Tensor, inner: int, group: Optional[int] = None) -> torch.Tensor:
+    """silu(gate) * up, where a row of gu holds gate and up interleaved in blocks of `group`
+    features ([group gates | group ups | ...]); group None or inner: all gates, then all ups."""
+    group = inner if group is None else group
     _need(gu.is_contiguous() and gu.dim() == 2 and gu.shape[1] == 2 * inner, "gu must be contiguous [T, 2*inner]")
+    _need(group >= 1 and inner % group == 0, "group must divide inner")
     out = torch.empty((gu.shape[0], inner), dtype=gu.dtype, device=gu.device)
-    _check("silu_mul", library().wpc_silu_mul(_p(gu), _p(out), _code(gu.dtype), gu.shape[0], inner, _stream()))
+    _check("silu_mul", library().wpc_silu_mul(_p(gu), _p(out), _code(gu.dtype), gu.shape[0], inner, group, _stream()))
     return out
+
+
+GATED_GROUP = 128     # gate/up interleave that lets the tensor-core product apply silu(gate) * up itself
+
+
+def gated_linear(x: torch.Tensor, w: torch.Tensor, inner: int, group: int, plain: bool = False) -> torch.Tensor:
+    """silu(x Wg^T) * (x Wu^T) as [T, inner], where w [2*inner, K] holds the rows of Wg and Wu
+    interleaved in blocks of `group`.  With bfloat16, group 128 and more than 128 tokens the
+    tensor-core product applies the activation in its epilogue and the [T, 2*inner]
+    intermediate never reaches memory; otherwise a product and `silu_mul` follow one another."""
+    _rows(x, "x")
+    _rows(w, "w")
+    M, K = x.shape
+    _need(w.shape == (2 * inner, K), "w must be [2*inner, K]")
+    if (not plain and group == GATED_GROUP and M > 128 and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+            and K % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
+            and w.data_ptr() % 16 == 0):
+        out = torch.empty((M, inner), dtype=torch.bfloat16, device=x.device)
+        scratch, counters, status = workspace(x.device)
+        _check("gemm_tc", library().wpc_gemm_tc(
+            _p(x), x.stride(0), M, _p(w), w.stride(0), 2 * inner, K, _p(None), _p(out), _BF16, out.stride(0), 0, 1,
+            0, 2 * GATED_GROUP, 1, _p(scratch), ctypes.c_size_t(scratch.numel()), _p(counters), counters.numel(),
+            _p(status), _stream()))
+        return out
+    return silu_mul(linear(x, w, plain=plain), inner, group)
 
 
 def add_(x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:

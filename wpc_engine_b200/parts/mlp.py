@@ -7,14 +7,18 @@ import torch
 
 from .. import ops
 from .base import FeedForward
-from .linear import Linear, fuse_rows
+from .linear import Linear
 
 
 class SwiGLU(FeedForward):
     """down( silu(gate(h)) * up(h) ), no biases (model.rs:107-109).
 
-    After loading, the gate and up matrices are stacked into one [2*inner, width] matrix so
-    that one product reads h once; the activation reads both halves of a row.
+    After loading, the gate and up matrices become one [2*inner, width] matrix so that one
+    product reads h once.  Their rows are interleaved in blocks of `group` features (`group`
+    gate rows, then the `group` up rows of the same features): with 16-bit weights and an
+    inner size that 128 divides the group is 128, which lets the product's epilogue apply the
+    activation; otherwise the group is the whole inner size (all gates, then all ups).  Each
+    output is still the same dot product of the same row: a pure re-layout.
     """
 
     def __init__(self, width: int, inner: int):
@@ -24,17 +28,23 @@ class SwiGLU(FeedForward):
         self.up_proj = Linear(width, inner)
         self.down_proj = Linear(inner, width)
         self.gate_up = None
+        self.group = self.inner
 
     def subparts(self) -> Dict[str, object]:
         return {"gate_proj": self.gate_proj, "up_proj": self.up_proj, "down_proj": self.down_proj}
 
     def finalize(self):
-        self.gate_up = fuse_rows([self.gate_proj, self.up_proj])
-        self.gate_proj.weight = self.gate_up.weight[: self.inner]
-        self.up_proj.weight = self.gate_up.weight[self.inner:]
+        g, u = self.gate_proj.weight, self.up_proj.weight
+        G = ops.GATED_GROUP
+        self.group = G if (self.inner % G == 0 and g.dtype == torch.bfloat16) else self.inner
+        blocks = self.inner // self.group
+        fused = torch.stack([g.view(blocks, self.group, self.width), u.view(blocks, self.group, self.width)], dim=1)
+        self.gate_up = Linear(self.width, 2 * self.inner)
+        self.gate_up.bind({"weight": fused.reshape(2 * self.inner, self.width).contiguous()})
+        view = self.gate_up.weight.view(blocks, 2, self.group, self.width)
+        self.gate_proj.weight, self.up_proj.weight = view[:, 0], view[:, 1]     # [blocks, group, width] views
 
     def forward(self, ctx, h: torch.Tensor, residual: torch.Tensor):
-        gu = self.gate_up.forward(h)
-        act = ops.silu_mul(gu, self.inner)
+        act = ops.gated_linear(h, self.gate_up.weight, self.inner, self.group)
         self.down_proj.forward(act, residual=residual)
         return None
