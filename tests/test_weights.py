@@ -93,7 +93,7 @@ def test_fusion_is_a_pure_relayout(folders):
     p = "model.layers.1."
     assert torch.equal(attn.qkv.weight, torch.cat([stored[p + f"self_attn.{x}_proj.weight"] for x in "qkv"]))
     assert torch.equal(attn.qkv.bias, torch.cat([stored[p + f"self_attn.{x}_proj.bias"].float() for x in "qkv"]))
-    assert mlp.group == 200                       # 128 does not divide 200: all gates, then all ups
+    assert mlp.group == 200                       # 64 does not divide 200: all gates, then all ups
     assert torch.equal(mlp.gate_up.weight, torch.cat([stored[p + "mlp.gate_proj.weight"], stored[p + "mlp.up_proj.weight"]]))
     assert torch.equal(attn.q_proj.weight, stored[p + "self_attn.q_proj.weight"])
 
@@ -106,8 +106,8 @@ def test_gate_up_interleave_is_a_pure_relayout(tmp_path):
     load_weights(model, folder, torch.bfloat16, "cpu")
     mlp = model.blocks[0].ffn
     g, u = stored["model.layers.0.mlp.gate_proj.weight"], stored["model.layers.0.mlp.up_proj.weight"]
-    assert mlp.group == 128
-    assert torch.equal(mlp.gate_up.weight, torch.cat([g[:128], u[:128], g[128:], u[128:]]))
+    assert mlp.group == 64
+    assert torch.equal(mlp.gate_up.weight, torch.cat([t[i:i + 64] for i in range(0, 256, 64) for t in (g, u)]))
     assert torch.equal(mlp.gate_proj.weight.reshape(256, 96), g) and torch.equal(mlp.up_proj.weight.reshape(256, 96), u)
 
 

@@ -29,7 +29,7 @@ def rmsnorm(x, gain, eps, out_dtype):
     return (x * (1.0 / torch.sqrt(ms + eps)) * gain).to(out_dtype)
 
 
-def linear(x, w, bias=None, out_dtype=None, residual=None):
+def linear(x, w, bias=None, out_dtype=None, residual=None, plain=False, static_weight=False):
     y = x.float() @ w.float().t()
     if bias is not None:
         y = y + bias
@@ -39,7 +39,7 @@ def linear(x, w, bias=None, out_dtype=None, residual=None):
     return y.to(out_dtype or x.dtype)
 
 
-GATED_GROUP = 128
+GATED_GROUP = 64
 
 
 def silu_mul(gu, inner, group=None):
@@ -49,7 +49,7 @@ def silu_mul(gu, inner, group=None):
     return (g / (1.0 + torch.exp(-g)) * u).to(gu.dtype)
 
 
-def gated_linear(x, w, inner, group, plain=False):
+def gated_linear(x, w, inner, group, plain=False, static_weight=False):
     return silu_mul(linear(x, w), inner, group)
 
 

@@ -10,6 +10,9 @@
 extern "C" {
 #endif
 
+// Programmatic dependent launch for all kernels of the library: on (1, the default) or off (0).
+int wpc_set_pdl(int on);
+
 int wpc_embed(const int* tokens, const void* table, int table_dtype, float* out, int T, int H, int V,
               cudaStream_t stream);
 int wpc_rmsnorm(const float* x, const float* gain, float eps, void* out, int out_dtype, int T, int H,
@@ -35,7 +38,7 @@ int wpc_gemm_tc_workspace(int rows_a, int rows_b, int bn, int splits, size_t* sc
 int wpc_gemm_tc(const void* a, int lda, int rows_a, const void* b, int ldb, int rows_b, int K, const float* bias,
                 void* out, int out_dtype, int ldc, int accumulate, int gated, int swap, int bn, int splits,
                 float* scratch, size_t scratch_floats, int* counters, int n_counters, int* status,
-                cudaStream_t stream);
+                int prefetch_weights, cudaStream_t stream);
 
 int wpc_attention_plain(const void* q, int q_stride, void* out, int out_stride, int dtype, const void* k_pages,
                         const void* v_pages, const int* page_table, int table_width, const int* seq_of_token,
@@ -46,7 +49,7 @@ int wpc_attention_mma_supports(int nh, int nkv, int hd);
 int wpc_attention_decode(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                          const void* v_pages, const int* page_table, int table_width, const int* ctx_lens, int B,
                          int nh, int nkv, int hd, float scale, int window, int splits, float* part_o, float* part_ml,
-                         cudaStream_t stream);
+                         int* counters, int n_counters, cudaStream_t stream);
 int wpc_attention_prefill(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                           const void* v_pages, const int* page_table, int table_width, const int* cu_seqlens,
                           const int* ctx_lens, int B, int max_new, int nh, int nkv, int hd, float scale, int window,

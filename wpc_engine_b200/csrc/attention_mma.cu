@@ -9,7 +9,7 @@
 //            rows hold the group's query heads; the four warps of a CTA take the four
 //            16-key quarters of each 64-key page and are merged at the end; a sequence's
 //            pages are divided over `splits` CTAs whose partial results (unnormalised
-//            output, running maximum, running sum) a second kernel combines.
+//            output, running maximum, running sum) the last of them to finish combines.
 //   prefill  any number of new tokens per sequence.  grid = (row tiles, kv heads,
 //            sequences); a tile is 64 rows of (token, head-in-group), 16 per warp; every warp
 //            walks the pages up to the tile's last visible key.
@@ -186,7 +186,9 @@ decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* 
               const __nv_bfloat16* __restrict__ k_pages, const __nv_bfloat16* __restrict__ v_pages,
               const int* __restrict__ page_table, int table_width, const int* __restrict__ ctx_lens,
               int nh, int nkv, float scale_log2, int window, int splits, float* __restrict__ part_o,
-              float* __restrict__ part_ml) {
+              float* __restrict__ part_ml, int* __restrict__ counters) {
+  pdl_trigger();
+  pdl_wait();
   extern __shared__ __align__(16) uint8_t smem_raw[];
   __nv_bfloat16* ks = (__nv_bfloat16*)smem_raw;                       // [2][PAGE][STRIDE]
   __nv_bfloat16* vs = ks + 2 * Cfg<HD>::PAGE_ELEMS;
@@ -303,11 +305,54 @@ decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* 
       }
     }
   }
+  if (splits == 1 || !counters) return;
+  // The CTA that draws the last ticket of this (sequence, kv head) combines all splits, in
+  // split order, so the result does not depend on which CTA came last.  Nobody waits.
+  __shared__ int s_last;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const int ticket = atomicAdd(counters + b * nkv + g, 1);
+    s_last = ticket == splits - 1;
+    if (s_last) counters[b * nkv + g] = 0;                 // ready for the next launch
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  // weights of the splits first (few values, staged in shared memory), then the outputs with
+  // independent loads
+  float* wf = (float*)smem_raw;                          // [n_rep][splits] factor, then [n_rep] 1 / sum
+  float* winv = wf + 16 * splits;
+  for (int row = tid; row < n_rep; row += THREADS) {
+    const size_t base = ((size_t)b * nh + g * n_rep + row) * splits;
+    float M = -INFINITY;
+    for (int s = 0; s < splits; ++s) M = fmaxf(M, __ldcg(part_ml + (base + s) * 2));
+    float Lsum = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const float ms = __ldcg(part_ml + (base + s) * 2);
+      const float f = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
+      wf[row * splits + s] = f;
+      Lsum += f * __ldcg(part_ml + (base + s) * 2 + 1);
+    }
+    winv[row] = Lsum > 0.f ? 1.f / Lsum : 0.f;
+  }
+  __syncthreads();
+  for (int e = tid; e < n_rep * HD; e += THREADS) {
+    const int row = e / HD, d = e - row * HD;
+    const int head = g * n_rep + row;
+    const float* po = part_o + ((size_t)b * nh + head) * splits * HD + d;
+    float acc = 0.f;
+#pragma unroll 4
+    for (int s = 0; s < splits; ++s) acc += wf[row * splits + s] * __ldcg(po + (size_t)s * HD);
+    out[(size_t)b * out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(acc * winv[row]);
+  }
 }
 
 template <int HD>
 __global__ void combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                __nv_bfloat16* __restrict__ out, int out_stride, int nh, int splits) {
+  pdl_trigger();
+  pdl_wait();
   const int b = blockIdx.x, head = blockIdx.y;
   const size_t base = ((size_t)b * nh + head) * splits;
   float M = -INFINITY;
@@ -331,6 +376,8 @@ prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16*
                const __nv_bfloat16* __restrict__ k_pages, const __nv_bfloat16* __restrict__ v_pages,
                const int* __restrict__ page_table, int table_width, const int* __restrict__ cu_seqlens,
                const int* __restrict__ ctx_lens, int nh, int nkv, float scale_log2, int window) {
+  pdl_trigger();
+  pdl_wait();
   extern __shared__ __align__(16) uint8_t smem_raw[];
   __nv_bfloat16* ks = (__nv_bfloat16*)smem_raw;
   __nv_bfloat16* vs = ks + 2 * Cfg<HD>::PAGE_ELEMS;
@@ -371,6 +418,8 @@ prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16*
   const int warp_pos0 = start + wr0 / n_rep;
   const int warp_lo = (window > 0 && warp_pos0 - window + 1 > 0) ? warp_pos0 - window + 1 : 0;
   const bool warp_active = row0 + warp * 16 < n_rows;
+  const bool warp_full = row0 + warp * 16 + 15 < n_rows;            // all 16 rows exist
+  const int warp_lo_last = (window > 0 && warp_hi - window + 1 > 0) ? warp_hi - window + 1 : 0;
 
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
   float o[HD / 8][4];
@@ -399,14 +448,22 @@ prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16*
     if (warp_active && abs0 <= warp_hi && abs0 + PAGE - 1 >= warp_lo) {
       float s[8][4];
       scores<HD, 8>(qf, ks + buf * Cfg<HD>::PAGE_ELEMS, 0, s, lane);
+      // a page that every row of the warp sees whole needs no mask
+      if (warp_full && abs0 + PAGE - 1 <= warp_pos0 && abs0 >= warp_lo_last) {
 #pragma unroll
-      for (int nt = 0; nt < 8; ++nt)
+        for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int kabs = abs0 + nt * 8 + (lane & 3) * 2 + (i & 1);
-          const bool vis = (i < 2) ? (v_lo && kabs >= lo_lo && kabs <= p_lo) : (v_hi && kabs >= lo_hi && kabs <= p_hi);
-          s[nt][i] = vis ? s[nt][i] * scale_log2 : -INFINITY;
-        }
+          for (int i = 0; i < 4; ++i) s[nt][i] *= scale_log2;
+      } else {
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int kabs = abs0 + nt * 8 + (lane & 3) * 2 + (i & 1);
+            const bool vis = (i < 2) ? (v_lo && kabs >= lo_lo && kabs <= p_lo) : (v_hi && kabs >= lo_hi && kabs <= p_hi);
+            s[nt][i] = vis ? s[nt][i] * scale_log2 : -INFINITY;
+          }
+      }
       softmax_step<HD, 8>(s, m, l, o);
       uint32_t pf[4][4];
       to_fragments<8>(s, pf);
@@ -435,7 +492,8 @@ template <int HD>
 static int launch_decode(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                          const void* v_pages, const int* page_table, int table_width, const int* ctx_lens, int B,
                          int nh, int nkv, float scale, int window, int splits, float* part_o, float* part_ml,
-                         cudaStream_t stream) {
+                         int* counters, int n_counters, cudaStream_t stream) {
+  if (B * nkv > n_counters) counters = nullptr;            // too many tickets: combine in a second kernel
   const int merge_bytes = (4 * 16 * HD + 2 * 4 * 16) * (int)sizeof(float);
   const int smem = Cfg<HD>::SMEM_BYTES > merge_bytes ? Cfg<HD>::SMEM_BYTES : merge_bytes;
   static bool configured = false;
@@ -445,13 +503,13 @@ static int launch_decode(const void* q, int q_stride, void* out, int out_stride,
     configured = true;
   }
   dim3 grid(splits, nkv, B);
-  decode_kernel<HD><<<grid, THREADS, smem, stream>>>(
+  wpc::launch(decode_kernel<HD>, grid, THREADS, smem, stream, 
       (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pages,
       (const __nv_bfloat16*)v_pages, page_table, table_width, ctx_lens, nh, nkv, scale * LOG2E, window, splits,
-      part_o, part_ml);
+      part_o, part_ml, counters);
   int rc = launch_status();
-  if (rc || splits == 1) return rc;
-  combine_kernel<HD><<<dim3(B, nh), HD < 32 ? 32 : HD, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, out_stride,
+  if (rc || splits == 1 || counters) return rc;
+  wpc::launch(combine_kernel<HD>, dim3(B, nh), HD < 32 ? 32 : HD, 0, stream, part_o, part_ml, (__nv_bfloat16*)out, out_stride,
                                                                    nh, splits);
   return launch_status();
 }
@@ -470,7 +528,7 @@ static int launch_prefill(const void* q, int q_stride, void* out, int out_stride
   }
   const int n_rep = nh / nkv;
   dim3 grid((max_new * n_rep + 63) / 64, nkv, B);
-  prefill_kernel<HD><<<grid, THREADS, Cfg<HD>::SMEM_BYTES, stream>>>(
+  wpc::launch(prefill_kernel<HD>, grid, THREADS, Cfg<HD>::SMEM_BYTES, stream, 
       (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pages,
       (const __nv_bfloat16*)v_pages, page_table, table_width, cu_seqlens, ctx_lens, nh, nkv, scale * LOG2E, window);
   return launch_status();
@@ -503,16 +561,18 @@ int wpc_attention_mma_supports(int nh, int nkv, int hd) {
 
 // One query token per sequence: q row b belongs to sequence b.  part_o: float32
 // [B * nh * splits * hd], part_ml: float32 [B * nh * splits * 2]; unused when splits == 1.
+// counters: B * nkv tickets, zero between launches (null or too few: a second kernel combines).
 int wpc_attention_decode(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                          const void* v_pages, const int* page_table, int table_width, const int* ctx_lens, int B,
                          int nh, int nkv, int hd, float scale, int window, int splits, float* part_o,
-                         float* part_ml, cudaStream_t stream) {
+                         float* part_ml, int* counters, int n_counters, cudaStream_t stream) {
   if (B <= 0) return 0;
-  if (!wpc_attention_mma_supports(nh, nkv, hd) || splits < 1 || (q_stride % 2) || (out_stride % 2))
+  if (!wpc_attention_mma_supports(nh, nkv, hd) || splits < 1 || splits > 64 || (q_stride % 2) || (out_stride % 2))
     return WPC_ERR_UNSUPPORTED;
   if (splits > 1 && (!part_o || !part_ml)) return WPC_ERR_BAD_ARGUMENT;
   WPC_DISPATCH_HD(hd, fa::launch_decode<HD>(q, q_stride, out, out_stride, k_pages, v_pages, page_table, table_width,
-                                           ctx_lens, B, nh, nkv, scale, window, splits, part_o, part_ml, stream));
+                                           ctx_lens, B, nh, nkv, scale, window, splits, part_o, part_ml, counters,
+                                           n_counters, stream));
 }
 
 int wpc_attention_prefill(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,

@@ -17,6 +17,8 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
                        const int* __restrict__ page_table, int table_width,
                        const int* __restrict__ seq_of_token, const int* __restrict__ positions,
                        int nh, int nkv, int hd, float scale, int window) {
+  pdl_trigger();
+  pdl_wait();
   extern __shared__ float smem[];
   float* qs = smem;                    // [hd]
   float* ps = smem + hd;               // [AP_CHUNK]
@@ -98,7 +100,7 @@ extern "C" int wpc_attention_plain(const void* q, int q_stride, void* out, int o
   const size_t smem = (size_t)(hd + AP_CHUNK) * sizeof(float);
   dim3 grid(T, nh);
   WPC_DISPATCH_DTYPE(dtype, Tt,
-                     attention_plain_kernel<Tt><<<grid, AP_THREADS, smem, stream>>>(
+                     wpc::launch(attention_plain_kernel<Tt>, grid, AP_THREADS, smem, stream, 
                          (const Tt*)q, q_stride, (Tt*)out, out_stride, (const Tt*)k_pages, (const Tt*)v_pages,
                          page_table, table_width, seq_of_token, positions, nh, nkv, hd, scale, window));
   return launch_status();

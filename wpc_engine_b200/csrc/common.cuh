@@ -69,7 +69,46 @@ __host__ __device__ __forceinline__ uint64_t mix64(uint64_t z) {
   return z ^ (z >> 31);
 }
 
-inline int launch_status() { return (int)cudaGetLastError(); }
+// ---- programmatic dependent launch ---------------------------------------------------------------
+// Every kernel of this library starts with pdl_trigger() and calls pdl_wait() before it touches
+// memory that an earlier kernel of the stream may have written.  Launched with the attribute
+// below, a kernel may then become resident, set itself up and (where it says so) fetch model
+// weights while the kernel before it is still finishing; pdl_wait() returns once that kernel
+// has completed and its writes are visible.  Without the attribute both calls do nothing.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+inline int& pdl_enabled() {
+  static int on = 1;
+  return on;
+}
+inline int& last_launch_error() {
+  static thread_local int rc = 0;
+  return rc;
+}
+
+template <typename... KArgs, typename... Args>
+inline void launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+  if (e != cudaSuccess) last_launch_error() = (int)e;
+}
+
+inline int launch_status() {
+  int rc = last_launch_error();
+  last_launch_error() = 0;
+  const int e = (int)cudaGetLastError();
+  return rc ? rc : e;
+}
 
 }  // namespace wpc
 

@@ -10,6 +10,8 @@ namespace wpc {
 template <typename Tw>
 __global__ void embed_kernel(const int* __restrict__ tokens, const Tw* __restrict__ table,
                              float* __restrict__ out, int H, int V) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   int id = tokens[t];
   if (id < 0 || id >= V) id = 0;                 // the host checks ids; never read outside
@@ -22,6 +24,8 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const Tw* __restric
 template <typename To>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ gain,
                                float eps, To* __restrict__ out, int H) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float red[32];
   const float* row = x + (size_t)blockIdx.x * H;
   To* o = out + (size_t)blockIdx.x * H;
@@ -49,6 +53,8 @@ __device__ __forceinline__ void store4(__nv_bfloat16* o, float4 v) {
 template <typename To, int VPT>
 __global__ void rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ gain,
                                    float eps, To* __restrict__ out, int H) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float red[32];
   const float4* row = (const float4*)(x + (size_t)blockIdx.x * H);
   const float4* g4 = (const float4*)gain;
@@ -80,6 +86,8 @@ __global__ void rmsnorm_vec_kernel(const float* __restrict__ x, const float* __r
 //      in blocks of G features: [G gate | G up | G gate | ...]; G = I is "all gates, then all ups".
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, int G, size_t n) {
+  pdl_trigger();
+  pdl_wait();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
     const size_t t = i / I;
     const int c = (int)(i - t * I);
@@ -93,6 +101,8 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
 // bfloat16, 8 features a thread (G a multiple of 8, rows 16-byte aligned)
 __global__ void silu_mul_vec_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int I,
                                     int G, size_t n8) {
+  pdl_trigger();
+  pdl_wait();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x) {
     const size_t e = i * 8;
     const size_t t = e / I;
@@ -114,12 +124,16 @@ __global__ void silu_mul_vec_kernel(const __nv_bfloat16* __restrict__ gu, __nv_b
 
 template <typename T>
 __global__ void add_kernel(float* __restrict__ x, const T* __restrict__ y, size_t n) {
+  pdl_trigger();
+  pdl_wait();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
     x[i] += to_float(y[i]);
 }
 
 __global__ void gather_rows_kernel(const float* __restrict__ x, const int* __restrict__ idx,
                                    float* __restrict__ out, int H, int T) {
+  pdl_trigger();
+  pdl_wait();
   int r = idx[blockIdx.x];
   if (r < 0 || r >= T) r = 0;
   const float* row = x + (size_t)r * H;
@@ -129,6 +143,8 @@ __global__ void gather_rows_kernel(const float* __restrict__ x, const int* __res
 
 template <typename Ti, typename To>
 __global__ void convert_kernel(const Ti* __restrict__ in, To* __restrict__ out, size_t n) {
+  pdl_trigger();
+  pdl_wait();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
     out[i] = from_float<To>(to_float(in[i]));
 }
@@ -136,6 +152,8 @@ __global__ void convert_kernel(const Ti* __restrict__ in, To* __restrict__ out, 
 // ---- rotation angles in float64, as wpc-runtime/src/rope.rs:30-33 computes them
 __global__ void rope_angles_kernel(const int* __restrict__ positions, const double* __restrict__ inv_freq,
                                    float* __restrict__ cosv, float* __restrict__ sinv, int R, int n) {
+  pdl_trigger();
+  pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const int t = i / R, r = i - t * R;
@@ -157,6 +175,8 @@ __device__ __forceinline__ void rotate_pair(const T* v, int r, int half, float c
 template <typename T>
 __global__ void rope_inplace_kernel(T* __restrict__ x, int row_stride, int n_heads, int hd, int R,
                                     const float* __restrict__ cosv, const float* __restrict__ sinv) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x, half = hd / 2;
   T* row = x + (size_t)t * row_stride;
   for (int i = threadIdx.x; i < n_heads * R; i += blockDim.x) {
@@ -171,7 +191,8 @@ __global__ void rope_inplace_kernel(T* __restrict__ x, int row_stride, int n_hea
 // ---- q and k rotated (q in place), k and v appended to the pages of their sequence
 //      (wpc-runtime/src/model.rs:464-475: keys are stored after rotation, values as they are).
 //      Row layout of qkv: nh query heads, then nkv key heads, then nkv value heads.
-//      One block per (token, head of the row).
+//      One warp per (token, head of the row), eight heads to a block.
+constexpr int ROPE_HEADS_PER_BLOCK = 8;
 template <typename T>
 __global__ void qk_rope_kv_store_kernel(T* __restrict__ qkv, int row_stride, int nh, int nkv, int hd, int R,
                                         const float* __restrict__ cosv, const float* __restrict__ sinv,
@@ -179,12 +200,16 @@ __global__ void qk_rope_kv_store_kernel(T* __restrict__ qkv, int row_stride, int
                                         const int* __restrict__ page_table, int table_width,
                                         const int* __restrict__ seq_of_token, const int* __restrict__ positions,
                                         int n_pages, int* __restrict__ status) {
-  const int t = blockIdx.x, head = blockIdx.y, half = hd / 2;
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x, half = hd / 2, lane = threadIdx.x & 31;
+  const int head = blockIdx.y * ROPE_HEADS_PER_BLOCK + (threadIdx.x >> 5);
+  if (head >= nh + 2 * nkv) return;
   T* src = qkv + (size_t)t * row_stride + (size_t)head * hd;
   const float* ct = cosv ? cosv + (size_t)t * R : nullptr;
   const float* st = sinv ? sinv + (size_t)t * R : nullptr;
   if (head < nh) {
-    for (int r = threadIdx.x; r < R; r += blockDim.x) {
+    for (int r = lane; r < R; r += 32) {
       float o1, o2;
       rotate_pair(src, r, half, ct[r], st[r], o1, o2);
       src[r] = from_float<T>(o1);
@@ -197,14 +222,14 @@ __global__ void qk_rope_kv_store_kernel(T* __restrict__ qkv, int row_stride, int
   const int block = pos / WPC_PAGE;
   const int page = (block < table_width) ? page_table[(size_t)b * table_width + block] : -1;
   if (page < 0 || page >= n_pages) {
-    if (threadIdx.x == 0 && status) atomicExch(status, WPC_ERR_BAD_ARGUMENT);
+    if (lane == 0 && status) atomicExch(status, WPC_ERR_BAD_ARGUMENT);
     return;
   }
   const int in_page = pos % WPC_PAGE;
   if (head < nh + nkv) {
     const int h = head - nh;
     T* dst = k_pages + (((size_t)page * nkv + h) * WPC_PAGE + in_page) * hd;
-    for (int r = threadIdx.x; r < half; r += blockDim.x) {
+    for (int r = lane; r < half; r += 32) {
       if (r < R) {
         float o1, o2;
         rotate_pair(src, r, half, ct[r], st[r], o1, o2);
@@ -218,7 +243,7 @@ __global__ void qk_rope_kv_store_kernel(T* __restrict__ qkv, int row_stride, int
   } else {
     const int h = head - nh - nkv;
     T* dst = v_pages + (((size_t)page * nkv + h) * WPC_PAGE + in_page) * hd;
-    for (int d = threadIdx.x; d < hd; d += blockDim.x) dst[d] = src[d];
+    for (int d = lane; d < hd; d += 32) dst[d] = src[d];
   }
 }
 
@@ -226,6 +251,8 @@ __global__ void qk_rope_kv_store_kernel(T* __restrict__ qkv, int row_stride, int
 //      draws from mix64(k ^ mix64(i)); Box-Muller on two 24-bit uniforms
 template <typename T>
 __global__ void fill_normal_kernel(T* __restrict__ out, size_t n, uint64_t key, float mean, float std) {
+  pdl_trigger();
+  pdl_wait();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
     const uint64_t z = mix64(key ^ mix64((uint64_t)i));
     const float u1 = ((float)((z >> 40) & 0xFFFFFF) + 1.0f) * (1.0f / 16777216.0f);   // (0, 1]
@@ -246,11 +273,17 @@ using namespace wpc;
 
 extern "C" {
 
+int wpc_set_pdl(int on) {
+  const int was = pdl_enabled();
+  pdl_enabled() = on ? 1 : 0;
+  return was;
+}
+
 int wpc_embed(const int* tokens, const void* table, int table_dtype, float* out, int T, int H, int V,
               cudaStream_t stream) {
   if (T <= 0) return 0;
   WPC_DISPATCH_DTYPE(table_dtype, Tw,
-                     (embed_kernel<Tw><<<T, 256, 0, stream>>>(tokens, (const Tw*)table, out, H, V)));
+                     (wpc::launch(embed_kernel<Tw>, T, 256, 0, stream, tokens, (const Tw*)table, out, H, V)));
   return launch_status();
 }
 
@@ -259,14 +292,14 @@ int wpc_rmsnorm(const float* x, const float* gain, float eps, void* out, int out
   if (T <= 0) return 0;
   const bool aligned = H % 4 == 0 && (((uintptr_t)x | (uintptr_t)gain | (uintptr_t)out) & 15) == 0;
   if (aligned && H <= 1024) {
-    WPC_DISPATCH_DTYPE(out_dtype, To, (rmsnorm_vec_kernel<To, 2><<<T, 128, 0, stream>>>(x, gain, eps, (To*)out, H)));
+    WPC_DISPATCH_DTYPE(out_dtype, To, (wpc::launch(rmsnorm_vec_kernel<To, 2>, T, 128, 0, stream, x, gain, eps, (To*)out, H)));
   } else if (aligned && H <= 4096) {
-    WPC_DISPATCH_DTYPE(out_dtype, To, (rmsnorm_vec_kernel<To, 4><<<T, 256, 0, stream>>>(x, gain, eps, (To*)out, H)));
+    WPC_DISPATCH_DTYPE(out_dtype, To, (wpc::launch(rmsnorm_vec_kernel<To, 4>, T, 256, 0, stream, x, gain, eps, (To*)out, H)));
   } else if (aligned && H <= 16384) {
-    WPC_DISPATCH_DTYPE(out_dtype, To, (rmsnorm_vec_kernel<To, 8><<<T, 512, 0, stream>>>(x, gain, eps, (To*)out, H)));
+    WPC_DISPATCH_DTYPE(out_dtype, To, (wpc::launch(rmsnorm_vec_kernel<To, 8>, T, 512, 0, stream, x, gain, eps, (To*)out, H)));
   } else {
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
-    WPC_DISPATCH_DTYPE(out_dtype, To, (rmsnorm_kernel<To><<<T, threads, 0, stream>>>(x, gain, eps, (To*)out, H)));
+    WPC_DISPATCH_DTYPE(out_dtype, To, (wpc::launch(rmsnorm_kernel<To>, T, threads, 0, stream, x, gain, eps, (To*)out, H)));
   }
   return launch_status();
 }
@@ -276,24 +309,24 @@ int wpc_silu_mul(const void* gu, void* out, int dtype, int T, int I, int group, 
   if (n == 0) return 0;
   if (group < 1 || I % group) return WPC_ERR_BAD_ARGUMENT;
   if (dtype == WPC_DTYPE_BF16 && group % 8 == 0 && (((uintptr_t)gu | (uintptr_t)out) & 15) == 0) {
-    silu_mul_vec_kernel<<<grid_for(n / 8, 256), 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I,
+    wpc::launch(silu_mul_vec_kernel, grid_for(n / 8, 256), 256, 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I,
                                                                  group, n / 8);
     return launch_status();
   }
-  WPC_DISPATCH_DTYPE(dtype, Tt, (silu_mul_kernel<Tt><<<grid_for(n, 256), 256, 0, stream>>>((const Tt*)gu, (Tt*)out,
+  WPC_DISPATCH_DTYPE(dtype, Tt, (wpc::launch(silu_mul_kernel<Tt>, grid_for(n, 256), 256, 0, stream, (const Tt*)gu, (Tt*)out,
                                                                                           I, group, n)));
   return launch_status();
 }
 
 int wpc_add(float* x, const void* y, int y_dtype, size_t n, cudaStream_t stream) {
   if (n == 0) return 0;
-  WPC_DISPATCH_DTYPE(y_dtype, Tt, (add_kernel<Tt><<<grid_for(n, 256), 256, 0, stream>>>(x, (const Tt*)y, n)));
+  WPC_DISPATCH_DTYPE(y_dtype, Tt, (wpc::launch(add_kernel<Tt>, grid_for(n, 256), 256, 0, stream, x, (const Tt*)y, n)));
   return launch_status();
 }
 
 int wpc_gather_rows(const float* x, const int* idx, float* out, int n_rows, int H, int T, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
-  gather_rows_kernel<<<n_rows, 256, 0, stream>>>(x, idx, out, H, T);
+  wpc::launch(gather_rows_kernel, n_rows, 256, 0, stream, x, idx, out, H, T);
   return launch_status();
 }
 
@@ -301,9 +334,9 @@ int wpc_convert(const void* in, int in_dtype, void* out, int out_dtype, size_t n
   if (n == 0) return 0;
   const int g = grid_for(n, 256);
   if (in_dtype == WPC_DTYPE_F32 && out_dtype == WPC_DTYPE_BF16)
-    convert_kernel<float, __nv_bfloat16><<<g, 256, 0, stream>>>((const float*)in, (__nv_bfloat16*)out, n);
+    wpc::launch(convert_kernel<float, __nv_bfloat16>, g, 256, 0, stream, (const float*)in, (__nv_bfloat16*)out, n);
   else if (in_dtype == WPC_DTYPE_BF16 && out_dtype == WPC_DTYPE_F32)
-    convert_kernel<__nv_bfloat16, float><<<g, 256, 0, stream>>>((const __nv_bfloat16*)in, (float*)out, n);
+    wpc::launch(convert_kernel<__nv_bfloat16, float>, g, 256, 0, stream, (const __nv_bfloat16*)in, (float*)out, n);
   else
     return WPC_ERR_BAD_ARGUMENT;
   return launch_status();
@@ -313,7 +346,7 @@ int wpc_rope_angles(const int* positions, const double* inv_freq, float* cosv, f
                     cudaStream_t stream) {
   const int n = T * R;
   if (n <= 0) return 0;
-  rope_angles_kernel<<<(n + 127) / 128, 128, 0, stream>>>(positions, inv_freq, cosv, sinv, R, n);
+  wpc::launch(rope_angles_kernel, (n + 127) / 128, 128, 0, stream, positions, inv_freq, cosv, sinv, R, n);
   return launch_status();
 }
 
@@ -321,7 +354,7 @@ int wpc_rope_inplace(void* x, int dtype, int row_stride, int T, int n_heads, int
                      const float* sinv, cudaStream_t stream) {
   if (T <= 0 || R <= 0) return 0;
   if (hd % 2 || R > hd / 2) return WPC_ERR_BAD_ARGUMENT;
-  WPC_DISPATCH_DTYPE(dtype, Tt, (rope_inplace_kernel<Tt><<<T, 256, 0, stream>>>((Tt*)x, row_stride, n_heads, hd,
+  WPC_DISPATCH_DTYPE(dtype, Tt, (wpc::launch(rope_inplace_kernel<Tt>, T, 256, 0, stream, (Tt*)x, row_stride, n_heads, hd,
                                                                                R, cosv, sinv)));
   return launch_status();
 }
@@ -333,7 +366,8 @@ int wpc_qk_rope_kv_store(void* qkv, int dtype, int row_stride, int T, int nh, in
   if (T <= 0) return 0;
   if (hd % 2 || R > hd / 2 || (R > 0 && (!cosv || !sinv))) return WPC_ERR_BAD_ARGUMENT;
   WPC_DISPATCH_DTYPE(dtype, Tt,
-                     (qk_rope_kv_store_kernel<Tt><<<dim3(T, nh + 2 * nkv), hd >= 128 ? 64 : 32, 0, stream>>>(
+                     (wpc::launch(qk_rope_kv_store_kernel<Tt>, dim3(T, (nh + 2 * nkv + ROPE_HEADS_PER_BLOCK - 1) / ROPE_HEADS_PER_BLOCK),
+                                 32 * ROPE_HEADS_PER_BLOCK, 0, stream, 
                          (Tt*)qkv, row_stride, nh, nkv, hd, R, cosv, sinv, (Tt*)k_pages, (Tt*)v_pages, page_table,
                          table_width, seq_of_token, positions, n_pages, status)));
   return launch_status();
@@ -341,7 +375,7 @@ int wpc_qk_rope_kv_store(void* qkv, int dtype, int row_stride, int T, int nh, in
 
 int wpc_fill_normal(void* out, int dtype, size_t n, uint64_t key, float mean, float std, cudaStream_t stream) {
   if (n == 0) return 0;
-  WPC_DISPATCH_DTYPE(dtype, Tt, (fill_normal_kernel<Tt><<<grid_for(n, 256), 256, 0, stream>>>((Tt*)out, n, key,
+  WPC_DISPATCH_DTYPE(dtype, Tt, (wpc::launch(fill_normal_kernel<Tt>, grid_for(n, 256), 256, 0, stream, (Tt*)out, n, key,
                                                                                              mean, std)));
   return launch_status();
 }

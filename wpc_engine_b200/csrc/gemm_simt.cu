@@ -14,6 +14,8 @@ template <typename Ta, typename Tw, typename To, int MODE>
 __global__ void __launch_bounds__(SG_THREADS)
 gemm_simt_kernel(const Ta* __restrict__ A, int lda, const Tw* __restrict__ W, int ldw,
                  const float* __restrict__ bias, To* __restrict__ C, int ldc, int M, int N, int K) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float As[SG_BK][SG_BM + 4];
   __shared__ float Ws[SG_BK][SG_BN + 4];
   const int tid = threadIdx.x;
@@ -76,13 +78,13 @@ static int launch_simt(const void* A, int lda, const void* W, int ldw, const flo
   dim3 grid((N + SG_BN - 1) / SG_BN, (M + SG_BM - 1) / SG_BM);
   if (accumulate) {
     if (out_dtype != WPC_DTYPE_F32) return WPC_ERR_BAD_ARGUMENT;
-    gemm_simt_kernel<Ta, Tw, float, 1><<<grid, SG_THREADS, 0, stream>>>((const Ta*)A, lda, (const Tw*)W, ldw, bias,
+    wpc::launch(gemm_simt_kernel<Ta, Tw, float, 1>, grid, SG_THREADS, 0, stream, (const Ta*)A, lda, (const Tw*)W, ldw, bias,
                                                                        (float*)C, ldc, M, N, K);
   } else if (out_dtype == WPC_DTYPE_F32) {
-    gemm_simt_kernel<Ta, Tw, float, 0><<<grid, SG_THREADS, 0, stream>>>((const Ta*)A, lda, (const Tw*)W, ldw, bias,
+    wpc::launch(gemm_simt_kernel<Ta, Tw, float, 0>, grid, SG_THREADS, 0, stream, (const Ta*)A, lda, (const Tw*)W, ldw, bias,
                                                                        (float*)C, ldc, M, N, K);
   } else if (out_dtype == WPC_DTYPE_BF16) {
-    gemm_simt_kernel<Ta, Tw, __nv_bfloat16, 0><<<grid, SG_THREADS, 0, stream>>>(
+    wpc::launch(gemm_simt_kernel<Ta, Tw, __nv_bfloat16, 0>, grid, SG_THREADS, 0, stream, 
         (const Ta*)A, lda, (const Tw*)W, ldw, bias, (__nv_bfloat16*)C, ldc, M, N, K);
   } else {
     return WPC_ERR_BAD_ARGUMENT;

@@ -51,11 +51,14 @@ struct Params {
   int ldc;                     // row stride of out, in elements
   int out_bf16;                // 1: bfloat16, 0: float32
   int accumulate;              // 1: out (float32) += result
-  int gated;                   // 1: columns c and c + BN/2 of a tile are gate and up of one feature;
-                               //    out[row, tile * BN/2 + c] = silu(gate) * up, bfloat16 (normal arrangement)
+  int gated;                   // 1: features come as [64 gate | 64 up] blocks; out = silu(gate) * up, bfloat16
   float* scratch;              // split-K partial sums: [tile][split][BN][BM] float32
   int* counters;               // one ticket counter per tile, zero between launches
   int* status;                 // device error word (may be null)
+  int stages;                  // depth of the operand ring (2..MAX_STAGES)
+  int prefetch_weights;        // 1: the weight operand (A when swapped, else B) is never written while the
+                               //    model runs, so its first stages may be fetched before the kernel
+                               //    ahead in the stream has finished
 };
 
 // ---- PTX wrappers -----------------------------------------------------------------------------
@@ -67,6 +70,9 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
                : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
@@ -168,15 +174,24 @@ __host__ __device__ constexpr uint32_t instr_desc(int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 }
 
+
+// Shared memory: 1 KiB of barriers and flags, then (1 KiB aligned) the ring of operand stages.
+// The number of stages is chosen at launch: a CTA that is alone on its SM takes as many as fit,
+// so that enough bytes are in flight to cover the memory latency; two co-resident CTAs share.
+constexpr int MAX_STAGES = 12;
+constexpr int SMEM_LIMIT = 227 * 1024;
 template <int BN>
 struct Smem {
-  static constexpr int STAGES = BN >= 256 ? 4 : (BN >= 128 ? 6 : 6);
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int TILES_BYTES = STAGES * STAGE_BYTES;
-  static constexpr int TOTAL = TILES_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
-  static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+  static constexpr int HEAD_BYTES = 1024;
+  static constexpr int TMEM_COLS = BN <= 32 ? 32 : BN <= 64 ? 64 : BN <= 128 ? 128 : 256;   // a power of two
+  static constexpr int total(int stages) { return HEAD_BYTES + 1024 /* alignment slack */ + stages * STAGE_BYTES; }
+  static constexpr int max_stages(int ctas_per_sm) {
+    int s = (SMEM_LIMIT / ctas_per_sm - HEAD_BYTES - 1024 - 1024 /* per-CTA reserve */) / STAGE_BYTES;
+    return s > MAX_STAGES ? MAX_STAGES : (s < 2 ? 2 : s);
+  }
 };
 
 __device__ __forceinline__ void store_row32(const Params& p, int row, int col0, int n_cols, const float (&v)[32]) {
@@ -222,33 +237,47 @@ template <int BN, bool SWAP>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
   using S = Smem<BN>;
+  pdl_trigger();
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint64_t* full = (uint64_t*)(tiles + S::TILES_BYTES);
-  uint64_t* empty = full + S::STAGES;
-  uint64_t* accum_full = empty + S::STAGES;
-  uint32_t* tmem_holder = (uint32_t*)(accum_full + 1);
+  uint64_t* full = (uint64_t*)smem_raw;
+  uint64_t* empty = full + MAX_STAGES;
+  uint64_t* accum_full = empty + MAX_STAGES;      // [2]: the MMAs of a unit have finished
+  uint64_t* accum_empty = accum_full + 2;         // [2]: the epilogue has read the accumulator
+  uint32_t* tmem_holder = (uint32_t*)(accum_empty + 2);
   int* flags = (int*)(tmem_holder + 1);          // [0]: a wait ran out, [1]: this CTA drew the last ticket
+  uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + S::HEAD_BYTES + 1023) & ~(uintptr_t)1023);
+  const int STAGES = p.stages;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
-  const int split = blockIdx.z;
+  // A unit of work is (tile, K slice).  Units are numbered with the M tile fastest, so CTAs
+  // that run side by side share weight tiles; a CTA takes units blockIdx.x, + gridDim.x, ...
+  // and keeps two accumulators in tensor memory, so that the epilogue of one unit runs while
+  // the MMAs of the next fill the other accumulator.
+  const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
+  const int n_tiles = tiles_m * tiles_n;
+  const int n_units = n_tiles * p.splits;
   const int kb_per = (p.k_blocks + p.splits - 1) / p.splits;
-  const int kb0 = split * kb_per;
-  const int kb1 = min(p.k_blocks, kb0 + kb_per);
-  const int n_kb = max(kb1 - kb0, 0);
+#define WPC_UNIT_COORDS(u)                                              \
+  const int split = (u) / n_tiles, tile_id = (u) - split * n_tiles;     \
+  const int tile_n = tile_id / tiles_m, tile_m = tile_id - tile_n * tiles_m; \
+  const int m0 = tile_m * BM, n0 = tile_n * BN;                         \
+  const int kb0 = split * kb_per;                                       \
+  const int n_kb = max(min(p.k_blocks, kb0 + kb_per) - kb0, 0);
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < S::STAGES; ++s) {
+    for (int s = 0; s < STAGES; ++s) {
       mbar_init(full + s, 1);
       mbar_init(empty + s, 1);
     }
-    mbar_init(accum_full, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(accum_full + b, 1);
+      mbar_init(accum_empty + b, 128);
+    }
     flags[0] = 0;
     flags[1] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 1) tmem_alloc(tmem_holder, S::TMEM_COLS);
+  if (warp == 1) tmem_alloc(tmem_holder, 2 * S::TMEM_COLS);
   fence_before_sync();
   __syncthreads();
   fence_after_sync();
@@ -256,140 +285,222 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   if (warp == 0) {
     if (lane == 0) {
-      for (int i = 0; i < n_kb; ++i) {
-        const int s = i % S::STAGES;
-        const uint32_t ph = (i / S::STAGES) & 1;
-        if (!mbar_wait(empty + s, ph ^ 1)) { atomicExch(flags, 1); break; }
-        mbar_expect_tx(full + s, S::STAGE_BYTES);
-        uint8_t* a_dst = tiles + s * S::STAGE_BYTES;
-        tma_load_2d(a_dst, &map_a, (kb0 + i) * BK, m0, full + s);
-        tma_load_2d(a_dst + S::A_BYTES, &map_b, (kb0 + i) * BK, n0, full + s);
+      int it = 0;                                   // k-blocks loaded so far: position in the ring
+      bool ok = true;
+      for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
+        WPC_UNIT_COORDS(u)
+        int i = 0;
+        if (u == (int)blockIdx.x) {
+          // the first ring of stages: the weight operand may start before the dependency wait
+          const int pre = p.prefetch_weights ? min(n_kb, STAGES) : 0;
+          for (i = 0; i < pre; ++i) {
+            mbar_expect_tx(full + i, S::STAGE_BYTES);
+            uint8_t* a_dst = tiles + i * S::STAGE_BYTES;
+            if (SWAP) tma_load_2d(a_dst, &map_a, (kb0 + i) * BK, m0, full + i);
+            else tma_load_2d(a_dst + S::A_BYTES, &map_b, (kb0 + i) * BK, n0, full + i);
+          }
+          pdl_wait();
+          for (i = 0; i < pre; ++i) {
+            uint8_t* a_dst = tiles + i * S::STAGE_BYTES;
+            if (SWAP) tma_load_2d(a_dst + S::A_BYTES, &map_b, (kb0 + i) * BK, n0, full + i);
+            else tma_load_2d(a_dst, &map_a, (kb0 + i) * BK, m0, full + i);
+          }
+          it = pre;
+        }
+        for (; i < n_kb; ++i, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(empty + s, ph ^ 1)) { atomicExch(flags, 1); ok = false; break; }
+          mbar_expect_tx(full + s, S::STAGE_BYTES);
+          uint8_t* a_dst = tiles + s * S::STAGE_BYTES;
+          tma_load_2d(a_dst, &map_a, (kb0 + i) * BK, m0, full + s);
+          tma_load_2d(a_dst + S::A_BYTES, &map_b, (kb0 + i) * BK, n0, full + s);
+        }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc = instr_desc(BN);
       bool ok = true;
-      for (int i = 0; i < n_kb && ok; ++i) {
-        const int s = i % S::STAGES;
-        const uint32_t ph = (i / S::STAGES) & 1;
-        if (!mbar_wait(full + s, ph)) { atomicExch(flags, 1); ok = false; break; }
+      int it = 0, j = 0;
+      for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x, ++j) {
+        WPC_UNIT_COORDS(u)
+        (void)m0; (void)n0;
+        const int b = j & 1;
+        if (!mbar_wait(accum_empty + b, ((j >> 1) & 1) ^ 1)) { atomicExch(flags, 1); break; }
         fence_after_sync();
-        const uint32_t a_addr = smem_u32(tiles + s * S::STAGE_BYTES);
-        const uint64_t da = smem_desc_sw128(a_addr), db = smem_desc_sw128(a_addr + S::A_BYTES);
+        const uint32_t tmem_d = tmem_base + b * S::TMEM_COLS;
+        for (int i = 0; i < n_kb; ++i, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(full + s, ph)) { atomicExch(flags, 1); ok = false; break; }
+          fence_after_sync();
+          const uint32_t a_addr = smem_u32(tiles + s * S::STAGE_BYTES);
+          const uint64_t da = smem_desc_sw128(a_addr), db = smem_desc_sw128(a_addr + S::A_BYTES);
 #pragma unroll
-        for (int k = 0; k < BK / UMMA_K; ++k) {
-          // 32 bytes further along K inside the swizzled row: + 2 in the (address / 16) field
-          umma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // 32 bytes further along K inside the swizzled row: + 2 in the (address / 16) field
+            umma_bf16(tmem_d, da + 2 * k, db + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(empty + s);       // the stage is free again once these MMAs have read it
         }
-        umma_commit(empty + s);       // the stage is free again once these MMAs have read it
+        umma_commit(accum_full + b);    // arrives when everything issued above has finished
       }
-      umma_commit(accum_full);        // arrives when everything issued above has finished
     }
   } else {
     // ---- epilogue: warps 2..5 read lanes 32*(warp % 4) .. +31 of the accumulator ----
+    pdl_wait();                                         // the output, the scratch and the tickets are shared
     const int q = warp & 3;
     const int r = q * 32 + lane;                        // row of the tile = TMEM lane
     const int et = threadIdx.x - 64;                    // 0..127 among the epilogue threads
-    bool ok = mbar_wait(accum_full, 0);
-    ok = __all_sync(0xffffffffu, ok);              // tcgen05.ld needs the whole warp on one path
-    if (!ok) atomicExch(flags, 1);
-    fence_after_sync();
-    const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
-    const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
-    const int n_valid = min(BN, p.N - n0);              // columns of the tile that exist
-    const bool have_acc = n_kb > 0 && ok;
+    int j = 0;
+    for (int u = blockIdx.x; u < n_units; u += gridDim.x, ++j) {
+      WPC_UNIT_COORDS(u)
+      const int b = j & 1;
+      bool ok = mbar_wait(accum_full + b, (j >> 1) & 1);
+      ok = __all_sync(0xffffffffu, ok);              // tcgen05.ld needs the whole warp on one path
+      if (!ok) atomicExch(flags, 1);
+      fence_after_sync();
+      const uint32_t lane_addr = tmem_base + b * S::TMEM_COLS + ((uint32_t)(q * 32) << 16);
+      const int n_valid = min(BN, p.N - n0);              // columns of the tile that exist
+      const bool have_acc = n_kb > 0 && ok;
 
-    bool run_epilogue = ok;
-    if (p.splits > 1) {
-      // partial sums to scratch: [tile][split][column][row], rows contiguous
-      float* part = p.scratch + ((size_t)tile_id * p.splits + split) * (size_t)(BN * BM);
-      for (int c = 0; c < n_valid; c += 32) {
-        uint32_t v[32];
-        if (have_acc) {
-          if (BN >= 32) tmem_ld32(lane_addr + c, v); else tmem_ld16(lane_addr + c, v);
-          tmem_ld_wait();
-        }
-        const int nc = min(32, n_valid - c);
-        for (int j = 0; j < nc; ++j) part[(size_t)(c + j) * BM + r] = have_acc ? __uint_as_float(v[j]) : 0.f;
-      }
-      __threadfence();
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (et == 0) {
-        const int ticket = atomicAdd(p.counters + tile_id, 1);
-        flags[1] = (ticket == p.splits - 1);
-        if (ticket == p.splits - 1) p.counters[tile_id] = 0;      // ready for the next launch
-      }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      run_epilogue = ok && flags[1];
-      if (run_epilogue) __threadfence();
-    }
-
-    if (!SWAP && BN >= 64 && run_epilogue && p.gated) {
-      // gate in columns [0, BN/2), up in [BN/2, BN) of the tile (wpc-runtime/src/model.rs:527-531)
-      const int row = m0 + r;
-      for (int c = 0; c < BN / 2; c += 32) {
-        uint32_t ug[32], uu[32];
-        float v[32];
-        if (have_acc) {
-          tmem_ld32(lane_addr + c, ug);
-          tmem_ld32(lane_addr + BN / 2 + c, uu);
-          tmem_ld_wait();
-        }
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const float g = have_acc ? __uint_as_float(ug[j]) : 0.f, u = have_acc ? __uint_as_float(uu[j]) : 0.f;
-          v[j] = g / (1.0f + expf(-g)) * u;
-        }
-        if (row < p.M) store_row32(p, row, blockIdx.y * (BN / 2) + c, 32, v);
-      }
-    } else if (run_epilogue) {
-      const float* part0 = p.scratch ? p.scratch + (size_t)tile_id * p.splits * (size_t)(BN * BM) : nullptr;
-      for (int c = 0; c < n_valid; c += 32) {
-        const int nc = min(32, n_valid - c);
-        float v[32];
-        if (p.splits > 1) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = 0.f;
-          for (int z = 0; z < p.splits; ++z) {
-            const float* pz = part0 + (size_t)z * (BN * BM);
-            for (int j = 0; j < nc; ++j) v[j] += __ldcg(pz + (size_t)(c + j) * BM + r);
-          }
-        } else {
-          uint32_t u[32];
+      bool run_epilogue = ok;
+      if (p.splits > 1) {
+        // partial sums to scratch: [tile][split][column][row], rows contiguous
+        float* part = p.scratch + ((size_t)tile_id * p.splits + split) * (size_t)(BN * BM);
+        for (int c = 0; c < n_valid; c += 32) {
+          uint32_t v[32];
           if (have_acc) {
-            if (BN >= 32) tmem_ld32(lane_addr + c, u); else tmem_ld16(lane_addr + c, u);
+            if (BN >= 32) tmem_ld32(lane_addr + c, v); else tmem_ld16(lane_addr + c, v);
             tmem_ld_wait();
           }
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = have_acc ? __uint_as_float(u[j]) : 0.f;
+          const int nc = min(32, n_valid - c);
+          for (int j = 0; j < nc; ++j) part[(size_t)(c + j) * BM + r] = have_acc ? __uint_as_float(v[j]) : 0.f;
         }
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (et == 0) {
+          const int ticket = atomicAdd(p.counters + tile_id, 1);
+          flags[1] = (ticket == p.splits - 1);
+          if (ticket == p.splits - 1) p.counters[tile_id] = 0;      // ready for the next launch
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        run_epilogue = ok && flags[1];
+        if (run_epilogue) __threadfence();
+      }
+
+      if (run_epilogue && p.gated) {
+        // gate and up rows are interleaved in blocks of 64 features (wpc-runtime/src/model.rs:527-531)
         if (!SWAP) {
-          // this thread owns token row m0 + r and features n0 + c ..
+          // columns of the tile: [64 gate | 64 up] repeated; this thread owns token row m0 + r
           const int row = m0 + r;
-          if (p.bias) {
+          for (int c = 0; c < (BN >= 128 ? BN : 0); c += 128) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (j < nc) v[j] += p.bias[n0 + c + j];
+            for (int k = 0; k < 2; ++k) {
+              uint32_t ug[32], uu[32];
+              float v[32];
+              if (have_acc) {
+                tmem_ld32(lane_addr + c + 32 * k, ug);
+                tmem_ld32(lane_addr + c + 64 + 32 * k, uu);
+                tmem_ld_wait();
+              }
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const float g = have_acc ? __uint_as_float(ug[j]) : 0.f, u = have_acc ? __uint_as_float(uu[j]) : 0.f;
+                v[j] = g / (1.0f + expf(-g)) * u;
+              }
+              if (row < p.M) store_row32(p, row, (n0 + c) / 2 + 32 * k, 32, v);
+            }
           }
-          if (row < p.M) store_row32(p, row, n0 + c, nc, v);
         } else {
-          // this thread owns feature m0 + r, the columns are tokens n0 + c ..
-          const int feat = m0 + r;
-          if (feat < p.M) {
-            const float b = p.bias ? p.bias[feat] : 0.f;
-            for (int j = 0; j < nc; ++j) {
-              const size_t o = (size_t)(n0 + c + j) * p.ldc + feat;
-              const float val = v[j] + b;
-              if (p.accumulate) ((float*)p.out)[o] += val;
-              else if (p.out_bf16) ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(val);
-              else ((float*)p.out)[o] = val;
+          // rows of the tile: 64 gate features, then the 64 up rows of the same features; the
+          // upper half hands its values to the lower half through shared memory (the operand
+          // stages are free: every MMA has finished)
+          float* xch = (float*)tiles;                          // [BN][64]
+          for (int c = 0; c < n_valid; c += 32) {
+            uint32_t u32[32];
+            if (have_acc) {
+              if (BN >= 32) tmem_ld32(lane_addr + c, u32); else tmem_ld16(lane_addr + c, u32);
+              tmem_ld_wait();
+            }
+            const int nc = min(32, n_valid - c);
+            if (r >= 64) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (j < nc) xch[(c + j) * 64 + (r - 64)] = have_acc ? __uint_as_float(u32[j]) : 0.f;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (r < 64) {
+              const int feat = (m0 >> 1) + r;
+              if (feat < (p.M >> 1)) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (j < nc) {
+                    const float g = have_acc ? __uint_as_float(u32[j]) : 0.f;
+                    const float u = xch[(c + j) * 64 + r];
+                    ((__nv_bfloat16*)p.out)[(size_t)(n0 + c + j) * p.ldc + feat] =
+                        __float2bfloat16_rn(g / (1.0f + expf(-g)) * u);
+                  }
+              }
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+          }
+        }
+      } else if (run_epilogue) {
+        const float* part0 = p.scratch ? p.scratch + (size_t)tile_id * p.splits * (size_t)(BN * BM) : nullptr;
+        for (int c = 0; c < n_valid; c += 32) {
+          const int nc = min(32, n_valid - c);
+          float v[32];
+          if (p.splits > 1) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = 0.f;
+            for (int z = 0; z < p.splits; ++z) {
+              const float* pz = part0 + (size_t)z * (BN * BM);
+              for (int j = 0; j < nc; ++j) v[j] += __ldcg(pz + (size_t)(c + j) * BM + r);
+            }
+          } else {
+            uint32_t u[32];
+            if (have_acc) {
+              if (BN >= 32) tmem_ld32(lane_addr + c, u); else tmem_ld16(lane_addr + c, u);
+              tmem_ld_wait();
+            }
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = have_acc ? __uint_as_float(u[j]) : 0.f;
+          }
+          if (!SWAP) {
+            // this thread owns token row m0 + r and features n0 + c ..
+            const int row = m0 + r;
+            if (p.bias) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (j < nc) v[j] += p.bias[n0 + c + j];
+            }
+            if (row < p.M) store_row32(p, row, n0 + c, nc, v);
+          } else {
+            // this thread owns feature m0 + r, the columns are tokens n0 + c ..
+            const int feat = m0 + r;
+            if (feat < p.M) {
+              const float b = p.bias ? p.bias[feat] : 0.f;
+              for (int j = 0; j < nc; ++j) {
+                const size_t o = (size_t)(n0 + c + j) * p.ldc + feat;
+                const float val = v[j] + b;
+                if (p.accumulate) ((float*)p.out)[o] += val;
+                else if (p.out_bf16) ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(val);
+                else ((float*)p.out)[o] = val;
+              }
             }
           }
         }
       }
+
+      // the accumulator may be overwritten now
+      fence_before_sync();
+      mbar_arrive(accum_empty + b);
+      if (!ok) break;
     }
   }
+#undef WPC_UNIT_COORDS
 
   fence_before_sync();
   __syncthreads();
@@ -402,7 +513,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   }
   if (warp == 1) {
     fence_after_sync();
-    tmem_dealloc(tmem_base, S::TMEM_COLS);
+    tmem_dealloc(tmem_base, 2 * S::TMEM_COLS);
   }
 }
 
@@ -471,17 +582,28 @@ static int tensor_map(const void* ptr, int rows, int cols, int ld, int box_rows,
 }
 
 template <int BN, bool SWAP>
-static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, cudaStream_t stream) {
+static int launch(const CUtensorMap& ma, const CUtensorMap& mb, Params& p, cudaStream_t stream) {
   using S = Smem<BN>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, SWAP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         S::TOTAL);
+                                         S::total(S::max_stages(1)));
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  dim3 grid((p.M + BM - 1) / BM, (p.N + BN - 1) / BN, p.splits);
-  gemm_tc_kernel<BN, SWAP><<<grid, THREADS, S::TOTAL, stream>>>(ma, mb, p);
+  const long units = (long)((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * p.splits;
+  if (units > 0x7fffffffL) return WPC_ERR_TOO_LARGE;
+  // Many tiles in the normal arrangement: one persistent CTA per SM walks the tiles, its
+  // epilogue overlapping the next tile's MMAs.  Otherwise one CTA per unit; if those are few,
+  // each is alone on its SM and takes a deep ring, if many, two share an SM.
+  const bool persistent = !SWAP && p.splits == 1 && units > 148;
+  const int per_sm = persistent ? 1 : ((units > 148 && S::max_stages(2) >= 4) ? 2 : 1);
+  int stages = S::max_stages(per_sm);
+  const int kb_per = (p.k_blocks + p.splits - 1) / p.splits;
+  if (!persistent && stages > kb_per) stages = kb_per < 2 ? 2 : kb_per;
+  p.stages = stages;
+  dim3 grid(persistent ? 148 : (unsigned)units);
+  wpc::launch(gemm_tc_kernel<BN, SWAP>, grid, THREADS, S::total(stages), stream, ma, mb, p);
   return launch_status();
 }
 
@@ -503,18 +625,22 @@ int wpc_gemm_tc_workspace(int rows_a, int rows_b, int bn, int splits, size_t* sc
 
 // a: [rows_a, K] bfloat16, row stride lda; b: [rows_b, K] bfloat16, row stride ldb.
 // swap = 0: out[rows_a, rows_b] (bias over rows_b);  swap = 1: out[rows_b, rows_a] (bias over
-// rows_a).  bn: the tile's extent along rows_b (16, 32, 64, 128; 256 without swap).
-// gated = 1 (normal arrangement only): b holds gate and up rows interleaved in blocks of bn/2
-// (bn/2 gate rows, then the bn/2 up rows of the same features); out is [rows_a, rows_b / 2]
-// bfloat16 = silu(gate) * up.
+// rows_a).  bn: the tile's extent along rows_b (16, 32, 64, 128; also 160, 192, 224, 256 without swap).
+// gated = 1: the weights hold gate and up rows interleaved in blocks of 64 features (64 gate
+// rows, then the 64 up rows of the same features); out is [tokens, features / 2] bfloat16 =
+// silu(gate) * up.  Needs no split and no bias, and bn >= 128 in the normal arrangement.
+// prefetch_weights = 1 promises that the weights are not written by earlier work still in
+// flight on the stream (model parameters): their first tiles are then fetched before the
+// preceding kernel has finished.
 int wpc_gemm_tc(const void* a, int lda, int rows_a, const void* b, int ldb, int rows_b, int K, const float* bias,
                 void* out, int out_dtype, int ldc, int accumulate, int gated, int swap, int bn, int splits,
                 float* scratch, size_t scratch_floats, int* counters, int n_counters, int* status,
-                cudaStream_t stream) {
+                int prefetch_weights, cudaStream_t stream) {
   if (rows_a <= 0 || rows_b <= 0) return 0;
   if (K <= 0 || (lda % 8) || (ldb % 8) || (((uintptr_t)a) & 15) || (((uintptr_t)b) & 15)) return WPC_ERR_UNSUPPORTED;
   if (accumulate && out_dtype != WPC_DTYPE_F32) return WPC_ERR_BAD_ARGUMENT;
   Params p;
+  p.stages = 2;
   p.M = rows_a; p.N = rows_b; p.K = K;
   p.k_blocks = (K + BK - 1) / BK;
   p.splits = splits < 1 ? 1 : (splits > p.k_blocks ? p.k_blocks : splits);
@@ -522,7 +648,9 @@ int wpc_gemm_tc(const void* a, int lda, int rows_a, const void* b, int ldb, int 
   p.out_bf16 = out_dtype == WPC_DTYPE_BF16; p.accumulate = accumulate;
   p.gated = gated;
   p.scratch = scratch; p.counters = counters; p.status = status;
-  if (gated && (swap || bn < 64 || p.splits != 1 || accumulate || !p.out_bf16 || bias || rows_b % bn))
+  p.prefetch_weights = prefetch_weights;
+  if (gated && (bn < (swap ? 16 : 128) || p.splits != 1 || accumulate || !p.out_bf16 || bias ||
+                (swap ? rows_a % BM : rows_b % 128)))
     return WPC_ERR_UNSUPPORTED;
   if (p.splits > 1) {
     size_t need_f; int need_c;
@@ -538,6 +666,9 @@ int wpc_gemm_tc(const void* a, int lda, int rows_a, const void* b, int ldb, int 
     switch (bn) {
       case 64: return launch<64, false>(ma, mb, p, stream);
       case 128: return launch<128, false>(ma, mb, p, stream);
+      case 160: return launch<160, false>(ma, mb, p, stream);
+      case 192: return launch<192, false>(ma, mb, p, stream);
+      case 224: return launch<224, false>(ma, mb, p, stream);
       case 256: return launch<256, false>(ma, mb, p, stream);
     }
   } else {
@@ -634,6 +765,7 @@ extern "C" int wpc_linear_few_tokens_static(const void* x, int ldx, int tokens, 
   if (e != cudaSuccess) return (int)e;
 
   Params p;
+  p.stages = 2;
   p.M = features; p.N = tokens; p.K = K;
   p.k_blocks = k_blocks;
   p.splits = splits;
@@ -641,6 +773,7 @@ extern "C" int wpc_linear_few_tokens_static(const void* x, int ldx, int tokens, 
   p.out_bf16 = out_dtype == WPC_DTYPE_BF16; p.accumulate = 0;
   p.gated = 0;
   p.scratch = scratch; p.counters = counters; p.status = status;
+  p.prefetch_weights = 0;
   CUtensorMap ma, mb;
   rc = tensor_map_uncached(w, features, K, ldw, BM, &ma);
   if (rc) return rc;

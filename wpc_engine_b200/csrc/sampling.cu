@@ -22,6 +22,8 @@ __global__ void __launch_bounds__(SP_THREADS)
 sample_kernel(const float* __restrict__ logits, int V, const int* __restrict__ slots,
               long long* __restrict__ seq_state, float temperature, const int* __restrict__ banned,
               int n_banned, int* __restrict__ out) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float red[32];
   __shared__ float s_val[SP_THREADS];
   __shared__ int s_idx[SP_THREADS];
@@ -118,7 +120,7 @@ extern "C" int wpc_sample(const float* logits, int n_rows, int V, const int* slo
                           float temperature, const int* banned, int n_banned, int* out, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (V <= 0) return WPC_ERR_BAD_ARGUMENT;
-  wpc::sample_kernel<<<n_rows, wpc::SP_THREADS, 0, stream>>>(logits, V, slots, seq_state, temperature, banned,
+  wpc::launch(wpc::sample_kernel, n_rows, wpc::SP_THREADS, 0, stream, logits, V, slots, seq_state, temperature, banned,
                                                             n_banned, out);
   return wpc::launch_status();
 }

@@ -86,6 +86,9 @@ class Engine:
         self._graphs: Dict[tuple, object] = {}
         self.vocab_size = model.embedding.vocab_size
         self.max_positions = getattr(model.config, "max_position_embeddings", None)
+        if self.device.type == "cuda":
+            # parameters are final from here on: kernels may fetch them ahead of their turn
+            torch.cuda.synchronize(self.device)
         self.steps_run = 0
         self.graph_launches = 0      # kernels that graph replays have launched so far
 

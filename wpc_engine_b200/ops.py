@@ -45,6 +45,11 @@ def library():
     return _lib
 
 
+def set_pdl(on: bool) -> bool:
+    """Programmatic dependent launch for all kernels, on by default; returns the old setting."""
+    return bool(library().wpc_set_pdl(int(bool(on))))
+
+
 def require_device(device="cuda") -> None:
     """Raises unless `device` is a CUDA device and the kernel library loads."""
     dev = torch.device(device)
@@ -117,13 +122,15 @@ def rmsnorm(x: torch.Tensor, gain: torch.Tensor, eps: float, out_dtype: torch.dt
 
 def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
            out_dtype: Optional[torch.dtype] = None, residual: Optional[torch.Tensor] = None,
-           plain: bool = False) -> torch.Tensor:
+           plain: bool = False, static_weight: bool = False) -> torch.Tensor:
     """x [T, K] times w [N, K] transposed, plus bias (float32 [N]).  With `residual` (float32
     [T, N], contiguous) the result is added to it in place in float32 and it is returned.
 
     bfloat16 x and w go to the tensor-core kernel (csrc/gemm_tc.cu) when their layout allows
     TMA (16-byte aligned rows); everything else, and everything with `plain`, runs on the
-    CUDA cores in float32 (csrc/gemm_simt.cu)."""
+    CUDA cores in float32 (csrc/gemm_simt.cu).  `static_weight` promises that w is a model
+    parameter that no earlier work still in flight writes; the tensor-core kernel then fetches
+    its first tiles while the kernel before it is still finishing."""
     _rows(x, "x")
     _rows(w, "w")
     M, K = x.shape
@@ -140,7 +147,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
         accumulate = 0
     if M == 0:
         return out
-    if not plain and _tensor_core_linear(x, w, bias, out, accumulate):
+    if not plain and _tensor_core_linear(x, w, bias, out, accumulate, static_weight):
         return out
     _check("gemm_simt", library().wpc_gemm_simt(
         _p(x), _code(x.dtype), x.stride(0), _p(w), _code(w.dtype), w.stride(0), _p(bias), _p(out),
@@ -188,8 +195,10 @@ def plan_tensor_core_linear(M: int, N: int, K: int):
         swap, bn = True, (16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128)
         tiles = (N + 127) // 128
     else:
-        swap, bn = False, (256 if N >= 256 else 128 if N > 64 else 64)
-        tiles = ((M + 127) // 128) * ((N + bn - 1) // bn)
+        swap = False
+        m_tiles = (M + 127) // 128
+        bn = 256 if N >= 256 else 128 if N > 64 else 64
+        tiles = m_tiles * ((N + bn - 1) // bn)
     splits = 1
     if tiles * 2 <= _SMS:
         splits = max(1, min(_SMS // tiles, k_blocks // 4, 16))
@@ -200,7 +209,7 @@ def plan_tensor_core_linear(M: int, N: int, K: int):
     return swap, bn, splits
 
 
-def _tensor_core_linear(x, w, bias, out, accumulate) -> bool:
+def _tensor_core_linear(x, w, bias, out, accumulate, static_weight=False) -> bool:
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         return False
     M, K = x.shape
@@ -216,7 +225,7 @@ def _tensor_core_linear(x, w, bias, out, accumulate) -> bool:
     _check("gemm_tc", library().wpc_gemm_tc(
         _p(a), a.stride(0), a.shape[0], _p(b), b.stride(0), b.shape[0], K, _p(bias), _p(out), _code(out.dtype),
         out.stride(0), accumulate, 0, int(swap), bn, splits, _p(scratch), ctypes.c_size_t(scratch.numel()),
-        _p(counters), counters.numel(), _p(status), _stream()))
+        _p(counters), counters.numel(), _p(status), int(static_weight), _stream()))
     return True
 
 
@@ -231,29 +240,33 @@ def silu_mul(gu: torch.Tensor, inner: int, group: Optional[int] = None) -> torch
     return out
 
 
-GATED_GROUP = 128     # gate/up interleave that lets the tensor-core product apply silu(gate) * up itself
+GATED_GROUP = 64      # gate/up interleave that lets the tensor-core product apply silu(gate) * up itself
 
 
-def gated_linear(x: torch.Tensor, w: torch.Tensor, inner: int, group: int, plain: bool = False) -> torch.Tensor:
+def gated_linear(x: torch.Tensor, w: torch.Tensor, inner: int, group: int, plain: bool = False,
+                 static_weight: bool = False) -> torch.Tensor:
     """silu(x Wg^T) * (x Wu^T) as [T, inner], where w [2*inner, K] holds the rows of Wg and Wu
-    interleaved in blocks of `group`.  With bfloat16, group 128 and more than 128 tokens the
-    tensor-core product applies the activation in its epilogue and the [T, 2*inner]
-    intermediate never reaches memory; otherwise a product and `silu_mul` follow one another."""
+    interleaved in blocks of `group`.  With bfloat16 and group 64 the tensor-core product
+    applies the activation in its epilogue and the [T, 2*inner] intermediate never reaches
+    memory; otherwise a product and `silu_mul` follow one another."""
     _rows(x, "x")
     _rows(w, "w")
     M, K = x.shape
     _need(w.shape == (2 * inner, K), "w must be [2*inner, K]")
-    if (not plain and group == GATED_GROUP and M > 128 and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+    if (not plain and group == GATED_GROUP and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
             and K % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
-            and w.data_ptr() % 16 == 0):
+            and w.data_ptr() % 16 == 0 and M > 0):
+        swap = M <= 128
+        bn = (16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128) if swap else (256 if (2 * inner) % 256 == 0 else 128)
         out = torch.empty((M, inner), dtype=torch.bfloat16, device=x.device)
         scratch, counters, status = workspace(x.device)
+        a, b = (w, x) if swap else (x, w)
         _check("gemm_tc", library().wpc_gemm_tc(
-            _p(x), x.stride(0), M, _p(w), w.stride(0), 2 * inner, K, _p(None), _p(out), _BF16, out.stride(0), 0, 1,
-            0, 2 * GATED_GROUP, 1, _p(scratch), ctypes.c_size_t(scratch.numel()), _p(counters), counters.numel(),
-            _p(status), _stream()))
+            _p(a), a.stride(0), a.shape[0], _p(b), b.stride(0), b.shape[0], K, _p(None), _p(out), _BF16,
+            out.stride(0), 0, 1, int(swap), bn, 1, _p(scratch), ctypes.c_size_t(scratch.numel()), _p(counters),
+            counters.numel(), _p(status), int(static_weight), _stream()))
         return out
-    return silu_mul(linear(x, w, plain=plain), inner, group)
+    return silu_mul(linear(x, w, plain=plain, static_weight=static_weight), inner, group)
 
 
 def add_(x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
@@ -344,13 +357,14 @@ def attention(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, k_p
         if splits is None:
             splits = plan_decode_splits(B, n_kv_heads, max_ctx_len, window)
         part_o = part_ml = None
+        _, counters, _ = workspace(q.device)
         if splits > 1:
             part_o = torch.empty((B * n_heads * splits * head_dim,), dtype=torch.float32, device=q.device)
             part_ml = torch.empty((B * n_heads * splits * 2,), dtype=torch.float32, device=q.device)
         _check("attention_decode", library().wpc_attention_decode(
             _p(q), q.stride(0), _p(out), out.stride(0), _p(k_pages), _p(v_pages), _p(page_table),
             page_table.shape[1], _p(ctx_lens), B, n_heads, n_kv_heads, head_dim, ctypes.c_float(scale),
-            int(window or 0), splits, _p(part_o), _p(part_ml), _stream()))
+            int(window or 0), splits, _p(part_o), _p(part_ml), _p(counters), counters.numel(), _stream()))
     else:
         _check("attention_prefill", library().wpc_attention_prefill(
             _p(q), q.stride(0), _p(out), out.stride(0), _p(k_pages), _p(v_pages), _p(page_table),

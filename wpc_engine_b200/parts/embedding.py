@@ -48,4 +48,4 @@ class OutputHead(Part):
 
     def forward(self, ctx, h: torch.Tensor) -> torch.Tensor:
         table = self.tied_to.table if self.tied_to is not None else self.table
-        return ops.linear(h, table, None, out_dtype=torch.float32)
+        return ops.linear(h, table, None, out_dtype=torch.float32, static_weight=True)

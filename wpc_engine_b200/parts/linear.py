@@ -33,7 +33,7 @@ class Linear(Part):
                 residual: Optional[torch.Tensor] = None) -> torch.Tensor:
         """With `residual` (float32 [T, out]) the product is added to it in place, in float32,
         and `residual` is returned; else a new [T, out] tensor of `out_dtype` (default x's)."""
-        return ops.linear(x, self.weight, self.bias, out_dtype=out_dtype, residual=residual)
+        return ops.linear(x, self.weight, self.bias, out_dtype=out_dtype, residual=residual, static_weight=True)
 
 
 def fuse_rows(parts):

@@ -16,7 +16,7 @@ class SwiGLU(FeedForward):
     After loading, the gate and up matrices become one [2*inner, width] matrix so that one
     product reads h once.  Their rows are interleaved in blocks of `group` features (`group`
     gate rows, then the `group` up rows of the same features): with 16-bit weights and an
-    inner size that 128 divides the group is 128, which lets the product's epilogue apply the
+    inner size that 64 divides the group is 64, which lets the product's epilogue apply the
     activation; otherwise the group is the whole inner size (all gates, then all ups).  Each
     output is still the same dot product of the same row: a pure re-layout.
     """
@@ -45,6 +45,6 @@ class SwiGLU(FeedForward):
         self.gate_proj.weight, self.up_proj.weight = view[:, 0], view[:, 1]     # [blocks, group, width] views
 
     def forward(self, ctx, h: torch.Tensor, residual: torch.Tensor):
-        act = ops.gated_linear(h, self.gate_up.weight, self.inner, self.group)
+        act = ops.gated_linear(h, self.gate_up.weight, self.inner, self.group, static_weight=True)
         self.down_proj.forward(act, residual=residual)
         return None
