@@ -34,6 +34,7 @@ int wpc_fill_normal(void* out, int dtype, size_t n, uint64_t key, float mean, fl
 int wpc_gemm_simt(const void* A, int a_dtype, int lda, const void* W, int w_dtype, int ldw, const float* bias,
                   void* C, int out_dtype, int ldc, int accumulate, int M, int N, int K, cudaStream_t stream);
 
+int wpc_gemm_tc_set_stage_limit(int limit);
 int wpc_gemm_tc_workspace(int rows_a, int rows_b, int bn, int splits, size_t* scratch_floats, int* n_counters);
 int wpc_gemm_tc(const void* a, int lda, int rows_a, const void* b, int ldb, int rows_b, int K, const float* bias,
                 void* out, int out_dtype, int ldc, int accumulate, int gated, int swap, int bn, int splits,

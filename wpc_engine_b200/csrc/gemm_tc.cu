@@ -20,7 +20,8 @@
 // With split-K every CTA of a tile writes its partial sums to scratch memory and takes a
 // ticket; the CTA that draws the last ticket adds the partial sums in slice order (so the
 // result does not depend on which CTA came last) and runs the epilogue.  Nobody waits for
-// anybody.  Every wait on an mbarrier is bounded: when it runs out the kernel records
+// anybody.  When the product is added to a float32 output anyway, the slices skip all that
+// and add their shares with red.global.add.  Every wait on an mbarrier is bounded: when it runs out the kernel records
 // WPC_ERR_DEVICE_WAIT in `status`, lets its copies land, frees its tensor memory and returns.
 //
 // The math is the reference's y = W x + b (wpc-runtime/src/weights.rs:59-78) in bfloat16
@@ -198,15 +199,24 @@ __device__ __forceinline__ void store_row32(const Params& p, int row, int col0, 
   // out[row, col0 .. col0 + n_cols) from v (normal arrangement: this thread owns a row)
   if (p.accumulate) {
     float* dst = (float*)p.out + (size_t)row * p.ldc + col0;
+    // all loads first, then all stores: a store between two loads would serialise them
     if (n_cols == 32 && (((uintptr_t)dst) & 15) == 0) {
+      float4 o[8];
 #pragma unroll
-      for (int j = 0; j < 32; j += 4) {
-        float4 o = *(float4*)(dst + j);
-        o.x += v[j]; o.y += v[j + 1]; o.z += v[j + 2]; o.w += v[j + 3];
-        *(float4*)(dst + j) = o;
+      for (int j = 0; j < 8; ++j) o[j] = __ldcg((const float4*)(dst + 4 * j));
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        o[j].x += v[4 * j]; o[j].y += v[4 * j + 1]; o[j].z += v[4 * j + 2]; o[j].w += v[4 * j + 3];
+        *(float4*)(dst + 4 * j) = o[j];
       }
     } else {
-      for (int j = 0; j < n_cols; ++j) dst[j] += v[j];
+      float o[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < n_cols) o[j] = __ldcg(dst + j);
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < n_cols) dst[j] = o[j] + v[j];
     }
   } else if (p.out_bf16) {
     __nv_bfloat16* dst = (__nv_bfloat16*)p.out + (size_t)row * p.ldc + col0;
@@ -220,7 +230,9 @@ __device__ __forceinline__ void store_row32(const Params& p, int row, int col0, 
         *(uint4*)(dst + j) = o;
       }
     } else {
-      for (int j = 0; j < n_cols; ++j) dst[j] = __float2bfloat16_rn(v[j]);
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < n_cols) dst[j] = __float2bfloat16_rn(v[j]);
     }
   } else {
     float* dst = (float*)p.out + (size_t)row * p.ldc + col0;
@@ -228,13 +240,15 @@ __device__ __forceinline__ void store_row32(const Params& p, int row, int col0, 
 #pragma unroll
       for (int j = 0; j < 32; j += 4) *(float4*)(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
     } else {
-      for (int j = 0; j < n_cols; ++j) dst[j] = v[j];
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < n_cols) dst[j] = v[j];
     }
   }
 }
 
 template <int BN, bool SWAP>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(THREADS, (BN <= 64 ? 2 : 1))     // narrow tiles run two CTAs to an SM
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
   using S = Smem<BN>;
   pdl_trigger();
@@ -366,7 +380,35 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const bool have_acc = n_kb > 0 && ok;
 
       bool run_epilogue = ok;
-      if (p.splits > 1) {
+      if (p.splits > 1 && p.accumulate) {
+        // Every slice adds its share straight into the float32 output with red.global.add: no
+        // scratch, no tickets, no fences.  The order in which the slices arrive is not fixed,
+        // so the sum may differ in its last bits from run to run.
+        run_epilogue = false;
+        for (int c = 0; c < n_valid && have_acc; c += 32) {
+          uint32_t v[32];
+          if (BN >= 32) tmem_ld32(lane_addr + c, v); else tmem_ld16(lane_addr + c, v);
+          tmem_ld_wait();
+          const int nc = min(32, n_valid - c);
+          if (!SWAP) {
+            const int row = m0 + r;
+            if (row < p.M) {
+              float* dst = (float*)p.out + (size_t)row * p.ldc + n0 + c;
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (j < nc) atomicAdd(dst + j, __uint_as_float(v[j]) + ((p.bias && split == 0) ? p.bias[n0 + c + j] : 0.f));
+            }
+          } else {
+            const int feat = m0 + r;
+            if (feat < p.M) {
+              const float bsum = (p.bias && split == 0) ? p.bias[feat] : 0.f;
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (j < nc) atomicAdd((float*)p.out + (size_t)(n0 + c + j) * p.ldc + feat, __uint_as_float(v[j]) + bsum);
+            }
+          }
+        }
+      } else if (p.splits > 1) {
         // partial sums to scratch: [tile][split][column][row], rows contiguous
         float* part = p.scratch + ((size_t)tile_id * p.splits + split) * (size_t)(BN * BM);
         for (int c = 0; c < n_valid; c += 32) {
@@ -376,7 +418,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             tmem_ld_wait();
           }
           const int nc = min(32, n_valid - c);
-          for (int j = 0; j < nc; ++j) part[(size_t)(c + j) * BM + r] = have_acc ? __uint_as_float(v[j]) : 0.f;
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (j < nc) part[(size_t)(c + j) * BM + r] = have_acc ? __uint_as_float(v[j]) : 0.f;
         }
         __threadfence();
         asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -457,7 +501,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for (int j = 0; j < 32; ++j) v[j] = 0.f;
             for (int z = 0; z < p.splits; ++z) {
               const float* pz = part0 + (size_t)z * (BN * BM);
-              for (int j = 0; j < nc; ++j) v[j] += __ldcg(pz + (size_t)(c + j) * BM + r);
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (j < nc) v[j] += __ldcg(pz + (size_t)(c + j) * BM + r);
             }
           } else {
             uint32_t u[32];
@@ -482,12 +528,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const int feat = m0 + r;
             if (feat < p.M) {
               const float b = p.bias ? p.bias[feat] : 0.f;
-              for (int j = 0; j < nc; ++j) {
-                const size_t o = (size_t)(n0 + c + j) * p.ldc + feat;
-                const float val = v[j] + b;
-                if (p.accumulate) ((float*)p.out)[o] += val;
-                else if (p.out_bf16) ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(val);
-                else ((float*)p.out)[o] = val;
+              if (p.accumulate) {
+                // all loads first, then all stores: a store between two loads would serialise them
+                float old[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (j < nc) old[j] = __ldcg((const float*)p.out + (size_t)(n0 + c + j) * p.ldc + feat);
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (j < nc) ((float*)p.out)[(size_t)(n0 + c + j) * p.ldc + feat] = old[j] + v[j] + b;
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                  if (j < nc) {
+                    const size_t o = (size_t)(n0 + c + j) * p.ldc + feat;
+                    const float val = v[j] + b;
+                    if (p.out_bf16) ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(val);
+                    else ((float*)p.out)[o] = val;
+                  }
+                }
               }
             }
           }
@@ -581,6 +640,9 @@ static int tensor_map(const void* ptr, int rows, int cols, int ld, int box_rows,
   return 0;
 }
 
+// Upper limit of the ring depth (a tuning knob; MAX_STAGES by default).
+static int g_stage_limit = MAX_STAGES;
+
 template <int BN, bool SWAP>
 static int launch(const CUtensorMap& ma, const CUtensorMap& mb, Params& p, cudaStream_t stream) {
   using S = Smem<BN>;
@@ -601,6 +663,7 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, Params& p, cudaS
   int stages = S::max_stages(per_sm);
   const int kb_per = (p.k_blocks + p.splits - 1) / p.splits;
   if (!persistent && stages > kb_per) stages = kb_per < 2 ? 2 : kb_per;
+  if (stages > g_stage_limit) stages = g_stage_limit < 2 ? 2 : g_stage_limit;
   p.stages = stages;
   dim3 grid(persistent ? 148 : (unsigned)units);
   wpc::launch(gemm_tc_kernel<BN, SWAP>, grid, THREADS, S::total(stages), stream, ma, mb, p);
@@ -614,6 +677,13 @@ using namespace wpc;
 using namespace wpc::tc;
 
 extern "C" {
+
+// Limits the depth of the operand ring (2..12); returns the old limit.
+int wpc_gemm_tc_set_stage_limit(int limit) {
+  const int was = g_stage_limit;
+  g_stage_limit = limit < 2 ? 2 : (limit > MAX_STAGES ? MAX_STAGES : limit);
+  return was;
+}
 
 // How many float32 of scratch and how many counters a call with these sizes needs.
 int wpc_gemm_tc_workspace(int rows_a, int rows_b, int bn, int splits, size_t* scratch_floats, int* n_counters) {
@@ -652,7 +722,7 @@ int wpc_gemm_tc(const void* a, int lda, int rows_a, const void* b, int ldb, int 
   if (gated && (bn < (swap ? 16 : 128) || p.splits != 1 || accumulate || !p.out_bf16 || bias ||
                 (swap ? rows_a % BM : rows_b % 128)))
     return WPC_ERR_UNSUPPORTED;
-  if (p.splits > 1) {
+  if (p.splits > 1 && !accumulate) {
     size_t need_f; int need_c;
     wpc_gemm_tc_workspace(rows_a, rows_b, bn, p.splits, &need_f, &need_c);
     if (!scratch || !counters || need_f > scratch_floats || need_c > n_counters) return WPC_ERR_TOO_LARGE;
