@@ -5,11 +5,11 @@
 // The query heads that share a KV head are stacked along the MMA's row dimension, so a page
 // of keys and values is read once for the whole group.
 //
-//   decode   one query token per sequence.  grid = (splits, kv heads, sequences); the 16 MMA
-//            rows hold the group's query heads; the four warps of a CTA take the four
-//            16-key quarters of each 64-key page and are merged at the end; a sequence's
-//            pages are divided over `splits` CTAs whose partial results (unnormalised
-//            output, running maximum, running sum) the last of them to finish combines.
+//   decode   one query token per sequence.  A fixed grid of CTAs shares all (sequence, kv
+//            head, page) work evenly; the 16 MMA rows hold the group's query heads; the four
+//            warps of a CTA take the four 16-key quarters of each 64-key page and are merged
+//            at the end; partial results of a pair that spans CTAs are combined by the last
+//            of them to finish.
 //   prefill  any number of new tokens per sequence.  grid = (row tiles, kv heads,
 //            sequences); a tile is 64 rows of (token, head-in-group), 16 per warp; every warp
 //            walks the pages up to the tile's last visible key.
@@ -179,193 +179,252 @@ __device__ __forceinline__ void load_q(uint32_t (&qf)[HD / 16][4], const __nv_bf
 }
 
 // ---- decode -------------------------------------------------------------------------------------
-// part_o: [T, nh, splits, HD] float32 (unnormalised), part_ml: [T, nh, splits, 2] (max, sum)
+// The work of a decode step is the list of (sequence, kv head, page) triples that the queries
+// see, in that order.  A fixed grid of CTAs divides the list evenly, so that every SM streams
+// about the same number of pages whatever the sequences' lengths are.  A CTA walks its share
+// as segments of one (sequence, kv head) pair each.  A pair that lies inside one CTA is
+// finished there; a pair that spans several CTAs gets one partial result (unnormalised output,
+// running maximum, running sum) from each, and the CTA that draws the pair's last ticket
+// combines them in CTA order, so the result does not depend on who came last.  Nobody waits.
+//
+// part_o: [(CTAs + pairs), 16, HD] float32; part_ml: [(CTAs + pairs), 16, 2]; the partial of CTA
+// c for pair k lives at slot c + k (consecutive pairs share at most one CTA, so slots are unique).
+constexpr int MAX_DECODE_SEQS = 1024;
+constexpr int DECODE_STAGES = 3;
+
 template <int HD>
 __global__ void __launch_bounds__(THREADS)
 decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* __restrict__ out, int out_stride,
               const __nv_bfloat16* __restrict__ k_pages, const __nv_bfloat16* __restrict__ v_pages,
-              const int* __restrict__ page_table, int table_width, const int* __restrict__ ctx_lens,
-              int nh, int nkv, float scale_log2, int window, int splits, float* __restrict__ part_o,
+              const int* __restrict__ page_table, int table_width, const int* __restrict__ ctx_lens, int B,
+              int nh, int nkv, float scale_log2, int window, float* __restrict__ part_o,
               float* __restrict__ part_ml, int* __restrict__ counters) {
   pdl_trigger();
   pdl_wait();
   extern __shared__ __align__(16) uint8_t smem_raw[];
-  __nv_bfloat16* ks = (__nv_bfloat16*)smem_raw;                       // [2][PAGE][STRIDE]
-  __nv_bfloat16* vs = ks + 2 * Cfg<HD>::PAGE_ELEMS;
-  const int split = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
+  __nv_bfloat16* ks = (__nv_bfloat16*)smem_raw;                       // [DECODE_STAGES][PAGE][STRIDE]
+  __nv_bfloat16* vs = ks + DECODE_STAGES * Cfg<HD>::PAGE_ELEMS;
+  __shared__ int s_cum[MAX_DECODE_SEQS + 1];                          // units before each sequence
+  __shared__ int s_last;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_rep = nh / nkv;
-  const int L = ctx_lens[b];
-  const int pos = L - 1;
-  const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-  const int first_block = lo / PAGE, last_block = pos / PAGE;
-  const int n_blocks = last_block - first_block + 1;
-  const int per = (n_blocks + splits - 1) / splits;
-  const int blk0 = first_block + split * per;
-  const int blk1 = min(last_block + 1, blk0 + per);
-  const int* table = page_table + (size_t)b * table_width;
   const size_t page_elems = (size_t)nkv * PAGE * HD;
 
-  const int r_lo = lane >> 2, r_hi = r_lo + 8;                        // rows = heads of the group
-  const __nv_bfloat16* qtok = q + (size_t)b * q_stride + (size_t)g * n_rep * HD;
-  uint32_t qf[HD / 16][4];
-  load_q<HD>(qf, r_lo < n_rep ? qtok + r_lo * HD : nullptr, r_hi < n_rep ? qtok + r_hi * HD : nullptr, lane);
-
-  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-  float o[HD / 8][4];
-#pragma unroll
-  for (int d = 0; d < HD / 8; ++d)
-#pragma unroll
-    for (int i = 0; i < 4; ++i) o[d][i] = 0.f;
-
-  if (blk0 < blk1) {
-    const size_t src0 = (size_t)max(table[blk0], 0) * page_elems + (size_t)g * PAGE * HD;
-    load_page<HD>(ks, k_pages + src0, tid);
-    load_page<HD>(vs, v_pages + src0, tid);
+  // ---- units of each sequence, and their running sum ----
+  for (int b = tid; b < B; b += THREADS) {
+    const int pos = ctx_lens[b] - 1;
+    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    s_cum[b + 1] = pos >= 0 ? (pos / PAGE - lo / PAGE + 1) * nkv : 0;
   }
-  cp_async_commit();
-  for (int blk = blk0; blk < blk1; ++blk) {
-    const int buf = (blk - blk0) & 1;
-    if (blk + 1 < blk1) {
-      const size_t src = (size_t)max(table[blk + 1], 0) * page_elems + (size_t)g * PAGE * HD;
-      load_page<HD>(ks + (buf ^ 1) * Cfg<HD>::PAGE_ELEMS, k_pages + src, tid);
-      load_page<HD>(vs + (buf ^ 1) * Cfg<HD>::PAGE_ELEMS, v_pages + src, tid);
-    }
-    cp_async_commit();
-    cp_async_wait<1>();
-    __syncthreads();
-    const int key0 = warp * 16;                                       // this warp's quarter of the page
-    const int abs0 = blk * PAGE + key0;
-    if (abs0 <= pos && abs0 + 15 >= lo) {
-      float s[2][4];
-      scores<HD, 2>(qf, ks + buf * Cfg<HD>::PAGE_ELEMS, key0, s, lane);
-#pragma unroll
-      for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int kabs = abs0 + nt * 8 + (lane & 3) * 2 + (i & 1);
-          s[nt][i] = (kabs >= lo && kabs <= pos) ? s[nt][i] * scale_log2 : -INFINITY;
-        }
-      softmax_step<HD, 2>(s, m, l, o);
-      uint32_t pf[1][4];
-      to_fragments<2>(s, pf);
-      weighted_values<HD, 2>(pf, vs + buf * Cfg<HD>::PAGE_ELEMS, key0, o, lane);
-    }
-    __syncthreads();
-  }
-  cp_async_wait<0>();
+  if (tid == 0) s_cum[0] = 0;
   __syncthreads();
+  if (warp == 0) {
+    // inclusive scan of s_cum[1..B]: each lane a contiguous chunk, then a scan of the chunk sums
+    const int chunk = (B + 31) / 32;
+    const int lo_i = 1 + lane * chunk, hi_i = min(B + 1, lo_i + chunk);
+    int sum = 0;
+    for (int i = lo_i; i < hi_i; ++i) sum += s_cum[i];
+    int incl = sum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += t;
+    }
+    int run = incl - sum;
+    for (int i = lo_i; i < hi_i; ++i) {
+      run += s_cum[i];
+      s_cum[i] = run;
+    }
+  }
+  __syncthreads();
+  const int U = s_cum[B];
+  const int per = (U + (int)gridDim.x - 1) / (int)gridDim.x;
+  const int u0 = blockIdx.x * per, u1 = min(U, u0 + per);
+  if (per == 0 || u0 >= u1) return;
 
-  // ---- merge the four warps (each saw a quarter of every page) through shared memory ----
-  float* so = (float*)smem_raw;                         // [4][16][HD]
+  // the sequence that holds unit u0
+  int b = 0;
+  {
+    int lo_b = 0, hi_b = B;                     // s_cum[lo_b] <= u0 < s_cum[hi_b]
+    while (hi_b - lo_b > 1) {
+      const int mid = (lo_b + hi_b) >> 1;
+      if (s_cum[mid] <= u0) lo_b = mid; else hi_b = mid;
+    }
+    b = lo_b;
+  }
+
+  const int r_lo = lane >> 2, r_hi = r_lo + 8;                        // rows = heads of the group
+  float* so = (float*)smem_raw;                         // merge area [4][16][HD] (after the pages are done)
   float* sm = so + 4 * 16 * HD;                         // [4][16]
   float* sl = sm + 4 * 16;                              // [4][16]
+
+  for (int u = u0; u < u1;) {
+    while (s_cum[b + 1] <= u) ++b;
+    const int nb = (s_cum[b + 1] - s_cum[b]) / nkv;                   // pages that sequence b's query sees
+    const int within = u - s_cum[b];
+    const int g = within / nb, pg = within - g * nb;
+    const int pair_start = s_cum[b] + g * nb, pair_end = pair_start + nb;
+    const int seg_end = min(u1, pair_end);
+    const int L = ctx_lens[b];
+    const int pos = L - 1;
+    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int blk0 = lo / PAGE + pg, blk1 = blk0 + (seg_end - u);
+    const int* table = page_table + (size_t)b * table_width;
+
+    const __nv_bfloat16* qtok = q + (size_t)b * q_stride + (size_t)g * n_rep * HD;
+    uint32_t qf[HD / 16][4];
+    load_q<HD>(qf, r_lo < n_rep ? qtok + r_lo * HD : nullptr, r_hi < n_rep ? qtok + r_hi * HD : nullptr, lane);
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float o[HD / 8][4];
 #pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
-    l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
-  }
+    for (int d = 0; d < HD / 8; ++d)
 #pragma unroll
-  for (int d = 0; d < HD / 8; ++d) {
-    const int c = d * 8 + (lane & 3) * 2;
-    so[(warp * 16 + r_lo) * HD + c] = o[d][0];
-    so[(warp * 16 + r_lo) * HD + c + 1] = o[d][1];
-    so[(warp * 16 + r_hi) * HD + c] = o[d][2];
-    so[(warp * 16 + r_hi) * HD + c + 1] = o[d][3];
-  }
-  if ((lane & 3) == 0) {
-    sm[warp * 16 + r_lo] = m[0];
-    sm[warp * 16 + r_hi] = m[1];
-    sl[warp * 16 + r_lo] = l[0];
-    sl[warp * 16 + r_hi] = l[1];
-  }
-  __syncthreads();
-  for (int e = tid; e < n_rep * HD; e += THREADS) {
-    const int row = e / HD, d = e - row * HD;
-    float M = -INFINITY;
+      for (int i = 0; i < 4; ++i) o[d][i] = 0.f;
+
+    // a ring of DECODE_STAGES pages: two are in flight while one is computed
 #pragma unroll
-    for (int w = 0; w < 4; ++w) M = fmaxf(M, sm[w * 16 + row]);
-    float acc = 0.f, Lsum = 0.f;
-#pragma unroll
-    for (int w = 0; w < 4; ++w) {
-      const float mw = sm[w * 16 + row];
-      const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
-      acc += f * so[(w * 16 + row) * HD + d];
-      Lsum += f * sl[w * 16 + row];
+    for (int i = 0; i < DECODE_STAGES - 1; ++i) {
+      if (blk0 + i < blk1) {
+        const size_t src = (size_t)max(table[blk0 + i], 0) * page_elems + (size_t)g * PAGE * HD;
+        load_page<HD>(ks + i * Cfg<HD>::PAGE_ELEMS, k_pages + src, tid);
+        load_page<HD>(vs + i * Cfg<HD>::PAGE_ELEMS, v_pages + src, tid);
+      }
+      cp_async_commit();
     }
-    const int head = g * n_rep + row;
-    if (splits == 1) {
-      out[(size_t)b * out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(Lsum > 0.f ? acc / Lsum : 0.f);
-    } else {
-      const size_t pi = ((size_t)b * nh + head) * splits + split;
-      part_o[pi * HD + d] = acc;
-      if (d == 0) {
-        part_ml[pi * 2] = M;
-        part_ml[pi * 2 + 1] = Lsum;
+    for (int blk = blk0; blk < blk1; ++blk) {
+      const int buf = (blk - blk0) % DECODE_STAGES;
+      if (blk + DECODE_STAGES - 1 < blk1) {
+        const int nbuf = (buf + DECODE_STAGES - 1) % DECODE_STAGES;
+        const size_t src = (size_t)max(table[blk + DECODE_STAGES - 1], 0) * page_elems + (size_t)g * PAGE * HD;
+        load_page<HD>(ks + nbuf * Cfg<HD>::PAGE_ELEMS, k_pages + src, tid);
+        load_page<HD>(vs + nbuf * Cfg<HD>::PAGE_ELEMS, v_pages + src, tid);
+      }
+      cp_async_commit();
+      cp_async_wait<DECODE_STAGES - 1>();
+      __syncthreads();
+      const int key0 = warp * 16;                                       // this warp's quarter of the page
+      const int abs0 = blk * PAGE + key0;
+      if (abs0 <= pos && abs0 + 15 >= lo) {
+        float s[2][4];
+        scores<HD, 2>(qf, ks + buf * Cfg<HD>::PAGE_ELEMS, key0, s, lane);
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int kabs = abs0 + nt * 8 + (lane & 3) * 2 + (i & 1);
+            s[nt][i] = (kabs >= lo && kabs <= pos) ? s[nt][i] * scale_log2 : -INFINITY;
+          }
+        softmax_step<HD, 2>(s, m, l, o);
+        uint32_t pf[1][4];
+        to_fragments<2>(s, pf);
+        weighted_values<HD, 2>(pf, vs + buf * Cfg<HD>::PAGE_ELEMS, key0, o, lane);
+      }
+      __syncthreads();
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+
+    // ---- merge the four warps (each saw a quarter of every page) through shared memory ----
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+      l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+    }
+#pragma unroll
+    for (int d = 0; d < HD / 8; ++d) {
+      const int c = d * 8 + (lane & 3) * 2;
+      so[(warp * 16 + r_lo) * HD + c] = o[d][0];
+      so[(warp * 16 + r_lo) * HD + c + 1] = o[d][1];
+      so[(warp * 16 + r_hi) * HD + c] = o[d][2];
+      so[(warp * 16 + r_hi) * HD + c + 1] = o[d][3];
+    }
+    if ((lane & 3) == 0) {
+      sm[warp * 16 + r_lo] = m[0];
+      sm[warp * 16 + r_hi] = m[1];
+      sl[warp * 16 + r_lo] = l[0];
+      sl[warp * 16 + r_hi] = l[1];
+    }
+    __syncthreads();
+    const int pair = b * nkv + g;
+    const int c_first = pair_start / per, c_last = (pair_end - 1) / per;
+    const bool whole = c_first == c_last;                 // the pair lies inside this CTA
+    const size_t slot = (size_t)blockIdx.x + pair;
+    for (int e = tid; e < n_rep * HD; e += THREADS) {
+      const int row = e / HD, d = e - row * HD;
+      float M = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) M = fmaxf(M, sm[w * 16 + row]);
+      float acc = 0.f, Lsum = 0.f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float mw = sm[w * 16 + row];
+        const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
+        acc += f * so[(w * 16 + row) * HD + d];
+        Lsum += f * sl[w * 16 + row];
+      }
+      if (whole) {
+        out[(size_t)b * out_stride + (size_t)(g * n_rep + row) * HD + d] =
+            __float2bfloat16_rn(Lsum > 0.f ? acc / Lsum : 0.f);
+      } else {
+        part_o[(slot * 16 + row) * HD + d] = acc;
+        if (d == 0) {
+          part_ml[(slot * 16 + row) * 2] = M;
+          part_ml[(slot * 16 + row) * 2 + 1] = Lsum;
+        }
       }
     }
-  }
-  if (splits == 1 || !counters) return;
-  // The CTA that draws the last ticket of this (sequence, kv head) combines all splits, in
-  // split order, so the result does not depend on which CTA came last.  Nobody waits.
-  __shared__ int s_last;
-  __threadfence();
-  __syncthreads();
-  if (tid == 0) {
-    const int ticket = atomicAdd(counters + b * nkv + g, 1);
-    s_last = ticket == splits - 1;
-    if (s_last) counters[b * nkv + g] = 0;                 // ready for the next launch
-  }
-  __syncthreads();
-  if (!s_last) return;
-  __threadfence();
-  // weights of the splits first (few values, staged in shared memory), then the outputs with
-  // independent loads
-  float* wf = (float*)smem_raw;                          // [n_rep][splits] factor, then [n_rep] 1 / sum
-  float* winv = wf + 16 * splits;
-  for (int row = tid; row < n_rep; row += THREADS) {
-    const size_t base = ((size_t)b * nh + g * n_rep + row) * splits;
-    float M = -INFINITY;
-    for (int s = 0; s < splits; ++s) M = fmaxf(M, __ldcg(part_ml + (base + s) * 2));
-    float Lsum = 0.f;
-    for (int s = 0; s < splits; ++s) {
-      const float ms = __ldcg(part_ml + (base + s) * 2);
-      const float f = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
-      wf[row * splits + s] = f;
-      Lsum += f * __ldcg(part_ml + (base + s) * 2 + 1);
+    if (!whole) {
+      __threadfence();
+      __syncthreads();
+      if (tid == 0) {
+        const int ticket = atomicAdd(counters + pair, 1);
+        s_last = ticket == c_last - c_first;
+        if (s_last) counters[pair] = 0;                    // ready for the next launch
+      }
+      __syncthreads();
+      if (s_last) {
+        __threadfence();
+        // maxima and sums of all partial results into shared memory (all loads at once), then a
+        // warp per row turns them into weights, then the outputs with independent loads
+        const int n_parts = c_last - c_first + 1;
+        float* wm = (float*)smem_raw;                      // [16][n_parts] maximum, then the weight
+        float* wl = wm + 16 * n_parts;                     // [16][n_parts] sum
+        float* winv = wl + 16 * n_parts;                   // [16] 1 / total
+        const size_t slot0 = (size_t)c_first + pair;
+        for (int e = tid; e < n_rep * n_parts; e += THREADS) {
+          const int row = e / n_parts, sidx = e - row * n_parts;
+          const float2 ml = __ldcg((const float2*)(part_ml + ((slot0 + sidx) * 16 + row) * 2));
+          wm[row * n_parts + sidx] = ml.x;
+          wl[row * n_parts + sidx] = ml.y;
+        }
+        __syncthreads();
+        for (int row = warp; row < n_rep; row += THREADS / 32) {
+          float M = -INFINITY;
+          for (int sidx = lane; sidx < n_parts; sidx += 32) M = fmaxf(M, wm[row * n_parts + sidx]);
+          M = warp_max(M);
+          float Lsum = 0.f;
+          for (int sidx = lane; sidx < n_parts; sidx += 32) {
+            const float ms = wm[row * n_parts + sidx];
+            const float f = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
+            wm[row * n_parts + sidx] = f;
+            Lsum += f * wl[row * n_parts + sidx];
+          }
+          Lsum = warp_sum(Lsum);
+          if (lane == 0) winv[row] = Lsum > 0.f ? 1.f / Lsum : 0.f;
+        }
+        __syncthreads();
+        for (int e = tid; e < n_rep * HD; e += THREADS) {
+          const int row = e / HD, d = e - row * HD;
+          const float* po = part_o + (slot0 * 16 + row) * HD + d;
+          float acc = 0.f;
+#pragma unroll 8
+          for (int sidx = 0; sidx < n_parts; ++sidx) acc += wm[row * n_parts + sidx] * __ldcg(po + (size_t)sidx * 16 * HD);
+          out[(size_t)b * out_stride + (size_t)(g * n_rep + row) * HD + d] = __float2bfloat16_rn(acc * winv[row]);
+        }
+      }
     }
-    winv[row] = Lsum > 0.f ? 1.f / Lsum : 0.f;
-  }
-  __syncthreads();
-  for (int e = tid; e < n_rep * HD; e += THREADS) {
-    const int row = e / HD, d = e - row * HD;
-    const int head = g * n_rep + row;
-    const float* po = part_o + ((size_t)b * nh + head) * splits * HD + d;
-    float acc = 0.f;
-#pragma unroll 4
-    for (int s = 0; s < splits; ++s) acc += wf[row * splits + s] * __ldcg(po + (size_t)s * HD);
-    out[(size_t)b * out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(acc * winv[row]);
-  }
-}
-
-template <int HD>
-__global__ void combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                               __nv_bfloat16* __restrict__ out, int out_stride, int nh, int splits) {
-  pdl_trigger();
-  pdl_wait();
-  const int b = blockIdx.x, head = blockIdx.y;
-  const size_t base = ((size_t)b * nh + head) * splits;
-  float M = -INFINITY;
-  for (int s = 0; s < splits; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
-  for (int d = threadIdx.x; d < HD; d += blockDim.x) {
-    float acc = 0.f, Lsum = 0.f;
-    for (int s = 0; s < splits; ++s) {
-      const float ms = part_ml[(base + s) * 2];
-      const float f = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
-      acc += f * part_o[(base + s) * HD + d];
-      Lsum += f * part_ml[(base + s) * 2 + 1];
-    }
-    out[(size_t)b * out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(Lsum > 0.f ? acc / Lsum : 0.f);
+    __syncthreads();                                       // shared memory is reused by the next segment
+    u = seg_end;
   }
 }
 
@@ -491,26 +550,24 @@ prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16*
 template <int HD>
 static int launch_decode(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                          const void* v_pages, const int* page_table, int table_width, const int* ctx_lens, int B,
-                         int nh, int nkv, float scale, int window, int splits, float* part_o, float* part_ml,
-                         int* counters, int n_counters, cudaStream_t stream) {
-  if (B * nkv > n_counters) counters = nullptr;            // too many tickets: combine in a second kernel
+                         int nh, int nkv, float scale, int window, int n_ctas, float* part_o, float* part_ml,
+                         int* counters, cudaStream_t stream) {
+  // shared memory: the page buffers, reused for the merge of the warps and for the combine
   const int merge_bytes = (4 * 16 * HD + 2 * 4 * 16) * (int)sizeof(float);
-  const int smem = Cfg<HD>::SMEM_BYTES > merge_bytes ? Cfg<HD>::SMEM_BYTES : merge_bytes;
-  static bool configured = false;
-  if (!configured) {
+  const int combine_bytes = (2 * 16 * n_ctas + 16) * (int)sizeof(float);
+  int smem = DECODE_STAGES * 2 * Cfg<HD>::PAGE_ELEMS * 2;
+  if (merge_bytes > smem) smem = merge_bytes;
+  if (combine_bytes > smem) smem = combine_bytes;
+  static int configured = 0;
+  if (configured < smem) {
     cudaError_t e = cudaFuncSetAttribute(decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    configured = smem;
   }
-  dim3 grid(splits, nkv, B);
-  wpc::launch(decode_kernel<HD>, grid, THREADS, smem, stream, 
+  wpc::launch(decode_kernel<HD>, dim3(n_ctas), THREADS, smem, stream, 
       (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pages,
-      (const __nv_bfloat16*)v_pages, page_table, table_width, ctx_lens, nh, nkv, scale * LOG2E, window, splits,
+      (const __nv_bfloat16*)v_pages, page_table, table_width, ctx_lens, B, nh, nkv, scale * LOG2E, window,
       part_o, part_ml, counters);
-  int rc = launch_status();
-  if (rc || splits == 1 || counters) return rc;
-  wpc::launch(combine_kernel<HD>, dim3(B, nh), HD < 32 ? 32 : HD, 0, stream, part_o, part_ml, (__nv_bfloat16*)out, out_stride,
-                                                                   nh, splits);
   return launch_status();
 }
 
@@ -559,20 +616,22 @@ int wpc_attention_mma_supports(int nh, int nkv, int hd) {
   return hd >= 16 && hd <= 128 && hd % 16 == 0 && nkv >= 1 && nh % nkv == 0 && nh / nkv <= 16;
 }
 
-// One query token per sequence: q row b belongs to sequence b.  part_o: float32
-// [B * nh * splits * hd], part_ml: float32 [B * nh * splits * 2]; unused when splits == 1.
-// counters: B * nkv tickets, zero between launches (null or too few: a second kernel combines).
+// One query token per sequence: q row b belongs to sequence b (at most 1024 sequences).
+// n_ctas CTAs share the pages of all sequences evenly (1..1024).  part_o: float32
+// [(n_ctas + B * nkv) * 16 * hd], part_ml: float32 [(n_ctas + B * nkv) * 16 * 2], counters:
+// B * nkv tickets that are zero between launches.
 int wpc_attention_decode(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                          const void* v_pages, const int* page_table, int table_width, const int* ctx_lens, int B,
-                         int nh, int nkv, int hd, float scale, int window, int splits, float* part_o,
+                         int nh, int nkv, int hd, float scale, int window, int n_ctas, float* part_o,
                          float* part_ml, int* counters, int n_counters, cudaStream_t stream) {
   if (B <= 0) return 0;
-  if (!wpc_attention_mma_supports(nh, nkv, hd) || splits < 1 || splits > 64 || (q_stride % 2) || (out_stride % 2))
+  if (!wpc_attention_mma_supports(nh, nkv, hd) || (q_stride % 2) || (out_stride % 2) || B > fa::MAX_DECODE_SEQS)
     return WPC_ERR_UNSUPPORTED;
-  if (splits > 1 && (!part_o || !part_ml)) return WPC_ERR_BAD_ARGUMENT;
+  if (n_ctas < 1 || n_ctas > 1024 || !part_o || !part_ml || !counters || B * nkv > n_counters)
+    return WPC_ERR_BAD_ARGUMENT;
   WPC_DISPATCH_HD(hd, fa::launch_decode<HD>(q, q_stride, out, out_stride, k_pages, v_pages, page_table, table_width,
-                                           ctx_lens, B, nh, nkv, scale, window, splits, part_o, part_ml, counters,
-                                           n_counters, stream));
+                                           ctx_lens, B, nh, nkv, scale, window, n_ctas, part_o, part_ml, counters,
+                                           stream));
 }
 
 int wpc_attention_prefill(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,

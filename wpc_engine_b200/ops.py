@@ -352,19 +352,17 @@ def attention(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, k_p
     _need(k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.dtype == q.dtype, "pages: wrong type")
     T, B = q.shape[0], ctx_lens.numel()
     out = torch.empty((T, n_heads * head_dim), dtype=q.dtype, device=q.device)
-    if max_new_tokens == 1:
+    if max_new_tokens == 1 and B <= 1024 and B * n_kv_heads <= _WORKSPACE_COUNTERS:
         _need(T == B, "one token per sequence expected")
-        if splits is None:
-            splits = plan_decode_splits(B, n_kv_heads, max_ctx_len, window)
-        part_o = part_ml = None
+        n_ctas = plan_decode_ctas(B, n_kv_heads, max_ctx_len, window, splits)
+        slots = n_ctas + B * n_kv_heads
+        part_o = torch.empty((slots * 16 * head_dim,), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((slots * 16 * 2,), dtype=torch.float32, device=q.device)
         _, counters, _ = workspace(q.device)
-        if splits > 1:
-            part_o = torch.empty((B * n_heads * splits * head_dim,), dtype=torch.float32, device=q.device)
-            part_ml = torch.empty((B * n_heads * splits * 2,), dtype=torch.float32, device=q.device)
         _check("attention_decode", library().wpc_attention_decode(
             _p(q), q.stride(0), _p(out), out.stride(0), _p(k_pages), _p(v_pages), _p(page_table),
             page_table.shape[1], _p(ctx_lens), B, n_heads, n_kv_heads, head_dim, ctypes.c_float(scale),
-            int(window or 0), splits, _p(part_o), _p(part_ml), _p(counters), counters.numel(), _stream()))
+            int(window or 0), n_ctas, _p(part_o), _p(part_ml), _p(counters), counters.numel(), _stream()))
     else:
         _check("attention_prefill", library().wpc_attention_prefill(
             _p(q), q.stride(0), _p(out), out.stride(0), _p(k_pages), _p(v_pages), _p(page_table),
@@ -373,15 +371,18 @@ def attention(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, k_p
     return out
 
 
-def plan_decode_splits(n_seqs: int, n_kv_heads: int, max_ctx_len: int, window: Optional[int]) -> int:
-    """How many CTAs share one sequence's pages in decode attention: enough that about two
-    waves of CTAs are in flight, and at least two pages each."""
+def plan_decode_ctas(n_seqs: int, n_kv_heads: int, max_ctx_len: int, window: Optional[int],
+                     per_pair: Optional[int] = None) -> int:
+    """How many CTAs share the pages of a decode step: two to an SM (an SM takes in only so
+    many bytes a second, so all of them should stream), fewer when there are not even four
+    pages of work for each.  `per_pair` forces about that many CTAs per (sequence, kv head)."""
     blocks = (max_ctx_len + PAGE - 1) // PAGE
     if window:
         blocks = min(blocks, (window + PAGE - 1) // PAGE + 1)
-    ctas = max(n_seqs * n_kv_heads, 1)
-    want = (2 * _SMS + ctas - 1) // ctas
-    return max(1, min(want, blocks // 2, 64))
+    pairs = max(n_seqs * n_kv_heads, 1)
+    if per_pair:
+        return max(1, min(pairs * per_pair, 1024))
+    return max(1, min(2 * _SMS, pairs * max(blocks // 4, 1)))
 
 
 def attention_plain(q, n_heads, n_kv_heads, head_dim, k_pages, v_pages, page_table, seq_of_token, positions,
