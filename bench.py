@@ -211,12 +211,6 @@ def main():
     roofline = {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                 "peaks": peak_src}
 
-    points = {}
-    if not args.skip_points:
-        for b in (1, 64):
-            s, _ = decode_run(b, max(K // 2, 8), W)
-            points[f"decode_b{b}"] = b * max(K // 2, 8) / s
-
     # ---- end to end through generate(): host token ids in, host token ids out, every step ------------
     e2e_prompt_len = start_ctx
     prompts = [torch.randint(0, vocab, (e2e_prompt_len,), generator=gen).tolist() for _ in range(BATCH)]
@@ -229,6 +223,12 @@ def main():
     e2e = {"value": stats["decode_tokens"] / stats["decode_s"], "unit": "tokens/s",
            "h2d_bytes_per_step": lay.total * 4 + BATCH * 4, "d2h_bytes_per_step": BATCH * 4,
            "prefill_tokens_per_s": stats["prefill_tokens"] / stats["prefill_s"]}
+
+    points = {}
+    if not args.skip_points:
+        for b in (1, 64):
+            s, _ = decode_run(b, max(K // 2, 8), W)
+            points[f"decode_b{b}"] = b * max(K // 2, 8) / s
 
     line = {
         "metric": "decode tokens/s at batch 8 (Qwen2.5-7B shape, bf16, context 4096)",

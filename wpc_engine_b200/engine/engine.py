@@ -89,6 +89,8 @@ class Engine:
         if self.device.type == "cuda":
             # parameters are final from here on: kernels may fetch them ahead of their turn
             torch.cuda.synchronize(self.device)
+        self._slot_tensors: Dict[tuple, torch.Tensor] = {}
+        self.supports_device_tokens = self.device.type == "cuda"   # generation may queue a step ahead
         self.steps_run = 0
         self.graph_launches = 0      # kernels that graph replays have launched so far
 
@@ -141,10 +143,15 @@ class Engine:
                 raise ValueError(f"slot {e.slot} would reach {end} positions; "
                                  f"max_position_embeddings is {self.max_positions}")
 
-    def step(self, entries: Sequence[SequenceStep]) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[SequenceStep],
+             device_tokens: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """Runs the tokens that each entry brings, from the cache that earlier steps left;
         returns float32 logits [wanted places, vocab] in the order of the entries and of their
-        `want` lists, or None if nothing is wanted."""
+        `want` lists, or None if nothing is wanted.
+
+        `device_tokens` (int32 on the device, one per entry, for single-token steps): the
+        token ids are taken from there instead of the entries', so that a step can be queued
+        behind the sampling of its tokens without the host having seen them."""
         self._check(entries)
         slots = [e.slot for e in entries]
         starts = [self.cache.reserve(e.slot, len(e.tokens)) for e in entries]
@@ -158,11 +165,16 @@ class Engine:
         plan = plan_step(entries, starts, rows, width, out=host.numpy())
         logits = None
         ran = False
+        if device_tokens is not None and not (plan.is_decode and device_tokens.numel() == len(entries)
+                                              and device_tokens.dtype == torch.int32):
+            raise ValueError("device_tokens needs a single-token step and one int32 id per entry")
         if plan.is_decode and self.use_graphs:
-            ran, logits = self._graph_step(plan, host)
+            ran, logits = self._graph_step(plan, host, device_tokens)
         if not ran:
             meta = host[: lay.total].to(self.device, non_blocking=True)
             self._ring.sent()
+            if device_tokens is not None:
+                meta[lay.tokens: lay.tokens + lay.n_tokens].copy_(device_tokens)
             ctx = context_from(meta, lay, self.dtype, plan.max_new_tokens, plan.max_ctx_len, plan.is_decode,
                                [len(e.tokens) for e in entries])
             logits = self.model.forward(ctx, self.cache)
@@ -171,7 +183,7 @@ class Engine:
         self.steps_run += 1
         return logits
 
-    def _graph_step(self, plan, host: torch.Tensor):
+    def _graph_step(self, plan, host: torch.Tensor, device_tokens: Optional[torch.Tensor] = None):
         """Single-token steps of a shape seen before are replayed from a CUDA graph.  The first
         step of a shape runs directly (returns ran=False); the second is captured, which runs
         nothing, and then replayed, so that no step ever runs twice."""
@@ -193,6 +205,8 @@ class Engine:
         graph, meta, logits, n_kernels = entry
         meta.copy_(host[: lay.total], non_blocking=True)
         self._ring.sent()
+        if device_tokens is not None:
+            meta[lay.tokens: lay.tokens + lay.n_tokens].copy_(device_tokens)
         graph.replay()
         self.graph_launches += n_kernels
         return True, logits
@@ -207,7 +221,13 @@ class Engine:
     def sample(self, logits: torch.Tensor, slots: Sequence[int], temperature: float,
                banned: Sequence[int] = ()) -> torch.Tensor:
         """One token per row of `logits`, int32 on the device; row i belongs to slots[i]."""
-        slot_t = torch.tensor(list(slots), dtype=torch.int32).to(self.device, non_blocking=True)
+        key = tuple(slots)
+        slot_t = self._slot_tensors.get(key)
+        if slot_t is None:
+            if len(self._slot_tensors) > 256:
+                self._slot_tensors.clear()
+            slot_t = torch.tensor(list(slots), dtype=torch.int32).to(self.device)
+            self._slot_tensors[key] = slot_t
         banned_t = None
         if len(banned):
             banned_t = torch.tensor(sorted(set(int(b) for b in banned)), dtype=torch.int32).to(self.device)

@@ -72,6 +72,77 @@ def advance(live: List[_Live], picked: Sequence[int], opts: GenerationOptions, s
     return go_on, done
 
 
+def _note(stats, first: bool, dt: float, entries) -> None:
+    if stats is None:
+        return
+    if first:
+        stats["prefill_s"] += dt
+        stats["prefill_tokens"] += sum(len(e.tokens) for e in entries)
+    else:
+        stats["decode_s"] += dt
+        stats["decode_tokens"] += len(entries)
+        stats["decode_steps"] += 1
+
+
+def _run_batch(engine, live, entries, opts, stop, outputs, stats) -> None:
+    """One batch, step by step: every step waits for its tokens on the host."""
+    first = True
+    while live:
+        t0 = time.perf_counter()
+        logits = engine.step(entries)
+        picked = engine.sample(logits, [s.slot for s in live], opts.temperature,
+                               opts.banned_token_ids).tolist()      # the step's one device-to-host read
+        _note(stats, first, time.perf_counter() - t0, entries)
+        first = False
+        live[:], done = advance(live, picked, opts, stop)
+        for seq in done:
+            outputs[seq.request] = seq.output
+            engine.close_sequence(seq.slot)
+        entries = [SequenceStep(s.slot, [s.output[-1]], want=[0]) for s in live]
+
+
+def _run_batch_pipelined(engine, live, entries, opts, stop, outputs, stats) -> None:
+    """One batch with the next step queued before the host has read the current tokens: the
+    sampled ids stay on the device and feed the next step from there, so the device never
+    waits for the host.  Who ends by reaching max_tokens is known in advance and gets no
+    further step.  A stop token is only seen one step late: that sequence has then run one
+    step too many, whose result is dropped (its slot is closed behind that step in stream
+    order).  The tokens that come out are the same as step by step."""
+    import torch
+    first = True
+    t0 = time.perf_counter()
+    logits = engine.step(entries)
+    while live:
+        ids = engine.sample(logits, [s.slot for s in live], opts.temperature, opts.banned_token_ids)
+        host_ids = ids.to("cpu", non_blocking=True)
+        done_event = torch.cuda.Event()
+        done_event.record()
+        # who would go on if the token just drawn is no stop token
+        ahead = [i for i, s in enumerate(live) if len(s.output) + 1 < opts.max_tokens]
+        next_logits = None
+        next_entries = []
+        if ahead:
+            next_entries = [SequenceStep(live[i].slot, [0], want=[0]) for i in ahead]
+            feed = ids if len(ahead) == len(live) else ids[torch.tensor(ahead, device=ids.device)]
+            next_logits = engine.step(next_entries, device_tokens=feed)
+        done_event.synchronize()                      # the step's one device-to-host read
+        picked = host_ids.tolist()
+        now = time.perf_counter()
+        _note(stats, first, now - t0, entries)
+        t0, first, entries = now, False, next_entries
+        ahead_seqs = [live[i] for i in ahead]
+        go_on, done = advance(live, picked, opts, stop)
+        for seq in done:
+            outputs[seq.request] = seq.output
+            engine.close_sequence(seq.slot)
+        if len(go_on) != len(ahead_seqs):
+            # some of those that ran ahead met a stop token: drop their rows
+            keep = [i for i, s in enumerate(ahead_seqs) if any(s is g for g in go_on)]
+            next_logits = next_logits[torch.tensor(keep, device=next_logits.device)] if keep else None
+        live[:] = go_on
+        logits = next_logits
+
+
 def generate(engine, prompts: Sequence[Sequence[int]], opts: GenerationOptions,
              stats: Optional[dict] = None) -> List[List[int]]:
     """Generated token ids for each prompt.  `engine` offers open_sequence, close_sequence,
@@ -94,27 +165,11 @@ def generate(engine, prompts: Sequence[Sequence[int]], opts: GenerationOptions,
             engine.set_sampler_state([s.slot for s in live], opts.seed, [s.request for s in live])
             entries = [SequenceStep(s.slot, list(prompts[s.request]), want=[len(prompts[s.request]) - 1])
                        for s in live]
-            first = True
-            while live:
-                t0 = time.perf_counter()
-                logits = engine.step(entries)
-                picked = engine.sample(logits, [s.slot for s in live], opts.temperature,
-                                       opts.banned_token_ids).tolist()      # the step's one device-to-host read
-                if stats is not None:
-                    dt = time.perf_counter() - t0
-                    if first:
-                        stats["prefill_s"] += dt
-                        stats["prefill_tokens"] += sum(len(e.tokens) for e in entries)
-                    else:
-                        stats["decode_s"] += dt
-                        stats["decode_tokens"] += len(entries)
-                        stats["decode_steps"] += 1
-                first = False
-                live, done = advance(live, picked, opts, stop)
-                for seq in done:
-                    outputs[seq.request] = seq.output
-                    engine.close_sequence(seq.slot)
-                entries = [SequenceStep(s.slot, [s.output[-1]], want=[0]) for s in live]
+            if getattr(engine, "supports_device_tokens", False):
+                _run_batch_pipelined(engine, live, entries, opts, stop, outputs, stats)
+            else:
+                _run_batch(engine, live, entries, opts, stop, outputs, stats)
+            live = []
         except BaseException:
             for seq in live:
                 try:
