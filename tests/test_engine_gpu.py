@@ -140,3 +140,63 @@ def test_stop_tokens_end_one_sequence_while_others_go_on(engines):
         assert g == f[:cut]
     eng.cache.check()
     assert eng.cache.slots.n_held == 0
+
+
+ODD = {
+    # head size over 128 (plain attention), width 8 does not divide (plain products), odd vocabulary
+    "wide_head": dict(num_hidden_layers=2, hidden_size=100, num_attention_heads=2, num_key_value_heads=1, head_dim=144,
+                      intermediate_size=52, vocab_size=333, rope_theta=7000.0, rms_norm_eps=2e-6),
+    # 32 query heads on one KV head (more than the tensor-core kernel stacks), tied head
+    "many_per_group": dict(num_hidden_layers=1, hidden_size=512, num_attention_heads=32, num_key_value_heads=1,
+                           intermediate_size=192, vocab_size=200, rope_theta=1e5, rms_norm_eps=1e-5,
+                           tie_word_embeddings=True),
+    # many heads and groups that are no power of two, head size 80, window on every layer
+    "odd_heads": dict(num_hidden_layers=2, hidden_size=240, num_attention_heads=6, num_key_value_heads=3, head_dim=80,
+                      intermediate_size=320, vocab_size=1000, rope_theta=1e4, rms_norm_eps=1e-6,
+                      use_sliding_window=True, sliding_window=70, max_window_layers=0),
+}
+
+
+@pytest.mark.parametrize("name", sorted(ODD))
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_unusual_sizes(tmp_path_factory, name, dtype):
+    """Sizes that the fast kernels do not take run on the plain kernels of the library, and
+    sizes that they do take at their edges, with the same answers."""
+    from conftest import make_folder
+    raw = dict(architectures=["Qwen2ForCausalLM"], tie_word_embeddings=False, max_position_embeddings=512)
+    raw.update(ODD[name])
+    folder = make_folder(tmp_path_factory, raw, 9, getattr(torch, dtype))
+    eng = Engine.from_folder(folder, dtype=dtype, max_tokens=2048)
+    reqs = [random_tokens(raw["vocab_size"], n, 800 + n) for n in (150, 9)]
+    assert_close_to_plain(run_whole(eng, reqs[0]), folder, reqs[0], dtype, f"{name} whole")
+    assert_close_to_plain(run_tail_one_by_one(eng, reqs[0], tail=40), folder, reqs[0], dtype, f"{name} tail")
+    for r, o in zip(reqs, run_batch(eng, reqs, [100, 9])):
+        assert_close_to_plain(o, folder, r, dtype, f"{name} batch")
+    eng.cache.check()
+
+
+def test_errors_are_loud(engines):
+    from wpc_engine_b200 import CacheError, SequenceStep
+    eng, _ = engines("A", "float32")
+    slot = eng.open_sequence()
+    try:
+        with pytest.raises(ValueError, match="token id outside"):
+            eng.step([SequenceStep(slot, [256], want=[0])])
+        with pytest.raises(ValueError, match="max_position_embeddings"):
+            eng.step([SequenceStep(slot, [1] * 129, want=[0])])
+        with pytest.raises(ValueError, match="twice"):
+            eng.step([SequenceStep(slot, [1], want=[0]), SequenceStep(slot, [2], want=[0])])
+        with pytest.raises(CacheError, match="not open"):
+            eng.step([SequenceStep(slot + 1000, [1], want=[0])])
+        assert eng.sequence_length(slot) == 0
+    finally:
+        eng.close_sequence(slot)
+    small = Engine.from_folder(engines("A", "float32")[1], dtype="float32", max_tokens=128)
+    a, b, c = small.open_sequence(), small.open_sequence(), None
+    small.step([SequenceStep(a, [1] * 64, want=[]), SequenceStep(b, [2] * 64, want=[])])
+    with pytest.raises(CacheError, match="out of pages"):
+        small.step([SequenceStep(a, [3], want=[0])])
+    with pytest.raises(CacheError, match="out of slots"):
+        small.open_sequence()
+    small.close_sequence(a)
+    assert small.step([SequenceStep(b, [3], want=[0])]).shape == (1, 256)
