@@ -206,7 +206,8 @@ def test_fill_normal_moments():
 
 # ---- the tensor-core product against its plain twin and the torch reference ----------------------
 TC_SHAPES = [(1, 128, 64), (8, 256, 128), (8, 4608, 3584), (8, 3584, 18944), (64, 1000, 520), (100, 384, 96),
-             (129, 200, 72), (256, 256, 256), (300, 1000, 520), (2048, 512, 256), (513, 4608, 3584), (16, 37888, 3584)]
+             (129, 200, 72), (256, 256, 256), (300, 1000, 520), (2048, 512, 256), (513, 4608, 3584), (16, 37888, 3584),
+             (2048, 3584, 1024), (1000, 5000, 520), (2100, 4608, 512)]     # more tiles than SMs: persistent, stream-K
 
 
 @pytest.mark.parametrize("shape", TC_SHAPES)

@@ -57,6 +57,8 @@ struct Params {
   int* counters;               // one ticket counter per tile, zero between launches
   int* status;                 // device error word (may be null)
   int stages;                  // depth of the operand ring (2..MAX_STAGES)
+  int stream_k;                // 1: every CTA takes an equal share of all k-blocks of all tiles (stream-K);
+                               //    tiles that are cut add their shares with red.add (needs accumulate)
   int prefetch_weights;        // 1: the weight operand (A when swapped, else B) is never written while the
                                //    model runs, so its first stages may be fetched before the kernel
                                //    ahead in the stream has finished
@@ -247,6 +249,61 @@ __device__ __forceinline__ void store_row32(const Params& p, int row, int col0, 
   }
 }
 
+// One piece of work of a CTA: a tile and a range of its k-blocks.
+struct Work {
+  int tile_id, split, m0, n0, kb0, n_kb;
+  bool partial;                // the range does not cover the tile's whole K
+};
+// The pieces of one CTA, in order.  Unit mode: (tile, K slice) units blockIdx.x, + gridDim.x, ...
+// with the M tile fastest, so that CTAs running side by side share weight tiles.  Stream-K
+// mode: the k-blocks of all tiles laid end to end, cut into gridDim.x equal shares.
+template <int BN>
+struct WorkIter {
+  int n_tiles, tiles_m, k_blocks, splits, kb_per;
+  int u, n_units, stride;      // unit mode
+  int g, g1;                   // stream-K mode
+  bool stream_k;
+  __device__ WorkIter(const Params& p) {
+    tiles_m = (p.M + BM - 1) / BM;
+    n_tiles = tiles_m * ((p.N + BN - 1) / BN);
+    k_blocks = p.k_blocks;
+    splits = p.splits;
+    kb_per = (k_blocks + splits - 1) / splits;
+    stream_k = p.stream_k != 0;
+    u = blockIdx.x;
+    n_units = n_tiles * splits;
+    stride = gridDim.x;
+    const long total = (long)n_tiles * k_blocks;
+    const long share = (total + gridDim.x - 1) / gridDim.x;
+    const long lo = share * blockIdx.x, hi = lo + share;
+    g = (int)(lo < total ? lo : total);
+    g1 = (int)(hi < total ? hi : total);
+  }
+  __device__ bool next(Work& w) {
+    if (!stream_k) {
+      if (u >= n_units) return false;
+      w.split = u / n_tiles;
+      w.tile_id = u - w.split * n_tiles;
+      w.kb0 = w.split * kb_per;
+      w.n_kb = max(min(k_blocks, w.kb0 + kb_per) - w.kb0, 0);
+      w.partial = splits > 1;
+      u += stride;
+    } else {
+      if (g >= g1) return false;
+      w.tile_id = g / k_blocks;
+      w.kb0 = g - w.tile_id * k_blocks;
+      w.n_kb = min(k_blocks - w.kb0, g1 - g);
+      w.partial = w.n_kb < k_blocks;
+      w.split = w.kb0 == 0 ? 0 : 1;      // only the share that starts the tile adds the bias
+      g += w.n_kb;
+    }
+    const int tile_n = w.tile_id / tiles_m, tile_m = w.tile_id - tile_n * tiles_m;
+    w.m0 = tile_m * BM;
+    w.n0 = tile_n * BN;
+    return true;
+  }
+};
+
 template <int BN, bool SWAP>
 __global__ void __launch_bounds__(THREADS, (BN <= 64 ? 2 : 1))     // narrow tiles run two CTAs to an SM
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
@@ -261,23 +318,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   int* flags = (int*)(tmem_holder + 1);          // [0]: a wait ran out, [1]: this CTA drew the last ticket
   uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + S::HEAD_BYTES + 1023) & ~(uintptr_t)1023);
   const int STAGES = p.stages;
+  float* red_stage = (float*)(tiles + STAGES * S::STAGE_BYTES);    // [4][32][33], present where cut tiles add (see launch)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // A unit of work is (tile, K slice).  Units are numbered with the M tile fastest, so CTAs
-  // that run side by side share weight tiles; a CTA takes units blockIdx.x, + gridDim.x, ...
-  // and keeps two accumulators in tensor memory, so that the epilogue of one unit runs while
-  // the MMAs of the next fill the other accumulator.
-  const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
-  const int n_tiles = tiles_m * tiles_n;
-  const int n_units = n_tiles * p.splits;
-  const int kb_per = (p.k_blocks + p.splits - 1) / p.splits;
-#define WPC_UNIT_COORDS(u)                                              \
-  const int split = (u) / n_tiles, tile_id = (u) - split * n_tiles;     \
-  const int tile_n = tile_id / tiles_m, tile_m = tile_id - tile_n * tiles_m; \
-  const int m0 = tile_m * BM, n0 = tile_n * BN;                         \
-  const int kb0 = split * kb_per;                                       \
-  const int n_kb = max(min(p.k_blocks, kb0 + kb_per) - kb0, 0);
-
+  // A CTA walks its pieces of work (see WorkIter) and keeps two accumulators in tensor memory,
+  // so that the epilogue of one piece runs while the MMAs of the next fill the other.
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full + s, 1);
@@ -301,10 +346,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (lane == 0) {
       int it = 0;                                   // k-blocks loaded so far: position in the ring
       bool ok = true;
-      for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
-        WPC_UNIT_COORDS(u)
+      WorkIter<BN> work(p);
+      Work w;
+      bool first = true;
+      while (ok && work.next(w)) {
+        const int m0 = w.m0, n0 = w.n0, kb0 = w.kb0, n_kb = w.n_kb;
         int i = 0;
-        if (u == (int)blockIdx.x) {
+        if (first) {
+          first = false;
           // the first ring of stages: the weight operand may start before the dependency wait
           const int pre = p.prefetch_weights ? min(n_kb, STAGES) : 0;
           for (i = 0; i < pre; ++i) {
@@ -337,9 +386,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       constexpr uint32_t idesc = instr_desc(BN);
       bool ok = true;
       int it = 0, j = 0;
-      for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x, ++j) {
-        WPC_UNIT_COORDS(u)
-        (void)m0; (void)n0;
+      WorkIter<BN> work(p);
+      Work w;
+      for (; ok && work.next(w); ++j) {
+        const int n_kb = w.n_kb;
         const int b = j & 1;
         if (!mbar_wait(accum_empty + b, ((j >> 1) & 1) ^ 1)) { atomicExch(flags, 1); break; }
         fence_after_sync();
@@ -368,8 +418,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int r = q * 32 + lane;                        // row of the tile = TMEM lane
     const int et = threadIdx.x - 64;                    // 0..127 among the epilogue threads
     int j = 0;
-    for (int u = blockIdx.x; u < n_units; u += gridDim.x, ++j) {
-      WPC_UNIT_COORDS(u)
+    WorkIter<BN> work(p);
+    Work w;
+    for (; work.next(w); ++j) {
+      const int m0 = w.m0, n0 = w.n0, n_kb = w.n_kb, split = w.split, tile_id = w.tile_id;
       const int b = j & 1;
       bool ok = mbar_wait(accum_full + b, (j >> 1) & 1);
       ok = __all_sync(0xffffffffu, ok);              // tcgen05.ld needs the whole warp on one path
@@ -380,7 +432,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const bool have_acc = n_kb > 0 && ok;
 
       bool run_epilogue = ok;
-      if (p.splits > 1 && p.accumulate) {
+      if (w.partial && p.accumulate) {
         // Every slice adds its share straight into the float32 output with red.global.add: no
         // scratch, no tickets, no fences.  The order in which the slices arrive is not fixed,
         // so the sum may differ in its last bits from run to run.
@@ -391,12 +443,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           tmem_ld_wait();
           const int nc = min(32, n_valid - c);
           if (!SWAP) {
-            const int row = m0 + r;
-            if (row < p.M) {
-              float* dst = (float*)p.out + (size_t)row * p.ldc + n0 + c;
+            // this thread holds 32 columns of one row; through shared memory the warp turns its
+            // 32 x 32 block around, so that one red.add instruction covers 32 columns of a row
+            float* st = red_stage + q * (32 * 33);
+            __syncwarp();
 #pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (j < nc) atomicAdd(dst + j, __uint_as_float(v[j]) + ((p.bias && split == 0) ? p.bias[n0 + c + j] : 0.f));
+            for (int j = 0; j < 32; ++j)
+              st[lane * 33 + j] = __uint_as_float(v[j]) + ((p.bias && split == 0 && j < nc) ? p.bias[n0 + c + j] : 0.f);
+            __syncwarp();
+            if (lane < nc) {
+              for (int rr = 0; rr < 32; ++rr) {
+                const int row = m0 + q * 32 + rr;
+                if (row < p.M) atomicAdd((float*)p.out + (size_t)row * p.ldc + n0 + c + lane, st[rr * 33 + lane]);
+              }
             }
           } else {
             const int feat = m0 + r;
@@ -559,7 +618,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       if (!ok) break;
     }
   }
-#undef WPC_UNIT_COORDS
 
   fence_before_sync();
   __syncthreads();
@@ -665,8 +723,18 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, Params& p, cudaS
   if (!persistent && stages > kb_per) stages = kb_per < 2 ? 2 : kb_per;
   if (stages > g_stage_limit) stages = g_stage_limit < 2 ? 2 : g_stage_limit;
   p.stages = stages;
+  // Stream-K (equal shares of all k-blocks) is implemented but off: on B200 the red.adds of the
+  // cut tiles cost more than the idle half of a second wave (33.5 ms against 31.3 ms for a
+  // 2,048-token prefill of the 7B shape).
+  p.stream_k = 0;
   dim3 grid(persistent ? 148 : (unsigned)units);
-  wpc::launch(gemm_tc_kernel<BN, SWAP>, grid, THREADS, S::total(stages), stream, ma, mb, p);
+  // cut tiles of the normal arrangement that add into the output turn their blocks around in
+  // shared memory first (see the epilogue): room for [4][32][33] floats behind the ring
+  constexpr int RED_STAGE_BYTES = 4 * 32 * 33 * 4;
+  const bool red_stage = !SWAP && p.accumulate && (p.splits > 1 || p.stream_k);
+  if (red_stage && S::total(stages) + RED_STAGE_BYTES > S::total(S::max_stages(1))) p.stages = --stages;
+  wpc::launch(gemm_tc_kernel<BN, SWAP>, grid, THREADS, S::total(stages) + (red_stage ? RED_STAGE_BYTES : 0), stream,
+              ma, mb, p);
   return launch_status();
 }
 
@@ -711,6 +779,7 @@ int wpc_gemm_tc(const void* a, int lda, int rows_a, const void* b, int ldb, int 
   if (accumulate && out_dtype != WPC_DTYPE_F32) return WPC_ERR_BAD_ARGUMENT;
   Params p;
   p.stages = 2;
+  p.stream_k = 0;
   p.M = rows_a; p.N = rows_b; p.K = K;
   p.k_blocks = (K + BK - 1) / BK;
   p.splits = splits < 1 ? 1 : (splits > p.k_blocks ? p.k_blocks : splits);
@@ -836,6 +905,7 @@ extern "C" int wpc_linear_few_tokens_static(const void* x, int ldx, int tokens, 
 
   Params p;
   p.stages = 2;
+  p.stream_k = 0;
   p.M = features; p.N = tokens; p.K = K;
   p.k_blocks = k_blocks;
   p.splits = splits;
