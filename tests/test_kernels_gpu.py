@@ -309,3 +309,40 @@ def test_gated_linear_fused_epilogue(T, inner, K):
 def test_silu_mul_groups(dtype, inner, group):
     gu = rnd((5, 2 * inner), dtype, 53, 2.0)
     close(ops.silu_mul(gu, inner, group), ref.silu_mul(gu.cpu(), inner, group).to(DEV), dtype)
+
+
+# ---- prefill attention on tcgen05 against the plain reference and the mma.sync twin ---------------
+@pytest.mark.parametrize("nh,nkv,hd", [(28, 4, 128), (14, 2, 64), (4, 4, 128), (3, 1, 64), (16, 1, 128)])
+@pytest.mark.parametrize("window", [None, 100])
+def test_attention_prefill_tcgen05(nh, nkv, hd, window):
+    lens, new = [300, 5, 131, 700, 64], [300, 5, 31, 190, 1]
+    qkv, kp, vp, table, seq, pos = paged_case(torch.bfloat16, nh, nkv, hd, lens, new, seed=11)
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(new)]), dtype=torch.int32, device=DEV)
+    ctx = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(hd)
+    got = ops.attention(qkv, nh, nkv, hd, kp, vp, table, cu, ctx, seq, pos, scale, window, max(new), max(lens))
+    twin = ops.attention(qkv, nh, nkv, hd, kp, vp, table, cu, ctx, seq, pos, scale, window, max(new), max(lens),
+                         mma_only=True)
+    assert ops.device_status() == 0
+    want = ref.attention_plain(qkv.cpu(), nh, nkv, hd, kp.cpu(), vp.cpu(), table.cpu(), seq.cpu(), pos.cpu(),
+                               scale, window)
+    close(twin.cpu(), want, torch.bfloat16)
+    close(got.cpu(), want, torch.bfloat16)
+
+
+def test_attention_prefill_tcgen05_growing_maximum():
+    """Scores that keep growing along the sequence force the lazy rescaling of the output rows."""
+    nh, nkv, hd = 2, 1, 128
+    lens, new = [520], [520]
+    qkv, kp, vp, table, seq, pos = paged_case(torch.bfloat16, nh, nkv, hd, lens, new, seed=12)
+    for p in range(520):                      # key p points along a fixed direction, ever longer
+        page = int(table[0, p // 64])
+        kp[page, 0, p % 64, :] = 0.0
+        kp[page, 0, p % 64, 0] = 0.25 * p
+    qkv[:, 0] = 2.0
+    qkv[:, hd] = 2.0
+    cu = torch.tensor([0, 520], dtype=torch.int32, device=DEV)
+    ctx = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    got = ops.attention(qkv, nh, nkv, hd, kp, vp, table, cu, ctx, seq, pos, 1.0, None, 520, 520)
+    want = ref.attention_plain(qkv.cpu(), nh, nkv, hd, kp.cpu(), vp.cpu(), table.cpu(), seq.cpu(), pos.cpu(), 1.0, None)
+    close(got.cpu(), want, torch.bfloat16)

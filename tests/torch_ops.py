@@ -107,7 +107,7 @@ def qk_rope_kv_store(qkv, n_heads, n_kv_heads, head_dim, cos, sin, k_pages, v_pa
 
 
 def attention(q, n_heads, n_kv_heads, head_dim, k_pages, v_pages, page_table, cu_seqlens, ctx_lens,
-              seq_of_token, positions, scale, window, max_new_tokens, max_ctx_len, splits=None):
+              seq_of_token, positions, scale, window, max_new_tokens, max_ctx_len, splits=None, mma_only=False):
     return attention_plain(q, n_heads, n_kv_heads, head_dim, k_pages, v_pages, page_table, seq_of_token,
                            positions, scale, window)
 

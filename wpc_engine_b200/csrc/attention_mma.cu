@@ -440,7 +440,8 @@ prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16*
   extern __shared__ __align__(16) uint8_t smem_raw[];
   __nv_bfloat16* ks = (__nv_bfloat16*)smem_raw;
   __nv_bfloat16* vs = ks + 2 * Cfg<HD>::PAGE_ELEMS;
-  const int tile = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
+  // the last tiles of a sequence see the most keys: they start first
+  const int tile = (int)gridDim.x - 1 - (int)blockIdx.x, g = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_rep = nh / nkv;
   const int tok0 = cu_seqlens[b];

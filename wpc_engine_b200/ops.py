@@ -337,13 +337,15 @@ def qk_rope_kv_store(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim:
 def attention(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, k_pages: torch.Tensor,
               v_pages: torch.Tensor, page_table: torch.Tensor, cu_seqlens: torch.Tensor, ctx_lens: torch.Tensor,
               seq_of_token: torch.Tensor, positions: torch.Tensor, scale: float, window: Optional[int],
-              max_new_tokens: int, max_ctx_len: int, splits: Optional[int] = None) -> torch.Tensor:
+              max_new_tokens: int, max_ctx_len: int, splits: Optional[int] = None,
+              mma_only: bool = False) -> torch.Tensor:
     """softmax(q . k * scale) . v over the cached positions that each query sees: 0..its own,
     or the last `window` of them.  q: the first n_heads*head_dim columns of each row.
 
-    bfloat16 with a head size that is a multiple of 16 up to 128 runs on the tensor cores
-    (csrc/attention_mma.cu): the split-KV kernel when every sequence brings one token, the
-    tiled kernel otherwise.  Everything else runs the plain kernel."""
+    bfloat16 with a head size that is a multiple of 16 up to 128 runs on the tensor cores: the
+    split-KV kernel when every sequence brings one token (csrc/attention_mma.cu); otherwise the
+    tcgen05 kernel for head sizes 64 and 128 (csrc/attention_tc.cu) and the mma.sync kernel for
+    the others (or with `mma_only`).  Everything else runs the plain kernel."""
     if q.dtype != torch.bfloat16 or not library().wpc_attention_mma_supports(n_heads, n_kv_heads, head_dim):
         return attention_plain(q, n_heads, n_kv_heads, head_dim, k_pages, v_pages, page_table, seq_of_token,
                                positions, scale, window)
@@ -363,6 +365,13 @@ def attention(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, k_p
             _p(q), q.stride(0), _p(out), out.stride(0), _p(k_pages), _p(v_pages), _p(page_table),
             page_table.shape[1], _p(ctx_lens), B, n_heads, n_kv_heads, head_dim, ctypes.c_float(scale),
             int(window or 0), n_ctas, _p(part_o), _p(part_ml), _p(counters), counters.numel(), _stream()))
+    elif (not mma_only and library().wpc_attention_prefill_tc_supports(n_heads, n_kv_heads, head_dim)
+          and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0):
+        _, _, status = workspace(q.device)
+        _check("attention_prefill_tc", library().wpc_attention_prefill_tc(
+            _p(q), q.stride(0), _p(out), out.stride(0), _p(k_pages), _p(v_pages), _p(page_table),
+            page_table.shape[1], _p(cu_seqlens), _p(ctx_lens), B, max_new_tokens, n_heads, n_kv_heads, head_dim,
+            ctypes.c_float(scale), int(window or 0), _p(status), _stream()))
     else:
         _check("attention_prefill", library().wpc_attention_prefill(
             _p(q), q.stride(0), _p(out), out.stride(0), _p(k_pages), _p(v_pages), _p(page_table),
