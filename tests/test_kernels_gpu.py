@@ -207,7 +207,8 @@ def test_fill_normal_moments():
 # ---- the tensor-core product against its plain twin and the torch reference ----------------------
 TC_SHAPES = [(1, 128, 64), (8, 256, 128), (8, 4608, 3584), (8, 3584, 18944), (64, 1000, 520), (100, 384, 96),
              (129, 200, 72), (256, 256, 256), (300, 1000, 520), (2048, 512, 256), (513, 4608, 3584), (16, 37888, 3584),
-             (2048, 3584, 1024), (1000, 5000, 520), (2100, 4608, 512)]     # more tiles than SMs: persistent, stream-K
+             (2048, 3584, 1024), (1000, 5000, 520), (2100, 4608, 512),     # more tiles than SMs: persistent
+             (2048, 4608, 256), (2000, 4608, 264), (2048, 3584, 264)]      # 256 x 256 tiles (one wave; tails)
 
 
 @pytest.mark.parametrize("shape", TC_SHAPES)
@@ -216,6 +217,8 @@ def test_tensor_core_linear(shape, mode):
     M, N, K = shape
     x, w = rnd((M, K), torch.bfloat16, 21), rnd((N, K), torch.bfloat16, 22, 0.05)
     swap, bn, splits = ops.plan_tensor_core_linear(M, N, K)
+    if shape in ((2048, 4608, 256), (2000, 4608, 264), (2048, 3584, 264)):
+        assert ops.tall_tiles(M, N, swap, bn, splits)
     if mode == "plain":
         got, want = ops.linear(x, w), ops.linear_plain(x, w)
         tol = 1.2e-2
@@ -289,7 +292,7 @@ def test_attention_prefill_window_edges():
 
 
 @pytest.mark.parametrize("T,inner,K", [(1, 64, 96), (8, 256, 96), (50, 192, 72), (100, 320, 520), (200, 256, 96),
-                                       (300, 384, 520), (2048, 1024, 256), (8, 18944, 3584)])
+                                       (300, 384, 520), (2048, 1024, 256), (8, 18944, 3584), (2048, 2304, 256), (4096, 1152, 128)])
 def test_gated_linear_fused_epilogue(T, inner, K):
     """silu(gate) * up applied by the product's epilogue (both arrangements) against the
     product followed by the activation kernel, and against torch."""

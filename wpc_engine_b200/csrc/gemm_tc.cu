@@ -183,9 +183,9 @@ __host__ __device__ constexpr uint32_t instr_desc(int n) {
 // so that enough bytes are in flight to cover the memory latency; two co-resident CTAs share.
 constexpr int MAX_STAGES = 12;
 constexpr int SMEM_LIMIT = 227 * 1024;
-template <int BN>
+template <int BN, int MT = 1>
 struct Smem {
-  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int A_BYTES = MT * BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int HEAD_BYTES = 1024;
@@ -257,14 +257,14 @@ struct Work {
 // The pieces of one CTA, in order.  Unit mode: (tile, K slice) units blockIdx.x, + gridDim.x, ...
 // with the M tile fastest, so that CTAs running side by side share weight tiles.  Stream-K
 // mode: the k-blocks of all tiles laid end to end, cut into gridDim.x equal shares.
-template <int BN>
+template <int BN, int MT = 1>
 struct WorkIter {
   int n_tiles, tiles_m, k_blocks, splits, kb_per;
   int u, n_units, stride;      // unit mode
   int g, g1;                   // stream-K mode
   bool stream_k;
   __device__ WorkIter(const Params& p) {
-    tiles_m = (p.M + BM - 1) / BM;
+    tiles_m = (p.M + MT * BM - 1) / (MT * BM);
     n_tiles = tiles_m * ((p.N + BN - 1) / BN);
     k_blocks = p.k_blocks;
     splits = p.splits;
@@ -298,16 +298,19 @@ struct WorkIter {
       g += w.n_kb;
     }
     const int tile_n = w.tile_id / tiles_m, tile_m = w.tile_id - tile_n * tiles_m;
-    w.m0 = tile_m * BM;
+    w.m0 = tile_m * MT * BM;
     w.n0 = tile_n * BN;
     return true;
   }
 };
 
-template <int BN, bool SWAP>
+// MT = 2: the tile is 256 rows of A by BN; the two 128-row halves are two MMAs that share the B
+// tile in shared memory (a third less operand traffic per flop) and fill both accumulators, so
+// the epilogue does not overlap the next tile.
+template <int BN, bool SWAP, int MT>
 __global__ void __launch_bounds__(THREADS, (BN <= 64 ? 2 : 1))     // narrow tiles run two CTAs to an SM
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
-  using S = Smem<BN>;
+  using S = Smem<BN, MT>;
   pdl_trigger();
   extern __shared__ uint8_t smem_raw[];
   uint64_t* full = (uint64_t*)smem_raw;
@@ -346,7 +349,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (lane == 0) {
       int it = 0;                                   // k-blocks loaded so far: position in the ring
       bool ok = true;
-      WorkIter<BN> work(p);
+      WorkIter<BN, MT> work(p);
       Work w;
       bool first = true;
       while (ok && work.next(w)) {
@@ -386,12 +389,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       constexpr uint32_t idesc = instr_desc(BN);
       bool ok = true;
       int it = 0, j = 0;
-      WorkIter<BN> work(p);
+      WorkIter<BN, MT> work(p);
       Work w;
       for (; ok && work.next(w); ++j) {
         const int n_kb = w.n_kb;
-        const int b = j & 1;
-        if (!mbar_wait(accum_empty + b, ((j >> 1) & 1) ^ 1)) { atomicExch(flags, 1); break; }
+        const int b = MT == 1 ? (j & 1) : 0;           // two accumulators take turns, or both serve one tile
+        const int use = MT == 1 ? (j >> 1) : j;        // how often this accumulator has been used before
+        if (!mbar_wait(accum_empty + b, (use & 1) ^ 1)) { atomicExch(flags, 1); break; }
         fence_after_sync();
         const uint32_t tmem_d = tmem_base + b * S::TMEM_COLS;
         for (int i = 0; i < n_kb; ++i, ++it) {
@@ -405,6 +409,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           for (int k = 0; k < BK / UMMA_K; ++k) {
             // 32 bytes further along K inside the swizzled row: + 2 in the (address / 16) field
             umma_bf16(tmem_d, da + 2 * k, db + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+            if (MT == 2)      // rows 128..255 of the A tile lie 16 KiB further; second accumulator
+              umma_bf16(tmem_d + S::TMEM_COLS, da + 2 * k + ((BM * BK * 2) >> 4), db + 2 * k, idesc,
+                        (i > 0 || k > 0) ? 1u : 0u);
           }
           umma_commit(empty + s);       // the stage is free again once these MMAs have read it
         }
@@ -418,18 +425,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int r = q * 32 + lane;                        // row of the tile = TMEM lane
     const int et = threadIdx.x - 64;                    // 0..127 among the epilogue threads
     int j = 0;
-    WorkIter<BN> work(p);
+    WorkIter<BN, MT> work(p);
     Work w;
     for (; work.next(w); ++j) {
-      const int m0 = w.m0, n0 = w.n0, n_kb = w.n_kb, split = w.split, tile_id = w.tile_id;
-      const int b = j & 1;
-      bool ok = mbar_wait(accum_full + b, (j >> 1) & 1);
+      const int n0 = w.n0, n_kb = w.n_kb, split = w.split, tile_id = w.tile_id;
+      const int b = MT == 1 ? (j & 1) : 0;
+      const int use = MT == 1 ? (j >> 1) : j;
+      bool ok = mbar_wait(accum_full + b, use & 1);
       ok = __all_sync(0xffffffffu, ok);              // tcgen05.ld needs the whole warp on one path
       if (!ok) atomicExch(flags, 1);
       fence_after_sync();
-      const uint32_t lane_addr = tmem_base + b * S::TMEM_COLS + ((uint32_t)(q * 32) << 16);
       const int n_valid = min(BN, p.N - n0);              // columns of the tile that exist
       const bool have_acc = n_kb > 0 && ok;
+      for (int half = 0; half < MT; ++half) {             // the 128-row halves of a 256-row tile
+      const int m0 = w.m0 + half * BM;
+      const uint32_t lane_addr = tmem_base + (MT == 1 ? b : half) * S::TMEM_COLS + ((uint32_t)(q * 32) << 16);
 
       bool run_epilogue = ok;
       if (w.partial && p.accumulate) {
@@ -612,6 +622,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
       }
 
+      }                                                   // halves
       // the accumulator may be overwritten now
       fence_before_sync();
       mbar_arrive(accum_empty + b);
@@ -701,17 +712,17 @@ static int tensor_map(const void* ptr, int rows, int cols, int ld, int box_rows,
 // Upper limit of the ring depth (a tuning knob; MAX_STAGES by default).
 static int g_stage_limit = MAX_STAGES;
 
-template <int BN, bool SWAP>
+template <int BN, bool SWAP, int MT = 1>
 static int launch(const CUtensorMap& ma, const CUtensorMap& mb, Params& p, cudaStream_t stream) {
-  using S = Smem<BN>;
+  using S = Smem<BN, MT>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, SWAP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, SWAP, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          S::total(S::max_stages(1)));
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  const long units = (long)((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * p.splits;
+  const long units = (long)((p.M + MT * BM - 1) / (MT * BM)) * ((p.N + BN - 1) / BN) * p.splits;
   if (units > 0x7fffffffL) return WPC_ERR_TOO_LARGE;
   // Many tiles in the normal arrangement: one persistent CTA per SM walks the tiles, its
   // epilogue overlapping the next tile's MMAs.  Otherwise one CTA per unit; if those are few,
@@ -733,7 +744,7 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, Params& p, cudaS
   constexpr int RED_STAGE_BYTES = 4 * 32 * 33 * 4;
   const bool red_stage = !SWAP && p.accumulate && (p.splits > 1 || p.stream_k);
   if (red_stage && S::total(stages) + RED_STAGE_BYTES > S::total(S::max_stages(1))) p.stages = --stages;
-  wpc::launch(gemm_tc_kernel<BN, SWAP>, grid, THREADS, S::total(stages) + (red_stage ? RED_STAGE_BYTES : 0), stream,
+  wpc::launch(gemm_tc_kernel<BN, SWAP, MT>, grid, THREADS, S::total(stages) + (red_stage ? RED_STAGE_BYTES : 0), stream,
               ma, mb, p);
   return launch_status();
 }
@@ -767,14 +778,16 @@ int wpc_gemm_tc_workspace(int rows_a, int rows_b, int bn, int splits, size_t* sc
 // gated = 1: the weights hold gate and up rows interleaved in blocks of 64 features (64 gate
 // rows, then the 64 up rows of the same features); out is [tokens, features / 2] bfloat16 =
 // silu(gate) * up.  Needs no split and no bias, and bn >= 128 in the normal arrangement.
+// tall = 1 (normal arrangement, bn 256, no split): 256 x 256 tiles, see the kernel.
 // prefetch_weights = 1 promises that the weights are not written by earlier work still in
 // flight on the stream (model parameters): their first tiles are then fetched before the
 // preceding kernel has finished.
 int wpc_gemm_tc(const void* a, int lda, int rows_a, const void* b, int ldb, int rows_b, int K, const float* bias,
                 void* out, int out_dtype, int ldc, int accumulate, int gated, int swap, int bn, int splits,
                 float* scratch, size_t scratch_floats, int* counters, int n_counters, int* status,
-                int prefetch_weights, cudaStream_t stream) {
+                int prefetch_weights, int tall, cudaStream_t stream) {
   if (rows_a <= 0 || rows_b <= 0) return 0;
+  if (tall && (swap || bn != 256 || splits > 1)) return WPC_ERR_UNSUPPORTED;
   if (K <= 0 || (lda % 8) || (ldb % 8) || (((uintptr_t)a) & 15) || (((uintptr_t)b) & 15)) return WPC_ERR_UNSUPPORTED;
   if (accumulate && out_dtype != WPC_DTYPE_F32) return WPC_ERR_BAD_ARGUMENT;
   Params p;
@@ -797,7 +810,7 @@ int wpc_gemm_tc(const void* a, int lda, int rows_a, const void* b, int ldb, int 
     if (!scratch || !counters || need_f > scratch_floats || need_c > n_counters) return WPC_ERR_TOO_LARGE;
   }
   CUtensorMap ma, mb;
-  int rc = tensor_map(a, rows_a, K, lda, BM, &ma);
+  int rc = tensor_map(a, rows_a, K, lda, tall ? 2 * BM : BM, &ma);
   if (rc) return rc;
   rc = tensor_map(b, rows_b, K, ldb, bn, &mb);
   if (rc) return rc;
@@ -808,7 +821,7 @@ int wpc_gemm_tc(const void* a, int lda, int rows_a, const void* b, int ldb, int 
       case 160: return launch<160, false>(ma, mb, p, stream);
       case 192: return launch<192, false>(ma, mb, p, stream);
       case 224: return launch<224, false>(ma, mb, p, stream);
-      case 256: return launch<256, false>(ma, mb, p, stream);
+      case 256: return tall ? launch<256, false, 2>(ma, mb, p, stream) : launch<256, false>(ma, mb, p, stream);
     }
   } else {
     switch (bn) {
