@@ -112,9 +112,11 @@ def _run_batch_pipelined(engine, live, entries, opts, stop, outputs, stats) -> N
     first = True
     t0 = time.perf_counter()
     logits = engine.step(entries)
+    pinned = torch.empty(len(live), dtype=torch.int32, pin_memory=True)   # pageable memory would make the copy block
     while live:
         ids = engine.sample(logits, [s.slot for s in live], opts.temperature, opts.banned_token_ids)
-        host_ids = ids.to("cpu", non_blocking=True)
+        host_ids = pinned[: len(live)]
+        host_ids.copy_(ids, non_blocking=True)
         done_event = torch.cuda.Event()
         done_event.record()
         # who would go on if the token just drawn is no stop token
