@@ -14,10 +14,11 @@
 //
 // The running maximum that the exponentials use is only raised when the true maximum has
 // grown by more than 8 (a factor 256, harmless in float32); then the thread rescales its row
-// of O in tensor memory.  The steps of a page follow one another; two CTAs share an SM, so
-// that one's matrix products run while the other does its softmax.  Pages are copied with
-// cp.async into swizzled shared memory, one page ahead.  Every wait on the MMA barrier is
-// bounded.  head_dim 64 or 128; other sizes take the mma.sync kernel.
+// of O in tensor memory.  There are two score buffers: while the threads do the softmax of
+// page j, the tensor pipe computes the scores of page j + 1 and the weighted values of page
+// j - 1; two CTAs share an SM on top of that.  Pages are copied with cp.async into swizzled
+// shared memory a whole page ahead.  Every wait on an MMA barrier is bounded.  head_dim 64
+// or 128; other sizes take the mma.sync kernel.
 #include "api.h"
 #include "common.cuh"
 
@@ -146,7 +147,7 @@ struct Cfg {
   static constexpr int P_BYTES = ROWS * 128;
   // 896 bytes of slack bring the 128-byte aligned start to a 1024-byte boundary; two CTAs fit an SM
   static constexpr int SMEM = 896 + Q_BYTES + 4 * PAGE_BYTES + P_BYTES + 64;
-  static constexpr int TMEM_COLS = HD == 128 ? 256 : 128;  // 64 for S, HD for O, a power of two
+  static constexpr int TMEM_COLS = 256;                   // two S buffers of 64, HD for O; a power of two
 };
 
 // Copies one page ([64, HD] contiguous) into NB swizzled [64, 64] blocks.
@@ -186,12 +187,15 @@ prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat
   const uint32_t v_s = k_s + 2 * C::PAGE_BYTES;       // two stages
   uint8_t* p_ptr = base + C::Q_BYTES + 4 * C::PAGE_BYTES;
   const uint32_t p_s = smem_u32(p_ptr);
-  uint64_t* bar = (uint64_t*)(p_ptr + C::P_BYTES);
-  uint32_t* tmem_holder = (uint32_t*)(bar + 1);
+  uint64_t* bar_s = (uint64_t*)(p_ptr + C::P_BYTES);      // [2]: the scores in buffer b are ready
+  uint64_t* bar_o = bar_s + 2;                             // the weighted values of a page are added
+  uint32_t* tmem_holder = (uint32_t*)(bar_o + 1);
   int* failed = (int*)(tmem_holder + 1);
 
   if (tid == 0) {
-    mbar_init(bar, 1);
+    mbar_init(bar_s, 1);
+    mbar_init(bar_s + 1, 1);
+    mbar_init(bar_o, 1);
     *failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -226,77 +230,84 @@ prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat
   const int tile_lo = (window > 0 && tile_pos_lo - window + 1 > 0) ? tile_pos_lo - window + 1 : 0;
   const int blk0 = tile_lo / PAGE, blk1 = tile_pos_hi / PAGE + 1;
 
-  {
-    const size_t src0 = (size_t)max(table[blk0], 0) * page_elems + (size_t)g * PAGE * HD;
-    load_page<HD>(k_s, k_pages + src0, tid);
-    load_page<HD>(v_s, v_pages + src0, tid);
-  }
+  // ---- copies ahead: K of pages 0 and 1, V of page 0 (one cp.async group each) ----
+  const int n_pg = blk1 - blk0;
+  auto page_src = [&](int j) { return (size_t)max(table[blk0 + j], 0) * page_elems + (size_t)g * PAGE * HD; };
+  load_page<HD>(k_s, k_pages + page_src(0), tid);
+  cp_async_commit();
+  load_page<HD>(v_s, v_pages + page_src(0), tid);
+  cp_async_commit();
+  if (n_pg > 1) load_page<HD>(k_s + C::PAGE_BYTES, k_pages + page_src(1), tid);
   cp_async_commit();
 
   fence_before_sync();
   __syncthreads();
   fence_after_sync();
   const uint32_t tmem_base = *tmem_holder;
-  const uint32_t tmem_S = tmem_base;                 // columns 0..63
-  const uint32_t tmem_O = tmem_base + 64;            // columns 64..64+HD-1
+  const uint32_t tmem_S = tmem_base;                 // two score buffers: columns 0..63 and 64..127
+  const uint32_t tmem_O = tmem_base + 128;           // columns 128..128+HD-1
   const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
 
   constexpr uint32_t idesc_qk = instr_desc(64, false);
   constexpr uint32_t idesc_pv = instr_desc(HD, true);
   float m_used = -INFINITY, l_sum = 0.f;
-  uint32_t phase = 0;
   bool ok = true;
 
-  for (int blk = blk0; blk < blk1 && ok; ++blk) {
-    const int st = (blk - blk0) & 1;
-    if (blk + 1 < blk1) {
-      const size_t src = (size_t)max(table[blk + 1], 0) * page_elems + (size_t)g * PAGE * HD;
-      load_page<HD>(k_s + (st ^ 1) * C::PAGE_BYTES, k_pages + src, tid);
-      load_page<HD>(v_s + (st ^ 1) * C::PAGE_BYTES, v_pages + src, tid);
-    }
-    cp_async_commit();
-    cp_async_wait<1>();
-    fence_async_smem();                               // what this thread wrote is visible to the MMA
-    __syncthreads();
-
-    // ---- S = Q K^T ----
-    if (tid == 0) {
-      fence_after_sync();
+  // S_j = Q K_j^T into score buffer j & 1 (issued by one thread)
+  auto issue_qk = [&](int j) {
+    fence_after_sync();
 #pragma unroll
-      for (int kk = 0; kk < HD / 16; ++kk) {
-        const uint32_t qa = q_s + (kk >> 2) * (ROWS * 128) + (kk & 3) * 32;
-        const uint32_t ka = k_s + st * C::PAGE_BYTES + (kk >> 2) * (PAGE * 128) + (kk & 3) * 32;
-        umma_bf16(tmem_S, smem_desc(qa, 16), smem_desc(ka, 16), idesc_qk, kk > 0 ? 1u : 0u);
-      }
-      umma_commit(bar);
+    for (int kk = 0; kk < HD / 16; ++kk) {
+      const uint32_t qa = q_s + (kk >> 2) * (ROWS * 128) + (kk & 3) * 32;
+      const uint32_t ka = k_s + (j & 1) * C::PAGE_BYTES + (kk >> 2) * (PAGE * 128) + (kk & 3) * 32;
+      umma_bf16(tmem_S + (j & 1) * 64, smem_desc(qa, 16), smem_desc(ka, 16), idesc_qk, kk > 0 ? 1u : 0u);
     }
-    ok = mbar_wait(bar, phase);
-    phase ^= 1;
+    umma_commit(bar_s + (j & 1));
+  };
+
+  // The products of page j + 1 (scores) and of page j - 1 (weighted values) run on the tensor
+  // pipe while the threads do the softmax of page j; copies are issued a whole page ahead.
+  for (int j = 0; j < n_pg; ++j) {
+    // (A) everything copied so far is in shared memory; start the scores of the next page
+    cp_async_wait<0>();
+    fence_async_smem();
+    fence_before_sync();
+    __syncthreads();
+    if (tid == 0 && j == 0) issue_qk(0);
+    if (tid == 0 && j + 1 < n_pg) issue_qk(j + 1);
+
+    // (B) the scores of this page
+    ok = mbar_wait(bar_s + (j & 1), (j >> 1) & 1);
     ok = __all_sync(0xffffffffu, ok);
     if (!ok) { atomicExch(failed, 1); break; }
     fence_after_sync();
+    if (j + 2 < n_pg) load_page<HD>(k_s + (j & 1) * C::PAGE_BYTES, k_pages + page_src(j + 2), tid);   // K_j has been read
+    cp_async_commit();
 
-    // ---- softmax of this thread's row ----
+    // (C) softmax of this thread's row, in registers
     uint32_t su[64];
-    tmem_ld32(tmem_S + lane_off, su);
-    tmem_ld32(tmem_S + lane_off + 32, su + 32);
+    tmem_ld32(tmem_S + (j & 1) * 64 + lane_off, su);
+    tmem_ld32(tmem_S + (j & 1) * 64 + lane_off + 32, su + 32);
     tmem_ld_wait();
-    const int abs0 = blk * PAGE;
+    const int abs0 = (blk0 + j) * PAGE;
     // raw scores; the scale (positive) goes into the exponent's multiply-add.  Only pages that
     // this row does not see whole are masked.
-    float mx = -INFINITY;
+    // four partial maxima (and sums below): a single running value would be a chain of 64
+    // dependent instructions
+    float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
     if (valid && abs0 + PAGE - 1 <= p_row && abs0 >= lo_row) {
 #pragma unroll
-      for (int j = 0; j < 64; ++j) mx = fmaxf(mx, __uint_as_float(su[j]));
+      for (int i = 0; i < 64; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(su[i]));
     } else {
 #pragma unroll
-      for (int j = 0; j < 64; ++j) {
-        const int kabs = abs0 + j;
-        const float s = (valid && kabs >= lo_row && kabs <= p_row) ? __uint_as_float(su[j]) : -INFINITY;
-        su[j] = __float_as_uint(s);
-        mx = fmaxf(mx, s);
+      for (int i = 0; i < 64; ++i) {
+        const int kabs = abs0 + i;
+        const float sc = (valid && kabs >= lo_row && kabs <= p_row) ? __uint_as_float(su[i]) : -INFINITY;
+        su[i] = __float_as_uint(sc);
+        mx4[i & 3] = fmaxf(mx4[i & 3], sc);
       }
     }
+    float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
     mx *= scale_log2;
     // raise the maximum in use only when the true one has outgrown it
     float alpha = 1.f;
@@ -306,6 +317,30 @@ prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat
       rescale = m_used != -INFINITY;
       m_used = mx;
     }
+    l_sum *= alpha;
+    const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;     // all scores are -inf then: p = 0
+    float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+    uint32_t pw[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const float p0 = exp2f(fmaf(__uint_as_float(su[2 * i]), scale_log2, neg_m));
+      const float p1 = exp2f(fmaf(__uint_as_float(su[2 * i + 1]), scale_log2, neg_m));
+      sum4[i & 3] += p0 + p1;
+      const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
+      pw[i] = *(const uint32_t*)&pb;
+    }
+    const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+    l_sum += sum;
+
+    // (D) the weighted values of the page before must be done before O and P are touched
+    if (j > 0) {
+      ok = mbar_wait(bar_o, (j - 1) & 1);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) { atomicExch(failed, 1); break; }
+      fence_after_sync();
+    }
+    if (j + 1 < n_pg) load_page<HD>(v_s + ((j + 1) & 1) * C::PAGE_BYTES, v_pages + page_src(j + 1), tid);   // V_{j-1} has been read
+    cp_async_commit();
     if (__any_sync(0xffffffffu, rescale)) {
       // the whole warp takes part (tcgen05.ld/st are warp-wide); rows that keep their maximum use 1
       const float a = rescale ? alpha : 1.f;
@@ -315,50 +350,37 @@ prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat
         tmem_ld32(tmem_O + lane_off + c, ou);
         tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 32; ++j) ou[j] = __float_as_uint(__uint_as_float(ou[j]) * a);
+        for (int i = 0; i < 32; ++i) ou[i] = __float_as_uint(__uint_as_float(ou[i]) * a);
         tmem_st32(tmem_O + lane_off + c, ou);
       }
       tmem_st_wait();
     }
-    l_sum *= alpha;
-    const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;     // all scores are -inf then: p = 0
-    float sum = 0.f;
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {
-      uint32_t w[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float p0 = exp2f(fmaf(__uint_as_float(su[c * 8 + 2 * j]), scale_log2, neg_m));
-        const float p1 = exp2f(fmaf(__uint_as_float(su[c * 8 + 2 * j + 1]), scale_log2, neg_m));
-        sum += p0 + p1;
-        const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
-        w[j] = *(const uint32_t*)&pb;
-      }
-      *(uint4*)(p_ptr + swz(tid, c)) = make_uint4(w[0], w[1], w[2], w[3]);
-    }
-    l_sum += sum;
+    for (int c = 0; c < 8; ++c)
+      *(uint4*)(p_ptr + swz(tid, c)) = make_uint4(pw[4 * c], pw[4 * c + 1], pw[4 * c + 2], pw[4 * c + 3]);
     fence_before_sync();
     fence_async_smem();
     __syncthreads();
 
-    // ---- O += P V ----
+    // (E) O += P V_j
     if (tid == 0) {
       fence_after_sync();
 #pragma unroll
       for (int kc = 0; kc < PAGE / 16; ++kc) {
         const uint32_t pa = p_s + kc * 32;
-        const uint32_t va = v_s + st * C::PAGE_BYTES + kc * 2048;
-        umma_bf16(tmem_O, smem_desc(pa, 16), smem_desc(va, PAGE * 128), idesc_pv, (blk > blk0 || kc > 0) ? 1u : 0u);
+        const uint32_t va = v_s + (j & 1) * C::PAGE_BYTES + kc * 2048;
+        umma_bf16(tmem_O, smem_desc(pa, 16), smem_desc(va, PAGE * 128), idesc_pv, (j > 0 || kc > 0) ? 1u : 0u);
       }
-      umma_commit(bar);
+      umma_commit(bar_o);
     }
-    ok = mbar_wait(bar, phase);
-    phase ^= 1;
-    ok = __all_sync(0xffffffffu, ok);
-    if (!ok) { atomicExch(failed, 1); break; }
-    fence_after_sync();
   }
   cp_async_wait<0>();
+  if (ok) {
+    ok = mbar_wait(bar_o, (n_pg - 1) & 1);
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok) atomicExch(failed, 1);
+    fence_after_sync();
+  }
 
   if (ok) {
     const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;

@@ -774,7 +774,7 @@ int wpc_gemm_tc_workspace(int rows_a, int rows_b, int bn, int splits, size_t* sc
 
 // a: [rows_a, K] bfloat16, row stride lda; b: [rows_b, K] bfloat16, row stride ldb.
 // swap = 0: out[rows_a, rows_b] (bias over rows_b);  swap = 1: out[rows_b, rows_a] (bias over
-// rows_a).  bn: the tile's extent along rows_b (16, 32, 64, 128; also 160, 192, 224, 256 without swap).
+// rows_a).  bn: the tile's extent along rows_b (16, 32, 64, 128; 256 without swap).
 // gated = 1: the weights hold gate and up rows interleaved in blocks of 64 features (64 gate
 // rows, then the 64 up rows of the same features); out is [tokens, features / 2] bfloat16 =
 // silu(gate) * up.  Needs no split and no bias, and bn >= 128 in the normal arrangement.
@@ -814,14 +814,13 @@ int wpc_gemm_tc(const void* a, int lda, int rows_a, const void* b, int ldb, int 
   if (rc) return rc;
   rc = tensor_map(b, rows_b, K, ldb, bn, &mb);
   if (rc) return rc;
-  if (!swap) {
+  if (!swap && tall) {
+    if (bn == 256) return launch<256, false, 2>(ma, mb, p, stream);
+  } else if (!swap) {
     switch (bn) {
       case 64: return launch<64, false>(ma, mb, p, stream);
       case 128: return launch<128, false>(ma, mb, p, stream);
-      case 160: return launch<160, false>(ma, mb, p, stream);
-      case 192: return launch<192, false>(ma, mb, p, stream);
-      case 224: return launch<224, false>(ma, mb, p, stream);
-      case 256: return tall ? launch<256, false, 2>(ma, mb, p, stream) : launch<256, false>(ma, mb, p, stream);
+      case 256: return launch<256, false>(ma, mb, p, stream);
     }
   } else {
     switch (bn) {

@@ -201,7 +201,9 @@ def plan_tensor_core_linear(M: int, N: int, K: int):
         tiles = m_tiles * ((N + bn - 1) // bn)
     splits = 1
     if tiles * 2 <= _SMS:
-        splits = max(1, min(_SMS // tiles, k_blocks // 4, 16))
+        # about one CTA to an SM; with many tokens (wide tiles, much activation traffic) two
+        ctas = 2 * _SMS if (swap and M > 32) else _SMS
+        splits = max(1, min(ctas // tiles, k_blocks // 4, 16))
         while splits > 1 and tiles * splits * bn * 128 > _WORKSPACE_FLOATS:
             splits -= 1
         if tiles > _WORKSPACE_COUNTERS:
@@ -209,17 +211,20 @@ def plan_tensor_core_linear(M: int, N: int, K: int):
     return swap, bn, splits
 
 
-def tall_tiles(M: int, N: int, swap: bool, bn: int, splits: int, K: int = 0, accumulate: bool = False) -> bool:
-    """Whether the product takes 256 x 256 tiles (two MMAs share each weight tile, a third less
-    operand traffic) instead of 128 x 256: when they make one wave that covers at least half of
-    the SMs.  With more tiles than SMs the 128 x 256 tiles win, because their epilogue overlaps
-    the next tile (measured: 1.30 against 1.27 PFLOP/s at 2,048 tokens, 1.27 against 0.94 at 8,192).
-    A product that adds into the residual stream and has a short K stays with 128 x 256 too: its
-    read-modify-write epilogue is not hidden in a tall tile (0.73 against 0.78 PFLOP/s)."""
+def tall_tiles(M: int, N: int, swap: bool, bn: int, splits: int, K: int = 0, accumulate: bool = False) -> int:
+    """The width of 256-row tiles for this product (256), or 0 to keep 128 x bn tiles.  In a
+    256-row tile two MMAs share each weight tile (a third less operand traffic per flop).  They
+    are used when all tiles make a single wave that covers at least half of the SMs.  Measured
+    at 2,048 tokens of the 7B shape: qkv 1.36 against 1.19 PFLOP/s, down 1.20 against 1.05.
+    With more tiles than SMs the 128 x 256 tiles win, because their epilogue overlaps the next
+    tile (1.27 against 0.94 PFLOP/s at 8,192 tokens); a product that adds into the residual
+    stream with a short K keeps them too (its read-modify-write epilogue is not hidden in a
+    tall tile: 0.73 against 0.78); narrower tall tiles that would fill the wave better (208
+    wide for 3584 features) were slower (0.47 and 1.09 against 0.78 and 1.20)."""
     if swap or bn != 256 or splits != 1 or M < 256 or (accumulate and K < 8192):
-        return False
+        return 0
     tiles = ((M + 255) // 256) * ((N + 255) // 256)
-    return _SMS // 2 <= tiles <= _SMS
+    return 256 if _SMS // 2 <= tiles <= _SMS else 0
 
 
 def _tensor_core_linear(x, w, bias, out, accumulate, static_weight=False) -> bool:
@@ -230,6 +235,9 @@ def _tensor_core_linear(x, w, bias, out, accumulate, static_weight=False) -> boo
     if K % 8 or x.stride(0) % 8 or w.stride(0) % 8 or x.data_ptr() % 16 or w.data_ptr() % 16:
         return False
     swap, bn, splits = plan_tensor_core_linear(M, N, K)
+    tall = tall_tiles(M, N, swap, bn, splits, K, bool(accumulate))
+    if tall:
+        bn = tall
     scratch, counters, status = workspace(x.device)
     if swap:
         a, b = w, x
@@ -238,7 +246,7 @@ def _tensor_core_linear(x, w, bias, out, accumulate, static_weight=False) -> boo
     _check("gemm_tc", library().wpc_gemm_tc(
         _p(a), a.stride(0), a.shape[0], _p(b), b.stride(0), b.shape[0], K, _p(bias), _p(out), _code(out.dtype),
         out.stride(0), accumulate, 0, int(swap), bn, splits, _p(scratch), ctypes.c_size_t(scratch.numel()),
-        _p(counters), counters.numel(), _p(status), int(static_weight), int(tall_tiles(M, N, swap, bn, splits, K, bool(accumulate))),
+        _p(counters), counters.numel(), _p(status), int(static_weight), int(bool(tall)),
         _stream()))
     return True
 
@@ -272,13 +280,14 @@ def gated_linear(x: torch.Tensor, w: torch.Tensor, inner: int, group: int, plain
             and w.data_ptr() % 16 == 0 and M > 0):
         swap = M <= 128
         bn = (16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128) if swap else (256 if (2 * inner) % 256 == 0 else 128)
+        tall = tall_tiles(M, 2 * inner, swap, bn, 1) == 256      # the gated epilogue needs whole 128-column groups
         out = torch.empty((M, inner), dtype=torch.bfloat16, device=x.device)
         scratch, counters, status = workspace(x.device)
         a, b = (w, x) if swap else (x, w)
         _check("gemm_tc", library().wpc_gemm_tc(
             _p(a), a.stride(0), a.shape[0], _p(b), b.stride(0), b.shape[0], K, _p(None), _p(out), _BF16,
             out.stride(0), 0, 1, int(swap), bn, 1, _p(scratch), ctypes.c_size_t(scratch.numel()), _p(counters),
-            counters.numel(), _p(status), int(static_weight), int(tall_tiles(M, 2 * inner, swap, bn, 1)), _stream()))
+            counters.numel(), _p(status), int(static_weight), int(tall), _stream()))
         return out
     return silu_mul(linear(x, w, plain=plain, static_weight=static_weight), inner, group)
 
