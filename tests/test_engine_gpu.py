@@ -200,3 +200,41 @@ def test_errors_are_loud(engines):
         small.open_sequence()
     small.close_sequence(a)
     assert small.step([SequenceStep(b, [3], want=[0])]).shape == (1, 256)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_prompt_in_chunks(tmp_path_factory, dtype):
+    """A 5,000-token request fed in chunks of 1,024 and then one token at a time, beside a
+    short request: many pages, chunks that attend to a deep cache, long decode contexts."""
+    from conftest import make_folder
+    from wpc_engine_b200 import SequenceStep
+    raw = dict(architectures=["Qwen2ForCausalLM"], num_hidden_layers=2, hidden_size=128, num_attention_heads=2,
+               num_key_value_heads=1, intermediate_size=192, vocab_size=500, rope_theta=1e6, rms_norm_eps=1e-6,
+               max_position_embeddings=8192, tie_word_embeddings=True)
+    folder = make_folder(tmp_path_factory, raw, 21, getattr(torch, dtype))
+    eng = Engine.from_folder(folder, dtype=dtype, max_tokens=8192)
+    long_req, short_req = random_tokens(500, 5008, 900), random_tokens(500, 40, 901)
+    want = P.forward(*P.read_model_folder(folder), long_req, np.float64)
+    a, b = eng.open_sequence(), eng.open_sequence()
+    rows = []
+    try:
+        fed = 0
+        while fed < 5000:
+            n = min(1024, 5000 - fed)
+            entries = [SequenceStep(a, long_req[fed:fed + n], want=[n - 1])]
+            if fed == 0:
+                entries.append(SequenceStep(b, short_req, want=[]))
+            rows.append((fed + n - 1, eng.step(entries).float().cpu().numpy()[0]))
+            fed += n
+        for i in range(5000, 5008):
+            out = eng.step([SequenceStep(a, [long_req[i]], want=[0]), SequenceStep(b, [short_req[i % 40]], want=[0])])
+            rows.append((i, out.float().cpu().numpy()[0]))
+    finally:
+        eng.close_sequence(a)
+        eng.close_sequence(b)
+    bound = 4 * np.abs(P.forward(*P.read_model_folder(folder), long_req[:600], np.float32)
+                       - want[:600]).max() + 1e-5 if dtype == "float32" else 0.03 * want.std() + 0.02 * np.abs(want).max()
+    for place, got in rows:
+        err = np.abs(got - want[place]).max()
+        assert err <= bound, (place, err, bound)
+    eng.cache.check()
