@@ -191,6 +191,7 @@ __device__ __forceinline__ void load_q(uint32_t (&qf)[HD / 16][4], const __nv_bf
 // c for pair k lives at slot c + k (consecutive pairs share at most one CTA, so slots are unique).
 constexpr int MAX_DECODE_SEQS = 1024;
 constexpr int DECODE_STAGES = 3;
+constexpr int MAX_SEGMENT_PAGES = 512;
 
 template <int HD>
 __global__ void __launch_bounds__(THREADS)
@@ -198,13 +199,17 @@ decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* 
               const __nv_bfloat16* __restrict__ k_pages, const __nv_bfloat16* __restrict__ v_pages,
               const int* __restrict__ page_table, int table_width, const int* __restrict__ ctx_lens, int B,
               int nh, int nkv, float scale_log2, int window, float* __restrict__ part_o,
-              float* __restrict__ part_ml, int* __restrict__ counters) {
+              float* __restrict__ part_ml, int* __restrict__ counters, int smem_bytes) {
   pdl_trigger();
-  pdl_wait();
+  // The step's lengths and page tables were written before the step began, and every page but
+  // the last of a sequence holds positions of earlier steps: the division of the work and the
+  // first copies can start before the kernel ahead (which writes this step's queries, key and
+  // value) has finished.
   extern __shared__ __align__(16) uint8_t smem_raw[];
   __nv_bfloat16* ks = (__nv_bfloat16*)smem_raw;                       // [DECODE_STAGES][PAGE][STRIDE]
   __nv_bfloat16* vs = ks + DECODE_STAGES * Cfg<HD>::PAGE_ELEMS;
   __shared__ int s_cum[MAX_DECODE_SEQS + 1];                          // units before each sequence
+  __shared__ int s_pages[MAX_SEGMENT_PAGES];                          // page numbers of the current segment
   __shared__ int s_last;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_rep = nh / nkv;
@@ -241,6 +246,7 @@ decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* 
   const int per = (U + (int)gridDim.x - 1) / (int)gridDim.x;
   const int u0 = blockIdx.x * per, u1 = min(U, u0 + per);
   if (per == 0 || u0 >= u1) return;
+  bool waited = false;                                  // pdl_wait() done (it comes before the first read of this step's data)
 
   // the sequence that holds unit u0
   int b = 0;
@@ -269,8 +275,34 @@ decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* 
     const int pos = L - 1;
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
     const int blk0 = lo / PAGE + pg, blk1 = blk0 + (seg_end - u);
-    const int* table = page_table + (size_t)b * table_width;
+    // the segment's page numbers go to shared memory at once: a lookup per page in the loop
+    // would put a trip to L2 before every copy
+    const int* gtable = page_table + (size_t)b * table_width + blk0;
+    const int n_seg = blk1 - blk0;
+    for (int i = tid; i < min(n_seg, MAX_SEGMENT_PAGES); i += THREADS) s_pages[i] = gtable[i];
+    __syncthreads();
+    auto page_of = [&](int blk) { const int i = blk - blk0; return i < MAX_SEGMENT_PAGES ? s_pages[i] : gtable[i]; };
 
+    const int last_blk = pos / PAGE;                     // the page that this step writes to
+    // a ring of DECODE_STAGES pages: two are in flight while one is computed.  Pages of earlier
+    // steps may be copied before the wait for the kernel ahead.
+    if (!waited && (blk0 == last_blk || (blk0 + 1 < blk1 && blk0 + 1 == last_blk))) {
+      pdl_wait();
+      waited = true;
+    }
+#pragma unroll
+    for (int i = 0; i < DECODE_STAGES - 1; ++i) {
+      if (blk0 + i < blk1) {
+        const size_t src = (size_t)max(page_of(blk0 + i), 0) * page_elems + (size_t)g * PAGE * HD;
+        load_page<HD>(ks + i * Cfg<HD>::PAGE_ELEMS, k_pages + src, tid);
+        load_page<HD>(vs + i * Cfg<HD>::PAGE_ELEMS, v_pages + src, tid);
+      }
+      cp_async_commit();
+    }
+    if (!waited) {
+      pdl_wait();
+      waited = true;
+    }
     const __nv_bfloat16* qtok = q + (size_t)b * q_stride + (size_t)g * n_rep * HD;
     uint32_t qf[HD / 16][4];
     load_q<HD>(qf, r_lo < n_rep ? qtok + r_lo * HD : nullptr, r_hi < n_rep ? qtok + r_hi * HD : nullptr, lane);
@@ -280,22 +312,11 @@ decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* 
     for (int d = 0; d < HD / 8; ++d)
 #pragma unroll
       for (int i = 0; i < 4; ++i) o[d][i] = 0.f;
-
-    // a ring of DECODE_STAGES pages: two are in flight while one is computed
-#pragma unroll
-    for (int i = 0; i < DECODE_STAGES - 1; ++i) {
-      if (blk0 + i < blk1) {
-        const size_t src = (size_t)max(table[blk0 + i], 0) * page_elems + (size_t)g * PAGE * HD;
-        load_page<HD>(ks + i * Cfg<HD>::PAGE_ELEMS, k_pages + src, tid);
-        load_page<HD>(vs + i * Cfg<HD>::PAGE_ELEMS, v_pages + src, tid);
-      }
-      cp_async_commit();
-    }
     for (int blk = blk0; blk < blk1; ++blk) {
       const int buf = (blk - blk0) % DECODE_STAGES;
       if (blk + DECODE_STAGES - 1 < blk1) {
         const int nbuf = (buf + DECODE_STAGES - 1) % DECODE_STAGES;
-        const size_t src = (size_t)max(table[blk + DECODE_STAGES - 1], 0) * page_elems + (size_t)g * PAGE * HD;
+        const size_t src = (size_t)max(page_of(blk + DECODE_STAGES - 1), 0) * page_elems + (size_t)g * PAGE * HD;
         load_page<HD>(ks + nbuf * Cfg<HD>::PAGE_ELEMS, k_pages + src, tid);
         load_page<HD>(vs + nbuf * Cfg<HD>::PAGE_ELEMS, v_pages + src, tid);
       }
@@ -384,42 +405,66 @@ decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* 
       __syncthreads();
       if (s_last) {
         __threadfence();
-        // maxima and sums of all partial results into shared memory (all loads at once), then a
-        // warp per row turns them into weights, then the outputs with independent loads
+        // All partial results of the pair come into shared memory with one burst of cp.async
+        // (loads through registers would go a few at a time, each batch a trip to L2), in
+        // chunks of as many parts as fit; a warp per row turns maxima and sums into weights.
         const int n_parts = c_last - c_first + 1;
+        const size_t slot0 = (size_t)c_first + pair;
         float* wm = (float*)smem_raw;                      // [16][n_parts] maximum, then the weight
         float* wl = wm + 16 * n_parts;                     // [16][n_parts] sum
         float* winv = wl + 16 * n_parts;                   // [16] 1 / total
-        const size_t slot0 = (size_t)c_first + pair;
-        for (int e = tid; e < n_rep * n_parts; e += THREADS) {
-          const int row = e / n_parts, sidx = e - row * n_parts;
-          const float2 ml = __ldcg((const float2*)(part_ml + ((slot0 + sidx) * 16 + row) * 2));
-          wm[row * n_parts + sidx] = ml.x;
-          wl[row * n_parts + sidx] = ml.y;
-        }
-        __syncthreads();
-        for (int row = warp; row < n_rep; row += THREADS / 32) {
-          float M = -INFINITY;
-          for (int sidx = lane; sidx < n_parts; sidx += 32) M = fmaxf(M, wm[row * n_parts + sidx]);
-          M = warp_max(M);
-          float Lsum = 0.f;
-          for (int sidx = lane; sidx < n_parts; sidx += 32) {
-            const float ms = wm[row * n_parts + sidx];
-            const float f = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
-            wm[row * n_parts + sidx] = f;
-            Lsum += f * wl[row * n_parts + sidx];
+        float* po_s = winv + 16;                           // [chunk][n_rep][HD] partial outputs
+        const int chunk = max(1, min(n_parts, (smem_bytes - (2 * 16 * n_parts + 16) * 4) / (n_rep * HD * 4)));
+        float acc[(16 * HD + THREADS - 1) / THREADS];
+#pragma unroll
+        for (int i = 0; i < (16 * HD + THREADS - 1) / THREADS; ++i) acc[i] = 0.f;
+        for (int s0 = 0; s0 < n_parts; s0 += chunk) {
+          const int ns = min(chunk, n_parts - s0);
+          // rows of HD floats are 16-byte multiples: copy row by row, 16 bytes a thread
+          for (int c = tid; c < ns * n_rep * (HD / 4); c += THREADS) {
+            const int part = c / (n_rep * (HD / 4)), rem = c - part * (n_rep * (HD / 4));
+            cp_async16(po_s + (size_t)part * n_rep * HD + rem * 4, part_o + ((slot0 + s0 + part) * 16) * HD + rem * 4);
           }
-          Lsum = warp_sum(Lsum);
-          if (lane == 0) winv[row] = Lsum > 0.f ? 1.f / Lsum : 0.f;
+          cp_async_commit();
+          if (s0 == 0) {
+            // maxima and sums travel while the copies are in flight
+            for (int e = tid; e < n_rep * n_parts; e += THREADS) {
+              const int row = e / n_parts, sidx = e - row * n_parts;
+              const float2 ml = __ldcg((const float2*)(part_ml + ((slot0 + sidx) * 16 + row) * 2));
+              wm[row * n_parts + sidx] = ml.x;
+              wl[row * n_parts + sidx] = ml.y;
+            }
+            __syncthreads();                               // wm, wl are written
+            for (int row = warp; row < n_rep; row += THREADS / 32) {
+              float M = -INFINITY;
+              for (int sidx = lane; sidx < n_parts; sidx += 32) M = fmaxf(M, wm[row * n_parts + sidx]);
+              M = warp_max(M);
+              float Lsum = 0.f;
+              for (int sidx = lane; sidx < n_parts; sidx += 32) {
+                const float ms = wm[row * n_parts + sidx];
+                const float f = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
+                wm[row * n_parts + sidx] = f;
+                Lsum += f * wl[row * n_parts + sidx];
+              }
+              Lsum = warp_sum(Lsum);
+              if (lane == 0) winv[row] = Lsum > 0.f ? 1.f / Lsum : 0.f;
+            }
+          }
+          cp_async_wait<0>();
+          __syncthreads();
+          int i = 0;
+          for (int e = tid; e < n_rep * HD; e += THREADS, ++i) {
+            const int row = e / HD;
+            float a = acc[i];
+            for (int sidx = 0; sidx < ns; ++sidx) a += wm[row * n_parts + s0 + sidx] * po_s[(size_t)sidx * n_rep * HD + e];
+            acc[i] = a;
+          }
+          __syncthreads();                                 // po_s is reused by the next chunk
         }
-        __syncthreads();
-        for (int e = tid; e < n_rep * HD; e += THREADS) {
+        int i = 0;
+        for (int e = tid; e < n_rep * HD; e += THREADS, ++i) {
           const int row = e / HD, d = e - row * HD;
-          const float* po = part_o + (slot0 * 16 + row) * HD + d;
-          float acc = 0.f;
-#pragma unroll 8
-          for (int sidx = 0; sidx < n_parts; ++sidx) acc += wm[row * n_parts + sidx] * __ldcg(po + (size_t)sidx * 16 * HD);
-          out[(size_t)b * out_stride + (size_t)(g * n_rep + row) * HD + d] = __float2bfloat16_rn(acc * winv[row]);
+          out[(size_t)b * out_stride + (size_t)(g * n_rep + row) * HD + d] = __float2bfloat16_rn(acc[i] * winv[row]);
         }
       }
     }
@@ -555,7 +600,7 @@ static int launch_decode(const void* q, int q_stride, void* out, int out_stride,
                          int* counters, cudaStream_t stream) {
   // shared memory: the page buffers, reused for the merge of the warps and for the combine
   const int merge_bytes = (4 * 16 * HD + 2 * 4 * 16) * (int)sizeof(float);
-  const int combine_bytes = (2 * 16 * n_ctas + 16) * (int)sizeof(float);
+  const int combine_bytes = (2 * 16 * n_ctas + 16 + 16 * HD) * (int)sizeof(float);   // weights and room for one part
   int smem = DECODE_STAGES * 2 * Cfg<HD>::PAGE_ELEMS * 2;
   if (merge_bytes > smem) smem = merge_bytes;
   if (combine_bytes > smem) smem = combine_bytes;
@@ -568,7 +613,7 @@ static int launch_decode(const void* q, int q_stride, void* out, int out_stride,
   wpc::launch(decode_kernel<HD>, dim3(n_ctas), THREADS, smem, stream, 
       (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pages,
       (const __nv_bfloat16*)v_pages, page_table, table_width, ctx_lens, B, nh, nkv, scale * LOG2E, window,
-      part_o, part_ml, counters);
+      part_o, part_ml, counters, smem);
   return launch_status();
 }
 
