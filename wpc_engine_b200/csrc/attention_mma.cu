@@ -201,10 +201,10 @@ decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* 
               int nh, int nkv, float scale_log2, int window, float* __restrict__ part_o,
               float* __restrict__ part_ml, int* __restrict__ counters, int smem_bytes) {
   pdl_trigger();
-  // The step's lengths and page tables were written before the step began, and every page but
-  // the last of a sequence holds positions of earlier steps: the division of the work and the
-  // first copies can start before the kernel ahead (which writes this step's queries, key and
-  // value) has finished.
+  // Nothing of the cache is read before the kernel ahead has finished: copying pages of earlier
+  // positions ahead of this wait gave wrong results under CUDA graphs (cause not found), and
+  // it saved about a microsecond.
+  pdl_wait();
   extern __shared__ __align__(16) uint8_t smem_raw[];
   __nv_bfloat16* ks = (__nv_bfloat16*)smem_raw;                       // [DECODE_STAGES][PAGE][STRIDE]
   __nv_bfloat16* vs = ks + DECODE_STAGES * Cfg<HD>::PAGE_ELEMS;
@@ -246,7 +246,6 @@ decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* 
   const int per = (U + (int)gridDim.x - 1) / (int)gridDim.x;
   const int u0 = blockIdx.x * per, u1 = min(U, u0 + per);
   if (per == 0 || u0 >= u1) return;
-  bool waited = false;                                  // pdl_wait() done (it comes before the first read of this step's data)
 
   // the sequence that holds unit u0
   int b = 0;
@@ -283,13 +282,7 @@ decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* 
     __syncthreads();
     auto page_of = [&](int blk) { const int i = blk - blk0; return i < MAX_SEGMENT_PAGES ? s_pages[i] : gtable[i]; };
 
-    const int last_blk = pos / PAGE;                     // the page that this step writes to
-    // a ring of DECODE_STAGES pages: two are in flight while one is computed.  Pages of earlier
-    // steps may be copied before the wait for the kernel ahead.
-    if (!waited && (blk0 == last_blk || (blk0 + 1 < blk1 && blk0 + 1 == last_blk))) {
-      pdl_wait();
-      waited = true;
-    }
+    // a ring of DECODE_STAGES pages: two are in flight while one is computed
 #pragma unroll
     for (int i = 0; i < DECODE_STAGES - 1; ++i) {
       if (blk0 + i < blk1) {
@@ -298,10 +291,6 @@ decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* 
         load_page<HD>(vs + i * Cfg<HD>::PAGE_ELEMS, v_pages + src, tid);
       }
       cp_async_commit();
-    }
-    if (!waited) {
-      pdl_wait();
-      waited = true;
     }
     const __nv_bfloat16* qtok = q + (size_t)b * q_stride + (size_t)g * n_rep * HD;
     uint32_t qf[HD / 16][4];
