@@ -201,9 +201,8 @@ def plan_tensor_core_linear(M: int, N: int, K: int):
         tiles = m_tiles * ((N + bn - 1) // bn)
     splits = 1
     if tiles * 2 <= _SMS:
-        # about one CTA to an SM; with many tokens (wide tiles, much activation traffic) two
-        ctas = 2 * _SMS if (swap and M > 32) else _SMS
-        splits = max(1, min(ctas // tiles, k_blocks // 4, 16))
+        # about one CTA to an SM (two to an SM measured slower in a whole step, also with many tokens)
+        splits = max(1, min(_SMS // tiles, k_blocks // 4, 16))
         while splits > 1 and tiles * splits * bn * 128 > _WORKSPACE_FLOATS:
             splits -= 1
         if tiles > _WORKSPACE_COUNTERS:
