@@ -238,3 +238,43 @@ def test_long_prompt_in_chunks(tmp_path_factory, dtype):
         err = np.abs(got - want[place]).max()
         assert err <= bound, (place, err, bound)
     eng.cache.check()
+
+
+def test_medium_model_graphs_and_dependent_launch_change_nothing(tmp_path_factory):
+    """A model large enough for the real tile shapes (split-K products, weight tiles fetched
+    ahead, many CTAs per attention pair, persistent prefill products, tcgen05 attention):
+    single-token steps replayed from graphs with programmatic dependent launch against the same
+    steps launched one by one without it, and both against the float32 path."""
+    from conftest import make_folder
+    from wpc_engine_b200 import SequenceStep, ops
+    raw = dict(architectures=["Qwen2ForCausalLM"], num_hidden_layers=3, hidden_size=1024, num_attention_heads=8,
+               num_key_value_heads=2, intermediate_size=2816, vocab_size=3000, rope_theta=1e6, rms_norm_eps=1e-6,
+               max_position_embeddings=4096, tie_word_embeddings=False, use_sliding_window=True,
+               sliding_window=200, max_window_layers=1)
+    folder = make_folder(tmp_path_factory, raw, 31, torch.bfloat16)
+    reqs = [random_tokens(3000, n, 970 + n) for n in (700, 130, 9, 333)]
+
+    def run(dtype, graphs, pdl):
+        was = ops.set_pdl(pdl)
+        try:
+            eng = Engine.from_folder(folder, dtype=dtype, max_tokens=8192, use_graphs=graphs)
+            slots = [eng.open_sequence() for _ in reqs]
+            out = [eng.step([SequenceStep(s, r, want=[len(r) - 1]) for s, r in zip(slots, reqs)]).float().cpu().numpy()]
+            for i in range(70):          # crosses page boundaries; the first step of a shape runs directly
+                toks = [int(r[(i * 7) % len(r)]) for r in reqs]
+                out.append(eng.step([SequenceStep(s, [t], want=[0]) for s, t in zip(slots, toks)]).float().cpu().numpy())
+            for s in slots:
+                eng.close_sequence(s)
+            eng.cache.check()
+            assert ops.device_status() == 0
+            return np.stack(out)
+        finally:
+            ops.set_pdl(was)
+
+    fast = run("bfloat16", True, True)
+    slow = run("bfloat16", False, False)
+    full = run("float32", False, False)
+    scale = np.abs(full).max()
+    # the same kernels either way: only the order of the red.add shares may differ
+    assert np.abs(fast - slow).max() <= 2e-2 * scale
+    assert np.abs(fast - full).max() <= 6e-2 * scale and np.abs(slow - full).max() <= 6e-2 * scale
