@@ -349,3 +349,44 @@ def test_attention_prefill_tcgen05_growing_maximum():
     got = ops.attention(qkv, nh, nkv, hd, kp, vp, table, cu, ctx, seq, pos, 1.0, None, 520, 520)
     want = ref.attention_plain(qkv.cpu(), nh, nkv, hd, kp.cpu(), vp.cpu(), table.cpu(), seq.cpu(), pos.cpu(), 1.0, None)
     close(got.cpu(), want, torch.bfloat16)
+
+
+# ---- few tokens, K split over the CTAs of a cluster that add up through shared memory -----------
+@pytest.mark.parametrize("M", [1, 7, 16, 33, 64, 100, 128])
+@pytest.mark.parametrize("N,K", [(128, 512), (200, 1032), (1000, 520), (3584, 3584), (130, 4104)])
+def test_few_token_linear_in_clusters(M, N, K):
+    """Every split count that the plan may pick (2..8) and the three kinds of output, against the
+    plain float32 product; sizes that are no multiples of the tile (weights.rs:59-78)."""
+    swap, bn, splits = ops.plan_tensor_core_linear(M, N, K)
+    assert swap
+    x, w = rnd((M, K), torch.bfloat16, 71), rnd((N, K), torch.bfloat16, 72, 0.05)
+    bias = rnd((N,), seed=73)
+    want = ref.linear(x.cpu(), w.cpu(), bias.cpu(), out_dtype=torch.float32)
+    mag = want.abs().max().item()
+    got = ops.linear(x, w, bias, out_dtype=torch.float32)
+    assert (got.cpu() - want).abs().max().item() <= 2e-3 * mag, (bn, splits)
+    got16 = ops.linear(x, w, bias)
+    assert (got16.cpu().float() - want).abs().max().item() <= 1.2e-2 * mag
+    r0 = rnd((M, N), seed=74)
+    acc = ops.linear(x, w, residual=r0.clone())
+    want_acc = r0.cpu() + ref.linear(x.cpu(), w.cpu(), None, out_dtype=torch.float32)
+    assert (acc.cpu() - want_acc).abs().max().item() <= 2e-3 * max(mag, want_acc.abs().max().item())
+    assert torch.equal(ops.linear(x, w, bias, out_dtype=torch.float32), got), "two runs differ"
+    assert ops.device_status() == 0
+
+
+def test_few_token_linear_in_clusters_every_slice_counts():
+    """A single one in x at a k of each slice of K picks one column of w exactly: no slice is
+    lost or added twice, whichever CTA of the cluster holds it."""
+    M, N, K = 5, 300, 2048
+    swap, bn, splits = ops.plan_tensor_core_linear(M, N, K)
+    assert swap and splits >= 2, "this size is meant to be split"
+    w = rnd((N, K), torch.bfloat16, 75)
+    per = -(-(K // 64) // splits) * 64
+    for s in range(splits):
+        for k in (s * per, min(K, (s + 1) * per) - 1):
+            x = torch.zeros((M, K), dtype=torch.bfloat16, device=DEV)
+            x[s % M, k] = 1.0
+            want = torch.zeros((M, N), device=DEV)
+            want[s % M] = w[:, k].float()
+            assert torch.equal(ops.linear(x, w, out_dtype=torch.float32), want), (s, k)

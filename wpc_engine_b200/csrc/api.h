@@ -39,7 +39,8 @@ int wpc_gemm_tc_workspace(int rows_a, int rows_b, int bn, int splits, size_t* sc
 int wpc_gemm_tc(const void* a, int lda, int rows_a, const void* b, int ldb, int rows_b, int K, const float* bias,
                 void* out, int out_dtype, int ldc, int accumulate, int gated, int swap, int bn, int splits,
                 float* scratch, size_t scratch_floats, int* counters, int n_counters, int* status,
-                int prefetch_weights, int tall, cudaStream_t stream);
+                int prefetch_weights, int tall, int cluster, cudaStream_t stream);
+int wpc_gemm_tc_cluster_capacity(int bn, int splits);
 
 int wpc_attention_plain(const void* q, int q_stride, void* out, int out_stride, int dtype, const void* k_pages,
                         const void* v_pages, const int* page_table, int table_width, const int* seq_of_token,

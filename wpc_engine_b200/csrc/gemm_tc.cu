@@ -17,12 +17,19 @@
 //            D^T and the epilogue writes out[token, feature].  This keeps the 128-row MMA
 //            full when there are only a few tokens (decode), so the weights stream once at
 //            full width.
-// With split-K every CTA of a tile writes its partial sums to scratch memory and takes a
-// ticket; the CTA that draws the last ticket adds the partial sums in slice order (so the
-// result does not depend on which CTA came last) and runs the epilogue.  Nobody waits for
-// anybody.  When the product is added to a float32 output anyway, the slices skip all that
-// and add their shares with red.global.add.  Every wait on an mbarrier is bounded: when it runs out the kernel records
+// Split K, three ways.  (1) Swapped arrangement, the usual one for few tokens: the CTAs of a
+// tile form a thread-block cluster (2..8); each puts its partial sums into its shared memory,
+// and after a cluster barrier each adds up, in rank order, a share of the tile's token rows
+// from all peers through distributed shared memory and writes it.  No scratch, no atomics,
+// the same bits every run.  The ring is kept so short that two CTAs fit on an SM.  (2) With
+// tickets: every CTA of a tile writes its partial sums to scratch memory and takes a ticket;
+// the CTA that draws the last ticket adds them in slice order and runs the epilogue.  Nobody
+// waits for anybody.  (3) When the product is added to a float32 output anyway, the slices
+// add their shares with red.global.add (normal arrangement).
+// Every wait on an mbarrier is bounded: when it runs out the kernel records
 // WPC_ERR_DEVICE_WAIT in `status`, lets its copies land, frees its tensor memory and returns.
+// The cluster barriers are hardware barriers that every thread of every CTA reaches on every
+// path (they stand after the roles join), so a CTA that gave up still arrives.
 //
 // The math is the reference's y = W x + b (wpc-runtime/src/weights.rs:59-78) in bfloat16
 // inputs with float32 accumulation.
@@ -109,6 +116,27 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
       : "memory");
+}
+
+// ---- thread-block clusters: barrier over all threads of all CTAs, and loads from a peer's shared memory ----
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// the address, in the cluster's shared window, of this CTA's shared address `addr` in CTA `rank`
+__device__ __forceinline__ uint32_t peer_smem(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ float ld_peer_f32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  return v;
 }
 
 __device__ __forceinline__ void tmem_alloc(uint32_t* holder, int cols) {
@@ -263,7 +291,9 @@ struct WorkIter {
   int u, n_units, stride;      // unit mode
   int g, g1;                   // stream-K mode
   bool stream_k;
-  __device__ WorkIter(const Params& p) {
+  bool split_fastest;          // units count (tile, split) with the split fastest: the CTAs of a cluster share a tile
+  __device__ WorkIter(const Params& p, bool split_fastest_ = false) {
+    split_fastest = split_fastest_;
     tiles_m = (p.M + MT * BM - 1) / (MT * BM);
     n_tiles = tiles_m * ((p.N + BN - 1) / BN);
     k_blocks = p.k_blocks;
@@ -282,8 +312,13 @@ struct WorkIter {
   __device__ bool next(Work& w) {
     if (!stream_k) {
       if (u >= n_units) return false;
-      w.split = u / n_tiles;
-      w.tile_id = u - w.split * n_tiles;
+      if (split_fastest) {
+        w.tile_id = u / splits;
+        w.split = u - w.tile_id * splits;
+      } else {
+        w.split = u / n_tiles;
+        w.tile_id = u - w.split * n_tiles;
+      }
       w.kb0 = w.split * kb_per;
       w.n_kb = max(min(k_blocks, w.kb0 + kb_per) - w.kb0, 0);
       w.partial = splits > 1;
@@ -307,7 +342,10 @@ struct WorkIter {
 // MT = 2: the tile is 256 rows of A by BN; the two 128-row halves are two MMAs that share the B
 // tile in shared memory (a third less operand traffic per flop) and fill both accumulators, so
 // the epilogue does not overlap the next tile.
-template <int BN, bool SWAP, int MT>
+// CL (swapped arrangement, split K): the CTAs that share a tile form a thread-block cluster and add
+// their partial sums through distributed shared memory, in rank order; each CTA writes its
+// share of the tile's token rows.  No scratch, no tickets, no atomics.
+template <int BN, bool SWAP, int MT, bool CL>
 __global__ void __launch_bounds__(THREADS, (BN <= 64 ? 2 : 1))     // narrow tiles run two CTAs to an SM
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
   using S = Smem<BN, MT>;
@@ -349,7 +387,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (lane == 0) {
       int it = 0;                                   // k-blocks loaded so far: position in the ring
       bool ok = true;
-      WorkIter<BN, MT> work(p);
+      WorkIter<BN, MT> work(p, CL);
       Work w;
       bool first = true;
       while (ok && work.next(w)) {
@@ -389,7 +427,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       constexpr uint32_t idesc = instr_desc(BN);
       bool ok = true;
       int it = 0, j = 0;
-      WorkIter<BN, MT> work(p);
+      WorkIter<BN, MT> work(p, CL);
       Work w;
       for (; ok && work.next(w); ++j) {
         const int n_kb = w.n_kb;
@@ -425,7 +463,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int r = q * 32 + lane;                        // row of the tile = TMEM lane
     const int et = threadIdx.x - 64;                    // 0..127 among the epilogue threads
     int j = 0;
-    WorkIter<BN, MT> work(p);
+    WorkIter<BN, MT> work(p, CL);
     Work w;
     for (; work.next(w); ++j) {
       const int n0 = w.n0, n_kb = w.n_kb, split = w.split, tile_id = w.tile_id;
@@ -442,7 +480,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const uint32_t lane_addr = tmem_base + (MT == 1 ? b : half) * S::TMEM_COLS + ((uint32_t)(q * 32) << 16);
 
       bool run_epilogue = ok;
-      if (w.partial && p.accumulate) {
+      if (CL && p.splits > 1) {
+        // this slice's sums go to shared memory as [token][feature of the tile] (the operand ring is
+        // free: every MMA has finished); the cluster adds them up after the barrier below
+        run_epilogue = false;
+        float* stage = (float*)tiles;
+        for (int c = 0; c < n_valid; c += 32) {
+          uint32_t v[32];
+          if (have_acc) {
+            if (BN >= 32) tmem_ld32(lane_addr + c, v); else tmem_ld16(lane_addr + c, v);
+            tmem_ld_wait();
+          }
+          const int nc = min(32, n_valid - c);
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (j < nc) stage[(c + j) * BM + r] = have_acc ? __uint_as_float(v[j]) : 0.f;
+        }
+      } else if (w.partial && p.accumulate) {
         // Every slice adds its share straight into the float32 output with red.global.add: no
         // scratch, no tickets, no fences.  The order in which the slices arrive is not fixed,
         // so the sum may differ in its last bits from run to run.
@@ -632,6 +686,50 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   fence_before_sync();
   __syncthreads();
+  if (CL && p.splits > 1) {
+    // Every thread of every CTA of the cluster comes here, whatever happened above.
+    cluster_sync_all();                                   // the partial sums of all ranks are in shared memory
+    if (warp >= 2) {
+      const int S = p.splits;
+      const int t = threadIdx.x - 64;                     // feature within the tile
+      const int tile_id = blockIdx.x / S, my = (int)cluster_rank();
+      const int tiles_m = (p.M + BM - 1) / BM;
+      const int tile_n = tile_id / tiles_m, tile_m = tile_id - tile_n * tiles_m;
+      const int m0 = tile_m * BM, n0 = tile_n * BN;
+      const int n_valid = min(BN, p.N - n0);
+      const int feat = m0 + t;
+      const float bias = (p.bias && feat < p.M) ? p.bias[feat] : 0.f;
+      const uint32_t stage = smem_u32(tiles) + (uint32_t)t * 4;
+      uint32_t peer[8];
+#pragma unroll
+      for (int s2 = 0; s2 < 8; ++s2) peer[s2] = peer_smem(stage, (uint32_t)(s2 < S ? s2 : 0));
+      // token rows my, my + S, ... are this CTA's; four of them in flight at a time
+      for (int j0 = my; j0 < n_valid; j0 += 4 * S) {
+        float v[4][8];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int j = j0 + u * S;
+#pragma unroll
+          for (int s2 = 0; s2 < 8; ++s2) v[u][s2] = (j < n_valid && s2 < S) ? ld_peer_f32(peer[s2] + (uint32_t)j * (BM * 4)) : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int j = j0 + u * S;
+          if (j < n_valid && feat < p.M) {
+            float sum = v[u][0];
+#pragma unroll
+            for (int s2 = 1; s2 < 8; ++s2) sum += v[u][s2];   // in rank order; ranks beyond S hold zeros
+            sum += bias;
+            const size_t o = (size_t)(n0 + j) * p.ldc + feat;
+            if (p.accumulate) ((float*)p.out)[o] += sum;
+            else if (p.out_bf16) ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(sum);
+            else ((float*)p.out)[o] = sum;
+          }
+        }
+      }
+    }
+    cluster_sync_all();                                   // no peer reads this CTA's shared memory any more
+  }
   if (flags[0]) {
     // a wait ran out: give copies in flight time to land before shared memory goes away
     if (threadIdx.x == 0 && p.status) atomicExch(p.status, WPC_ERR_DEVICE_WAIT);
@@ -712,18 +810,34 @@ static int tensor_map(const void* ptr, int rows, int cols, int ld, int box_rows,
 // Upper limit of the ring depth (a tuning knob; MAX_STAGES by default).
 static int g_stage_limit = MAX_STAGES;
 
-template <int BN, bool SWAP, int MT = 1>
+template <int BN, bool SWAP, int MT = 1, bool CL = false>
 static int launch(const CUtensorMap& ma, const CUtensorMap& mb, Params& p, cudaStream_t stream) {
   using S = Smem<BN, MT>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, SWAP, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, SWAP, MT, CL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          S::total(S::max_stages(1)));
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   const long units = (long)((p.M + MT * BM - 1) / (MT * BM)) * ((p.N + BN - 1) / BN) * p.splits;
   if (units > 0x7fffffffL) return WPC_ERR_TOO_LARGE;
+  if (CL) {
+    // one CTA per (tile, K slice), the slices of a tile side by side in one cluster
+    if (p.splits < 2 || p.splits > 8) return WPC_ERR_UNSUPPORTED;
+    // a ring so short that two CTAs fit on an SM: more clusters then run side by side (the
+    // clusters of a GPC's SMs leave fewer SMs idle), and all of them must stream at once
+    int stages = S::max_stages(2);
+    const int kb_per = (p.k_blocks + p.splits - 1) / p.splits;
+    if (stages > kb_per) stages = kb_per < 2 ? 2 : kb_per;
+    if (stages > g_stage_limit) stages = g_stage_limit < 2 ? 2 : g_stage_limit;
+    if (S::total(stages) < S::HEAD_BYTES + 1024 + BN * BM * 4) stages = (BN * BM * 4 + S::STAGE_BYTES - 1) / S::STAGE_BYTES;
+    p.stages = stages;
+    p.stream_k = 0;
+    wpc::launch_clusters(gemm_tc_kernel<BN, SWAP, MT, CL>, dim3((unsigned)units), THREADS, S::total(stages), stream,
+                         (unsigned)p.splits, ma, mb, p);
+    return launch_status();
+  }
   // Many tiles in the normal arrangement: one persistent CTA per SM walks the tiles, its
   // epilogue overlapping the next tile's MMAs.  Otherwise one CTA per unit; if those are few,
   // each is alone on its SM and takes a deep ring, if many, two share an SM.
@@ -744,7 +858,7 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, Params& p, cudaS
   constexpr int RED_STAGE_BYTES = 4 * 32 * 33 * 4;
   const bool red_stage = !SWAP && p.accumulate && (p.splits > 1 || p.stream_k);
   if (red_stage && S::total(stages) + RED_STAGE_BYTES > S::total(S::max_stages(1))) p.stages = --stages;
-  wpc::launch(gemm_tc_kernel<BN, SWAP, MT>, grid, THREADS, S::total(stages) + (red_stage ? RED_STAGE_BYTES : 0), stream,
+  wpc::launch(gemm_tc_kernel<BN, SWAP, MT, CL>, grid, THREADS, S::total(stages) + (red_stage ? RED_STAGE_BYTES : 0), stream,
               ma, mb, p);
   return launch_status();
 }
@@ -785,8 +899,9 @@ int wpc_gemm_tc_workspace(int rows_a, int rows_b, int bn, int splits, size_t* sc
 int wpc_gemm_tc(const void* a, int lda, int rows_a, const void* b, int ldb, int rows_b, int K, const float* bias,
                 void* out, int out_dtype, int ldc, int accumulate, int gated, int swap, int bn, int splits,
                 float* scratch, size_t scratch_floats, int* counters, int n_counters, int* status,
-                int prefetch_weights, int tall, cudaStream_t stream) {
+                int prefetch_weights, int tall, int cluster, cudaStream_t stream) {
   if (rows_a <= 0 || rows_b <= 0) return 0;
+  if (cluster && (!swap || splits < 2 || splits > 8 || gated)) return WPC_ERR_UNSUPPORTED;
   if (tall && (swap || bn != 256 || splits > 1)) return WPC_ERR_UNSUPPORTED;
   if (K <= 0 || (lda % 8) || (ldb % 8) || (((uintptr_t)a) & 15) || (((uintptr_t)b) & 15)) return WPC_ERR_UNSUPPORTED;
   if (accumulate && out_dtype != WPC_DTYPE_F32) return WPC_ERR_BAD_ARGUMENT;
@@ -804,7 +919,8 @@ int wpc_gemm_tc(const void* a, int lda, int rows_a, const void* b, int ldb, int 
   if (gated && (bn < (swap ? 16 : 128) || p.splits != 1 || accumulate || !p.out_bf16 || bias ||
                 (swap ? rows_a % BM : rows_b % 128)))
     return WPC_ERR_UNSUPPORTED;
-  if (p.splits > 1 && !accumulate) {
+  if (cluster && p.splits < 2) cluster = 0;
+  if (p.splits > 1 && !accumulate && !cluster) {
     size_t need_f; int need_c;
     wpc_gemm_tc_workspace(rows_a, rows_b, bn, p.splits, &need_f, &need_c);
     if (!scratch || !counters || need_f > scratch_floats || need_c > n_counters) return WPC_ERR_TOO_LARGE;
@@ -822,6 +938,13 @@ int wpc_gemm_tc(const void* a, int lda, int rows_a, const void* b, int ldb, int 
       case 128: return launch<128, false>(ma, mb, p, stream);
       case 256: return launch<256, false>(ma, mb, p, stream);
     }
+  } else if (cluster) {
+    switch (bn) {
+      case 16: return launch<16, true, 1, true>(ma, mb, p, stream);
+      case 32: return launch<32, true, 1, true>(ma, mb, p, stream);
+      case 64: return launch<64, true, 1, true>(ma, mb, p, stream);
+      case 128: return launch<128, true, 1, true>(ma, mb, p, stream);
+    }
   } else {
     switch (bn) {
       case 16: return launch<16, true>(ma, mb, p, stream);
@@ -831,6 +954,44 @@ int wpc_gemm_tc(const void* a, int lda, int rows_a, const void* b, int ldb, int 
     }
   }
   return WPC_ERR_UNSUPPORTED;
+}
+
+// How many clusters of `splits` CTAs of the swapped kernel with tile width bn the device can
+// hold at once (0 if the sizes are not supported); -1 on a CUDA error.  The runtime's answer is
+// for one CTA to an SM; the kernel keeps its ring so short that two fit (see launch), and
+// measured on B200 twice as many clusters then run side by side, so the answer is doubled.
+int wpc_gemm_tc_cluster_capacity(int bn, int splits) {
+  if (splits < 2 || splits > 8) return 0;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(splits * 148));
+  cfg.blockDim = dim3(THREADS);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)splits;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  cudaError_t e = cudaErrorInvalidValue;
+#define WPC_CAP(BN_)                                                                                              \
+  {                                                                                                               \
+    using S = Smem<BN_, 1>;                                                                                       \
+    cfg.dynamicSmemBytes = S::total(S::max_stages(2));                                                            \
+    e = cudaFuncSetAttribute(gemm_tc_kernel<BN_, true, 1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,     \
+                             S::total(S::max_stages(1)));                                                         \
+    if (e == cudaSuccess) e = cudaOccupancyMaxActiveClusters(&n, gemm_tc_kernel<BN_, true, 1, true>, &cfg);       \
+  }
+  switch (bn) {
+    case 16: WPC_CAP(16) break;
+    case 32: WPC_CAP(32) break;
+    case 64: WPC_CAP(64) break;
+    case 128: WPC_CAP(128) break;
+    default: return 0;
+  }
+#undef WPC_CAP
+  if (e != cudaSuccess) { cudaGetLastError(); return -1; }
+  return 2 * n;
 }
 
 }  // extern "C"

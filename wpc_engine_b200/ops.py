@@ -161,6 +161,7 @@ def linear_plain(x, w, bias=None, out_dtype=None, residual=None) -> torch.Tensor
 
 
 _SMS = 148
+CLUSTER_SPLITS = True     # the CTAs that split one tile's K form a cluster and add up through shared memory
 _WORKSPACE_FLOATS = 8 << 20        # 32 MiB of split-K partial sums
 _WORKSPACE_COUNTERS = 4096
 _workspaces = {}
@@ -186,10 +187,23 @@ def device_status(device="cuda") -> int:
     return 0 if ws is None else int(ws[2].item())
 
 
+_cluster_capacity = {}
+
+
+def cluster_capacity(bn: int, splits: int) -> int:
+    """How many clusters of `splits` CTAs of the few-token kernel run side by side (asked once)."""
+    key = (bn, splits)
+    if key not in _cluster_capacity:
+        _cluster_capacity[key] = max(0, int(library().wpc_gemm_tc_cluster_capacity(bn, splits)))
+    return _cluster_capacity[key]
+
+
 def plan_tensor_core_linear(M: int, N: int, K: int):
     """(swap, bn, splits) for x [M, K] . w [N, K]^T.  Few tokens: the weights take the MMA's
     128 rows and the tokens its columns (swap).  Few tiles: K is split over CTAs so that
-    about all SMs stream weights."""
+    about all SMs stream weights.  With few tokens the CTAs of a tile form a cluster (at most
+    8) that adds the slices up through shared memory: the split is the largest for which all
+    clusters run at once."""
     k_blocks = (K + 63) // 64
     if M <= 128:
         swap, bn = True, (16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128)
@@ -201,6 +215,12 @@ def plan_tensor_core_linear(M: int, N: int, K: int):
         tiles = m_tiles * ((N + bn - 1) // bn)
     splits = 1
     if tiles * 2 <= _SMS:
+        if swap and CLUSTER_SPLITS:
+            for s in range(min(8, k_blocks // 4), 1, -1):
+                if tiles <= cluster_capacity(bn, s):
+                    splits = s
+                    break
+            return swap, bn, splits
         # about one CTA to an SM (two to an SM measured slower in a whole step, also with many tokens)
         splits = max(1, min(_SMS // tiles, k_blocks // 4, 16))
         while splits > 1 and tiles * splits * bn * 128 > _WORKSPACE_FLOATS:
@@ -246,7 +266,7 @@ def _tensor_core_linear(x, w, bias, out, accumulate, static_weight=False) -> boo
         _p(a), a.stride(0), a.shape[0], _p(b), b.stride(0), b.shape[0], K, _p(bias), _p(out), _code(out.dtype),
         out.stride(0), accumulate, 0, int(swap), bn, splits, _p(scratch), ctypes.c_size_t(scratch.numel()),
         _p(counters), counters.numel(), _p(status), int(static_weight), int(bool(tall)),
-        _stream()))
+        int(bool(swap and CLUSTER_SPLITS and 2 <= splits <= 8)), _stream()))
     return True
 
 
@@ -286,7 +306,7 @@ def gated_linear(x: torch.Tensor, w: torch.Tensor, inner: int, group: int, plain
         _check("gemm_tc", library().wpc_gemm_tc(
             _p(a), a.stride(0), a.shape[0], _p(b), b.stride(0), b.shape[0], K, _p(None), _p(out), _BF16,
             out.stride(0), 0, 1, int(swap), bn, 1, _p(scratch), ctypes.c_size_t(scratch.numel()), _p(counters),
-            counters.numel(), _p(status), int(static_weight), int(tall), _stream()))
+            counters.numel(), _p(status), int(static_weight), int(tall), 0, _stream()))
         return out
     return silu_mul(linear(x, w, plain=plain, static_weight=static_weight), inner, group)
 
