@@ -162,6 +162,14 @@ def linear_plain(x, w, bias=None, out_dtype=None, residual=None) -> torch.Tensor
 
 _SMS = 148
 CLUSTER_SPLITS = True     # the CTAs that split one tile's K form a cluster and add up through shared memory
+# Products that add into the float32 residual with few tokens and a short K keep the older
+# scheme (one CTA to an SM, deep rings, the slices add their shares with red.global.add): the
+# whole matrix is prefetched into shared memory behind the kernel ahead, and a cluster, which
+# needs all its CTAs placed at once, starts later (o_proj of the 7B shape inside a step: 6.4
+# against 9.0 us at 8 tokens).  The atomics grow with the token count: from 64 tokens on the
+# cluster wins (25.5 against 14.8 us).
+RED_MAX_TOKENS = 32
+RED_MAX_K_BLOCKS = 64
 _WORKSPACE_FLOATS = 8 << 20        # 32 MiB of split-K partial sums
 _WORKSPACE_COUNTERS = 4096
 _workspaces = {}
@@ -221,13 +229,19 @@ def plan_tensor_core_linear(M: int, N: int, K: int):
                     splits = s
                     break
             return swap, bn, splits
-        # about one CTA to an SM (two to an SM measured slower in a whole step, also with many tokens)
-        splits = max(1, min(_SMS // tiles, k_blocks // 4, 16))
-        while splits > 1 and tiles * splits * bn * 128 > _WORKSPACE_FLOATS:
-            splits -= 1
-        if tiles > _WORKSPACE_COUNTERS:
-            splits = 1
+        splits = _ticket_splits(tiles, k_blocks, bn)
     return swap, bn, splits
+
+
+def _ticket_splits(tiles: int, k_blocks: int, bn: int) -> int:
+    """Slices of K for products that combine through scratch memory or red.add: about one CTA
+    to an SM (two to an SM measured slower in a whole step, also with many tokens)."""
+    splits = max(1, min(_SMS // tiles, k_blocks // 4, 16))
+    while splits > 1 and tiles * splits * bn * 128 > _WORKSPACE_FLOATS:
+        splits -= 1
+    if tiles > _WORKSPACE_COUNTERS:
+        splits = 1
+    return splits
 
 
 def tall_tiles(M: int, N: int, swap: bool, bn: int, splits: int, K: int = 0, accumulate: bool = False) -> int:
@@ -254,6 +268,10 @@ def _tensor_core_linear(x, w, bias, out, accumulate, static_weight=False) -> boo
     if K % 8 or x.stride(0) % 8 or w.stride(0) % 8 or x.data_ptr() % 16 or w.data_ptr() % 16:
         return False
     swap, bn, splits = plan_tensor_core_linear(M, N, K)
+    cluster = bool(swap and CLUSTER_SPLITS and 2 <= splits <= 8)
+    if cluster and accumulate and M <= RED_MAX_TOKENS and (K + 63) // 64 <= RED_MAX_K_BLOCKS:
+        # few tokens, short K, added into float32: the slices add their shares with red.add
+        cluster, splits = False, _ticket_splits((N + 127) // 128, (K + 63) // 64, bn)
     tall = tall_tiles(M, N, swap, bn, splits, K, bool(accumulate))
     if tall:
         bn = tall
@@ -266,7 +284,7 @@ def _tensor_core_linear(x, w, bias, out, accumulate, static_weight=False) -> boo
         _p(a), a.stride(0), a.shape[0], _p(b), b.stride(0), b.shape[0], K, _p(bias), _p(out), _code(out.dtype),
         out.stride(0), accumulate, 0, int(swap), bn, splits, _p(scratch), ctypes.c_size_t(scratch.numel()),
         _p(counters), counters.numel(), _p(status), int(static_weight), int(bool(tall)),
-        int(bool(swap and CLUSTER_SPLITS and 2 <= splits <= 8)), _stream()))
+        int(cluster), _stream()))
     return True
 
 
