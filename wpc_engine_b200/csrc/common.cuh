@@ -82,6 +82,11 @@ inline int& pdl_enabled() {
   static int on = 1;
   return on;
 }
+// Set to 1 before a launch that should not start ahead of the kernel before it; cleared by the launch.
+inline int& pdl_skip_next() {
+  static thread_local int skip = 0;
+  return skip;
+}
 inline int& last_launch_error() {
   static thread_local int rc = 0;
   return rc;
@@ -98,7 +103,8 @@ inline void launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  cfg.numAttrs = (pdl_enabled() && !pdl_skip_next()) ? 1 : 0;
+  pdl_skip_next() = 0;
   const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
   if (e != cudaSuccess) last_launch_error() = (int)e;
 }

@@ -858,6 +858,12 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, Params& p, cudaS
   constexpr int RED_STAGE_BYTES = 4 * 32 * 33 * 4;
   const bool red_stage = !SWAP && p.accumulate && (p.splits > 1 || p.stream_k);
   if (red_stage && S::total(stages) + RED_STAGE_BYTES > S::total(S::max_stages(1))) p.stages = --stages;
+  // A product over many tokens does not start ahead of the kernel before it: measured on B200,
+  // CTAs of these long kernels that become resident early (as SMs happen to fall free) run the
+  // whole product slower (o_proj 97 against 75 us, down 268 against 236 us at 2,048 tokens of
+  // the 7B shape), far more than the two microseconds of launch latency that the overlap saves.
+  // With 512 tokens the kernels are short and the overlap still wins (10.5 against 10.7 ms).
+  if (!SWAP && p.M >= 1024) wpc::pdl_skip_next() = 1;
   wpc::launch(gemm_tc_kernel<BN, SWAP, MT, CL>, grid, THREADS, S::total(stages) + (red_stage ? RED_STAGE_BYTES : 0), stream,
               ma, mb, p);
   return launch_status();
