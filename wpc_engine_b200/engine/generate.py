@@ -82,6 +82,8 @@ def _note(stats, first: bool, dt: float, entries) -> None:
         stats["decode_s"] += dt
         stats["decode_tokens"] += len(entries)
         stats["decode_steps"] += 1
+        stats["decode_step_s"].append(dt)
+        stats["decode_step_tokens"].append(len(entries))
 
 
 def _run_batch(engine, live, entries, opts, stop, outputs, stats) -> None:
@@ -152,11 +154,13 @@ def generate(engine, prompts: Sequence[Sequence[int]], opts: GenerationOptions,
 
     With `stats` (a dict) the loop records what the reference prints to standard error
     (wpc-runtime/src/main.rs:294, 309): seconds and tokens of the prompt steps and of the
-    single-token steps, summed over the batches."""
+    single-token steps, summed over the batches; `decode_step_s` and `decode_step_tokens` list
+    the seconds and tokens of every single-token step in order."""
     if opts.max_tokens < 1:
         return [[] for _ in prompts]
     if stats is not None:
-        stats.update(prefill_s=0.0, prefill_tokens=0, decode_s=0.0, decode_tokens=0, decode_steps=0)
+        stats.update(prefill_s=0.0, prefill_tokens=0, decode_s=0.0, decode_tokens=0, decode_steps=0,
+                     decode_step_s=[], decode_step_tokens=[])
     stop = frozenset(int(s) for s in opts.stop_token_ids)
     outputs: List[Optional[List[int]]] = [None] * len(prompts)
     batches = plan_batches([len(p) for p in prompts], opts.max_tokens, engine.cache.n_pages,
