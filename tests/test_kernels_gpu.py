@@ -213,8 +213,13 @@ TC_SHAPES = [(1, 128, 64), (8, 256, 128), (8, 4608, 3584), (8, 3584, 18944), (64
 
 @pytest.mark.parametrize("shape", TC_SHAPES)
 @pytest.mark.parametrize("mode", ["plain", "bias_f32out", "residual"])
-def test_tensor_core_linear(shape, mode):
+@pytest.mark.parametrize("pair", [True, False])
+def test_tensor_core_linear(shape, mode, pair, monkeypatch):
+    """`pair` False keeps the tiles on single SMs (the kernels that sizes without pair tiles use)."""
     M, N, K = shape
+    if not pair and M <= 128:
+        pytest.skip("few tokens never run in pair tiles")
+    monkeypatch.setattr(ops, "PAIR_TILES", pair)
     x, w = rnd((M, K), torch.bfloat16, 21), rnd((N, K), torch.bfloat16, 22, 0.05)
     swap, bn, splits = ops.plan_tensor_core_linear(M, N, K)
     if shape in ((2048, 4608, 256), (2000, 4608, 264), (2048, 3584, 264)):
@@ -390,3 +395,52 @@ def test_few_token_linear_in_clusters_every_slice_counts():
             want = torch.zeros((M, N), device=DEV)
             want[s % M] = w[:, k].float()
             assert torch.equal(ops.linear(x, w, out_dtype=torch.float32), want), (s, k)
+
+
+# ---- many tokens: 256-row tiles on pairs of SMs (tcgen05 cta_group::2) ----------------------------
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 300, 200), (400, 1000, 520), (2048, 4608, 512), (1500, 3584, 264),
+                                   (3000, 520, 96)])
+@pytest.mark.parametrize("width", [256, 224, 208, 144, 128])
+def test_pair_tiles(M, N, K, width, monkeypatch):
+    """Every tile width that the kernel takes, sizes that leave partial tiles in both
+    directions, and the three kinds of output, against the float32 product (weights.rs:59-78)."""
+    monkeypatch.setattr(ops, "PAIR_TILES", True)
+    monkeypatch.setattr(ops, "PAIR_WIDTHS", (width,))
+    assert ops.pair_tiles(M, N, False, 256)
+    x, w = rnd((M, K), torch.bfloat16, 81), rnd((N, K), torch.bfloat16, 82, 0.05)
+    bias = rnd((N,), seed=83)
+    want = ops.linear_plain(x, w, bias, out_dtype=torch.float32)
+    mag = want.abs().max().item()
+    got = ops.linear(x, w, bias, out_dtype=torch.float32)
+    assert (got - want).abs().max().item() <= 2e-3 * mag
+    assert (ops.linear(x, w, bias).float() - want).abs().max().item() <= 1.2e-2 * mag
+    r0 = rnd((M, N), seed=84)
+    acc, want_acc = ops.linear(x, w, residual=r0.clone()), ops.linear_plain(x, w, residual=r0.clone())
+    assert (acc - want_acc).abs().max().item() <= 2e-3 * max(mag, want_acc.abs().max().item())
+    assert ops.device_status() == 0
+
+
+def test_pair_tiles_find_one_element(monkeypatch):
+    """A single one in x picks one column of w exactly, for rows in either CTA of a pair and
+    features in either half of the tile (each CTA holds half of the weight rows)."""
+    monkeypatch.setattr(ops, "PAIR_TILES", True)
+    M, N, K = 512, 600, 200
+    w = rnd((N, K), torch.bfloat16, 85)
+    for (m, k) in [(0, 0), (127, 63), (128, 64), (255, 199), (256, 1), (511, 130), (300, 65)]:
+        x = torch.zeros((M, K), dtype=torch.bfloat16, device=DEV)
+        x[m, k] = 1.0
+        want = torch.zeros((M, N), device=DEV)
+        want[m] = w[:, k].float()
+        assert torch.equal(ops.linear(x, w, out_dtype=torch.float32), want), (m, k)
+
+
+@pytest.mark.parametrize("T,inner,K", [(256, 128, 96), (2048, 1152, 256), (700, 320, 520)])
+def test_pair_tiles_gated(T, inner, K, monkeypatch):
+    monkeypatch.setattr(ops, "PAIR_TILES", True)
+    x = rnd((T, K), torch.bfloat16, 86)
+    w = rnd((2 * inner, K), torch.bfloat16, 87, 0.1)
+    got = ops.gated_linear(x, w, inner, 64)
+    want = ref.gated_linear(x.cpu(), w.cpu(), inner, 64)
+    mag = want.float().abs().max().item()
+    assert (got.cpu().float() - want.float()).abs().max().item() <= 1.5e-2 * mag
+    assert ops.device_status() == 0

@@ -2,7 +2,10 @@
 //
 //     D[M, N] = A[M, K] . B[N, K]^T        (both operands row-major with K contiguous)
 //
-// One CTA computes one 128 x BN tile of D (optionally only a slice of K: split-K).  Operand
+// Two kernels.  gemm_tc_kernel: one CTA computes one 128 x BN tile of D (optionally only a slice
+// of K: split-K); it serves few tokens (swapped arrangement) and the sizes that the second
+// does not take.  gemm_pair_kernel (further down): two CTAs of a cluster compute one 256 x 256
+// tile with tcgen05.mma.cta_group::2; it serves many tokens.  In gemm_tc_kernel operand
 // tiles of 64 K-elements (one 128-byte swizzle row) travel from global to shared memory by TMA
 // through a ring of stages; a single thread issues tcgen05.mma into a float32 accumulator in
 // tensor memory; four warps read the accumulator back with tcgen05.ld and write the result.
@@ -66,6 +69,7 @@ struct Params {
   int stages;                  // depth of the operand ring (2..MAX_STAGES)
   int stream_k;                // 1: every CTA takes an equal share of all k-blocks of all tiles (stream-K);
                                //    tiles that are cut add their shares with red.add (needs accumulate)
+  int pair_n;                  // gemm_pair_kernel: columns of a pair's tile (128..256 in steps of 16)
   int prefetch_weights;        // 1: the weight operand (A when swapped, else B) is never written while the
                                //    model runs, so its first stages may be fetched before the kernel
                                //    ahead in the stream has finished
@@ -743,6 +747,220 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   }
 }
 
+// ---- the product on pairs of SMs (tcgen05 cta_group::2) -----------------------------------------
+// Normal arrangement, many tokens.  Two CTAs of a cluster compute one 256 x 256 tile of D: CTA
+// `rank` holds rows m0 + 128*rank .. +127 of A and rows n0 + 128*rank .. +127 of B in its shared
+// memory; one thread of the leader (rank 0) issues tcgen05.mma.cta_group::2 with M = 256, which
+// reads A from each CTA's own memory and B from both, and leaves each CTA's 128 rows of D in its
+// own tensor memory.  Against 128 x 256 tiles on single SMs every SM fetches a third less per
+// flop.  Protocol (as in CUTLASS's sm100 2-SM kernels):
+//   * both producers copy with cta_group::2 TMA loads that signal the LEADER's "full" barrier;
+//     the leader's producer arms it with the bytes of both CTAs;
+//   * the leader's MMA thread commits to the "empty" barrier of both CTAs (multicast commit),
+//     and to the "accumulator full" barrier of both;
+//   * the epilogue warps of both CTAs arrive on the leader's "accumulator empty" barrier;
+//   * tensor memory is allocated and freed by one warp of each CTA with cta_group::2.
+// Cluster barriers (hardware, reached by every thread on every path) stand after the set-up
+// and before the exit; every mbarrier wait is bounded as in the kernel above.
+constexpr int PAIR_STAGES = 6;
+constexpr int PAIR_STAGE_BYTES = 2 * BM * BK * 2;       // this CTA's halves of A and B: 16 KiB each
+constexpr int PAIR_SMEM = 1024 + 1024 + PAIR_STAGES * PAIR_STAGE_BYTES;
+constexpr int PAIR_N = 256;
+
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, int x, int y, uint32_t leader_bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(leader_bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// One arrival at `bar` of both CTAs of the pair when all MMAs issued so far have finished.
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(smem_u32(bar)), "h"((uint16_t)3)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* holder, int cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(holder)), "r"(cols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t addr, int cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
+  pdl_trigger();
+  extern __shared__ uint8_t smem_raw[];
+  uint64_t* full = (uint64_t*)smem_raw;                  // [PAIR_STAGES], used in the leader
+  uint64_t* empty = full + PAIR_STAGES;                   // [PAIR_STAGES], in each CTA
+  uint64_t* accum_full = empty + PAIR_STAGES;             // [2], in each CTA
+  uint64_t* accum_empty = accum_full + 2;                 // [2], used in the leader: 256 arrivals
+  uint32_t* tmem_holder = (uint32_t*)(accum_empty + 2);
+  int* flags = (int*)(tmem_holder + 1);
+  uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1024 + 1023) & ~(uintptr_t)1023);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_rank();                   // 0: leader
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const int PN = p.pair_n;                                // columns of the tile; each CTA holds PN / 2 rows of B
+  const int tiles_m = (p.M + 2 * BM - 1) / (2 * BM);
+  const int n_tiles = tiles_m * ((p.N + PN - 1) / PN);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < PAIR_STAGES; ++s) {
+      mbar_init(full + s, 1);
+      mbar_init(empty + s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(accum_full + b, 1);
+      mbar_init(accum_empty + b, 256);
+    }
+    flags[0] = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc_pair(tmem_holder, 512);
+  fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();                                     // both CTAs' barriers exist before anything signals them
+  fence_after_sync();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      pdl_wait();
+      int it = 0;
+      bool ok = true;
+      for (int t = pair; ok && t < n_tiles; t += n_pairs) {
+        const int tile_n = t / tiles_m, tile_m = t - tile_n * tiles_m;
+        const int m0 = tile_m * 2 * BM + (int)rank * BM, n0 = tile_n * PN + (int)rank * (PN >> 1);
+        for (int i = 0; i < p.k_blocks; ++i, ++it) {
+          const int s = it % PAIR_STAGES;
+          const uint32_t ph = (it / PAIR_STAGES) & 1;
+          if (!mbar_wait(empty + s, ph ^ 1)) { atomicExch(flags, 1); ok = false; break; }
+          if (rank == 0) mbar_expect_tx(full + s, 2 * (BM * BK * 2 + (PN >> 1) * BK * 2));
+          const uint32_t leader_bar = peer_smem(smem_u32(full + s), 0);
+          uint8_t* dst = tiles + s * PAIR_STAGE_BYTES;
+          tma_load_2d_pair(dst, &map_a, i * BK, m0, leader_bar);
+          tma_load_2d_pair(dst + BM * BK * 2, &map_b, i * BK, n0, leader_bar);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      // M = 256 over the pair, N = 256, bfloat16 inputs, float32 accumulator, both operands K-major
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(PN >> 3) << 17) |
+                             ((uint32_t)((2 * BM) >> 4) << 24);
+      int it = 0, j = 0;
+      bool ok = true;
+      for (int t = pair; ok && t < n_tiles; t += n_pairs, ++j) {
+        const int b = j & 1, use = j >> 1;
+        if (!mbar_wait(accum_empty + b, (use & 1) ^ 1)) { atomicExch(flags, 1); break; }
+        fence_after_sync();
+        const uint32_t tmem_d = tmem_base + b * PAIR_N;
+        for (int i = 0; i < p.k_blocks; ++i, ++it) {
+          const int s = it % PAIR_STAGES;
+          const uint32_t ph = (it / PAIR_STAGES) & 1;
+          if (!mbar_wait(full + s, ph)) { atomicExch(flags, 1); ok = false; break; }
+          fence_after_sync();
+          const uint32_t a_addr = smem_u32(tiles + s * PAIR_STAGE_BYTES);
+          const uint64_t da = smem_desc_sw128(a_addr), db = smem_desc_sw128(a_addr + BM * BK * 2);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma_bf16_pair(tmem_d, da + 2 * k, db + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+          umma_commit_pair(empty + s);
+        }
+        umma_commit_pair(accum_full + b);
+      }
+    }
+  } else {
+    pdl_wait();
+    const int q = warp & 3;
+    const int r = q * 32 + lane;
+    int j = 0;
+    for (int t = pair; t < n_tiles; t += n_pairs, ++j) {
+      const int tile_n = t / tiles_m, tile_m = t - tile_n * tiles_m;
+      const int m0 = tile_m * 2 * BM + (int)rank * BM, n0 = tile_n * PN;
+      const int b = j & 1, use = j >> 1;
+      bool ok = mbar_wait(accum_full + b, use & 1);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) atomicExch(flags, 1);
+      fence_after_sync();
+      const int n_valid = min(PN, p.N - n0);
+      const bool have_acc = p.k_blocks > 0 && ok;
+      const uint32_t lane_addr = tmem_base + b * PAIR_N + ((uint32_t)(q * 32) << 16);
+      const int row = m0 + r;
+      if (ok && p.gated) {
+        // columns: [64 gate | 64 up] repeated (wpc-runtime/src/model.rs:527-531)
+        for (int c = 0; c < PN; c += 128) {
+#pragma unroll
+          for (int k = 0; k < 2; ++k) {
+            uint32_t ug[32], uu[32];
+            float v[32];
+            if (have_acc) {
+              tmem_ld32(lane_addr + c + 32 * k, ug);
+              tmem_ld32(lane_addr + c + 64 + 32 * k, uu);
+              tmem_ld_wait();
+            }
+#pragma unroll
+            for (int jj = 0; jj < 32; ++jj) {
+              const float g = have_acc ? __uint_as_float(ug[jj]) : 0.f, u = have_acc ? __uint_as_float(uu[jj]) : 0.f;
+              v[jj] = g / (1.0f + expf(-g)) * u;
+            }
+            if (row < p.M && c < n_valid) store_row32(p, row, (n0 + c) / 2 + 32 * k, 32, v);
+          }
+        }
+      } else if (ok) {
+        for (int c = 0; c < n_valid; c += 32) {
+          const int nc = min(32, n_valid - c);
+          uint32_t u[32];
+          float v[32];
+          if (have_acc) {
+            tmem_ld32(lane_addr + c, u);
+            tmem_ld_wait();
+          }
+#pragma unroll
+          for (int jj = 0; jj < 32; ++jj) v[jj] = have_acc ? __uint_as_float(u[jj]) : 0.f;
+          if (p.bias) {
+#pragma unroll
+            for (int jj = 0; jj < 32; ++jj)
+              if (jj < nc) v[jj] += p.bias[n0 + c + jj];
+          }
+          if (row < p.M) store_row32(p, row, n0 + c, nc, v);
+        }
+      }
+      fence_before_sync();
+      mbar_arrive_cluster(peer_smem(smem_u32(accum_empty + b), 0));   // the leader's barrier, from both CTAs
+      if (!ok) break;
+    }
+  }
+
+  fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();                                     // the peer is done with this CTA's memory and barriers
+  if (flags[0]) {
+    if (threadIdx.x == 0 && p.status) atomicExch(p.status, WPC_ERR_DEVICE_WAIT);
+    const unsigned long long t0 = global_ns();
+    while (global_ns() - t0 < 2000000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    fence_after_sync();
+    tmem_dealloc_pair(tmem_base, 512);
+  }
+}
+
 // ---- host side --------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -869,6 +1087,22 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, Params& p, cudaS
   return launch_status();
 }
 
+static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, Params& p, cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const long n_tiles = (long)((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + p.pair_n - 1) / p.pair_n);
+  if (n_tiles > 0x3fffffffL) return WPC_ERR_TOO_LARGE;
+  const unsigned pairs = (unsigned)(n_tiles < 74 ? n_tiles : 74);
+  p.stages = PAIR_STAGES;
+  if (p.M >= 1024) wpc::pdl_skip_next() = 1;          // as in launch(): long kernels do not start early
+  wpc::launch_clusters(gemm_pair_kernel, dim3(2 * pairs), THREADS, PAIR_SMEM, stream, 2u, ma, mb, p);
+  return launch_status();
+}
+
 }  // namespace tc
 }  // namespace wpc
 
@@ -898,7 +1132,8 @@ int wpc_gemm_tc_workspace(int rows_a, int rows_b, int bn, int splits, size_t* sc
 // gated = 1: the weights hold gate and up rows interleaved in blocks of 64 features (64 gate
 // rows, then the 64 up rows of the same features); out is [tokens, features / 2] bfloat16 =
 // silu(gate) * up.  Needs no split and no bias, and bn >= 128 in the normal arrangement.
-// tall = 1 (normal arrangement, bn 256, no split): 256 x 256 tiles, see the kernel.
+// tall = 1 (normal arrangement, bn 256, no split): 256 x 256 tiles on one SM, see the kernel;
+// tall = 2: 256 x bn tiles on pairs of SMs (gemm_pair_kernel), bn 128..256 in steps of 16.
 // prefetch_weights = 1 promises that the weights are not written by earlier work still in
 // flight on the stream (model parameters): their first tiles are then fetched before the
 // preceding kernel has finished.
@@ -908,7 +1143,8 @@ int wpc_gemm_tc(const void* a, int lda, int rows_a, const void* b, int ldb, int 
                 int prefetch_weights, int tall, int cluster, cudaStream_t stream) {
   if (rows_a <= 0 || rows_b <= 0) return 0;
   if (cluster && (!swap || splits < 2 || splits > 8 || gated)) return WPC_ERR_UNSUPPORTED;
-  if (tall && (swap || bn != 256 || splits > 1)) return WPC_ERR_UNSUPPORTED;
+  if (tall && (swap || splits > 1 || tall > 2 || (tall == 1 && bn != 256))) return WPC_ERR_UNSUPPORTED;
+  if (tall == 2 && (bn < 128 || bn > 256 || bn % 16 || (gated && bn % 128))) return WPC_ERR_UNSUPPORTED;
   if (K <= 0 || (lda % 8) || (ldb % 8) || (((uintptr_t)a) & 15) || (((uintptr_t)b) & 15)) return WPC_ERR_UNSUPPORTED;
   if (accumulate && out_dtype != WPC_DTYPE_F32) return WPC_ERR_BAD_ARGUMENT;
   Params p;
@@ -932,10 +1168,14 @@ int wpc_gemm_tc(const void* a, int lda, int rows_a, const void* b, int ldb, int 
     if (!scratch || !counters || need_f > scratch_floats || need_c > n_counters) return WPC_ERR_TOO_LARGE;
   }
   CUtensorMap ma, mb;
-  int rc = tensor_map(a, rows_a, K, lda, tall ? 2 * BM : BM, &ma);
+  int rc = tensor_map(a, rows_a, K, lda, tall == 1 ? 2 * BM : BM, &ma);
   if (rc) return rc;
-  rc = tensor_map(b, rows_b, K, ldb, bn, &mb);
+  rc = tensor_map(b, rows_b, K, ldb, tall == 2 ? bn / 2 : bn, &mb);
   if (rc) return rc;
+  if (!swap && tall == 2) {
+    p.pair_n = bn;
+    return launch_pair(ma, mb, p, stream);
+  }
   if (!swap && tall) {
     if (bn == 256) return launch<256, false, 2>(ma, mb, p, stream);
   } else if (!swap) {
