@@ -139,6 +139,15 @@ __host__ __device__ constexpr uint32_t instr_desc(int n, bool b_mn_major) {
 // Byte offset of 16-byte chunk c (0..7) of row `row` inside a swizzled [rows, 64] bfloat16 block.
 __device__ __forceinline__ uint32_t swz(int row, int c) { return (uint32_t)(row * 128 + ((c ^ (row & 7)) << 4)); }
 
+// 2^x in one instruction (relative error 2^-22, results below the normal range are zero): the
+// weights are rounded to bfloat16 right after, and exp2f's handling of subnormal results costs
+// three more instructions for each of the 64 scores of a row and page.
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 template <int HD>
 struct Cfg {
   static constexpr int NB = HD / 64;                      // 64-wide blocks along head_dim
@@ -268,8 +277,9 @@ prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat
   // The products of page j + 1 (scores) and of page j - 1 (weighted values) run on the tensor
   // pipe while the threads do the softmax of page j; copies are issued a whole page ahead.
   for (int j = 0; j < n_pg; ++j) {
-    // (A) everything copied so far is in shared memory; start the scores of the next page
-    cp_async_wait<0>();
+    // (A) the keys of the next page are in shared memory (only the newest group of copies, the
+    // values of this page, may still be on its way); start the scores of the next page
+    if (j == 0) cp_async_wait<0>(); else cp_async_wait<1>();
     fence_async_smem();
     fence_before_sync();
     __syncthreads();
@@ -323,8 +333,8 @@ prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat
     uint32_t pw[32];
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
-      const float p0 = exp2f(fmaf(__uint_as_float(su[2 * i]), scale_log2, neg_m));
-      const float p1 = exp2f(fmaf(__uint_as_float(su[2 * i + 1]), scale_log2, neg_m));
+      const float p0 = ex2(fmaf(__uint_as_float(su[2 * i]), scale_log2, neg_m));
+      const float p1 = ex2(fmaf(__uint_as_float(su[2 * i + 1]), scale_log2, neg_m));
       sum4[i & 3] += p0 + p1;
       const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
       pw[i] = *(const uint32_t*)&pb;
@@ -358,6 +368,7 @@ prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat
 #pragma unroll
     for (int c = 0; c < 8; ++c)
       *(uint4*)(p_ptr + swz(tid, c)) = make_uint4(pw[4 * c], pw[4 * c + 1], pw[4 * c + 2], pw[4 * c + 3]);
+    cp_async_wait<2>();                 // the values of this page (two groups have been started since)
     fence_before_sync();
     fence_async_smem();
     __syncthreads();
