@@ -444,3 +444,47 @@ def test_pair_tiles_gated(T, inner, K, monkeypatch):
     mag = want.float().abs().max().item()
     assert (got.cpu().float() - want.float()).abs().max().item() <= 1.5e-2 * mag
     assert ops.device_status() == 0
+
+
+# ---- the q/k/v product that rotates and writes the cache in its tail ------------------------------
+@pytest.mark.parametrize("nh,nkv,hd,K", [(28, 4, 128, 3584), (14, 2, 64, 896), (3, 1, 64, 520), (5, 5, 32, 1032),
+                                         (8, 2, 16, 4104), (7, 1, 128, 2048)])
+@pytest.mark.parametrize("new", [[1, 1, 1], [1] * 8, [6, 5, 1], [40, 3, 17, 30]])
+def test_linear_qk_rope_kv_store_fused(nh, nkv, hd, K, new, monkeypatch):
+    """One kernel (product in clusters, rotation and cache write in its tail) against the product
+    followed by the rotation kernel, and against torch (rope.rs:24-40, model.rs:464-475).
+    Several tokens of a sequence, pages that start in the middle, and sequences of one token."""
+    lens = [n + off for n, off in zip(new, [70, 5, 130, 64, 0, 1, 63, 200])]
+    T = sum(new)
+    _, kp, vp, table, seq, pos = paged_case(torch.bfloat16, nh, nkv, hd, lens, new, seed=13)
+    N = (nh + 2 * nkv) * hd
+    x, w = rnd((T, K), torch.bfloat16, 91), rnd((N, K), torch.bfloat16, 92, 0.05)
+    bias = rnd((N,), seed=93)
+    inv = torch.tensor(np.power(1e4, -2.0 * np.arange(hd // 2) / hd), dtype=torch.float64, device=DEV)
+    cos, sin = ops.rope_angles(pos, inv)
+    swap, bn, splits = ops.plan_tensor_core_linear(T, N, K)
+    assert swap and 2 <= splits <= 8, "this case is meant to run in clusters"
+    k1, v1 = kp.clone(), vp.clone()
+    q1 = ops.linear_qk_rope_kv_store(x, w, bias, nh, nkv, hd, cos, sin, k1, v1, table, seq, pos)
+    assert ops.device_status() == 0
+    monkeypatch.setattr(ops, "FUSE_ROPE_STORE", False)
+    k2, v2 = kp.clone(), vp.clone()
+    q2 = ops.linear_qk_rope_kv_store(x, w, bias, nh, nkv, hd, cos, sin, k2, v2, table, seq, pos)
+    # torch: float32 product, rotation, cache write
+    qkv3 = ref.linear(x.cpu(), w.cpu(), bias.cpu(), out_dtype=torch.float32)
+    k3, v3 = kp.cpu().float(), vp.cpu().float()
+    ref.qk_rope_kv_store(qkv3, nh, nkv, hd, cos.cpu(), sin.cpu(), k3, v3, table.cpu(), seq.cpu(), pos.cpu())
+    mag = qkv3.abs().max().item()
+    nq = nh * hd
+    assert (q1[:, :nq].cpu().float() - qkv3[:, :nq]).abs().max().item() <= 1.2e-2 * mag
+    assert (k1.cpu().float() - k3).abs().max().item() <= 1.2e-2 * mag
+    assert (v1.cpu().float() - v3).abs().max().item() <= 1.2e-2 * mag
+    assert (q1[:, :nq].float() - q2[:, :nq].float()).abs().max().item() <= 1.6e-2 * mag
+    assert (k1.float() - k2.float()).abs().max().item() <= 1.6e-2 * mag
+    # nothing but the new positions of the cache was touched
+    untouched = torch.ones(kp.shape[0], 64, dtype=torch.bool)
+    for t in range(T):
+        b, p_ = int(seq[t]), int(pos[t])
+        untouched[int(table[b, p_ // 64]), p_ % 64] = False
+    assert torch.equal(k1.cpu()[untouched[:, None, :].expand(-1, nkv, -1)], kp.cpu()[untouched[:, None, :].expand(-1, nkv, -1)])
+    assert torch.equal(v1.cpu()[untouched[:, None, :].expand(-1, nkv, -1)], vp.cpu()[untouched[:, None, :].expand(-1, nkv, -1)])

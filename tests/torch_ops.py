@@ -11,7 +11,8 @@ import torch
 
 PAGE = 64
 __all__ = ["require_device", "embed", "rmsnorm", "linear", "silu_mul", "gated_linear", "add_", "gather_rows", "convert",
-           "rope_angles", "rope_inplace", "qk_rope_kv_store", "attention", "sample", "fill_normal"]
+           "rope_angles", "rope_inplace", "qk_rope_kv_store", "linear_qk_rope_kv_store", "attention", "sample",
+           "fill_normal"]
 
 _M64 = (1 << 64) - 1
 
@@ -104,6 +105,13 @@ def qk_rope_kv_store(qkv, n_heads, n_kv_heads, head_dim, cos, sin, k_pages, v_pa
         assert page >= 0
         k_pages[page, :, pos % PAGE, :] = k[t].to(k_pages.dtype)
         v_pages[page, :, pos % PAGE, :] = v[t]
+
+
+def linear_qk_rope_kv_store(x, w, bias, n_heads, n_kv_heads, head_dim, cos, sin, k_pages, v_pages, page_table,
+                            seq_of_token, positions):
+    qkv = linear(x, w, bias)
+    qk_rope_kv_store(qkv, n_heads, n_kv_heads, head_dim, cos, sin, k_pages, v_pages, page_table, seq_of_token, positions)
+    return qkv
 
 
 def attention(q, n_heads, n_kv_heads, head_dim, k_pages, v_pages, page_table, cu_seqlens, ctx_lens,

@@ -41,6 +41,11 @@ int wpc_gemm_tc(const void* a, int lda, int rows_a, const void* b, int ldb, int 
                 float* scratch, size_t scratch_floats, int* counters, int n_counters, int* status,
                 int prefetch_weights, int tall, int cluster, cudaStream_t stream);
 int wpc_gemm_tc_cluster_capacity(int bn, int splits);
+int wpc_gemm_tc_rope_store(const void* w, int ldw, const void* x, int ldx, int tokens, int K, const float* bias, void* out,
+                           int ldc, int bn, int splits, int prefetch_weights, int nh, int nkv, int hd, int R,
+                           const float* cosv, const float* sinv, void* k_pages, void* v_pages, const int* page_table,
+                           int table_width, const int* seq_of_token, const int* positions, int n_pages, int* status,
+                           cudaStream_t stream);
 
 int wpc_attention_plain(const void* q, int q_stride, void* out, int out_stride, int dtype, const void* k_pages,
                         const void* v_pages, const int* page_table, int table_width, const int* seq_of_token,

@@ -70,6 +70,21 @@ struct Params {
   int stream_k;                // 1: every CTA takes an equal share of all k-blocks of all tiles (stream-K);
                                //    tiles that are cut add their shares with red.add (needs accumulate)
   int pair_n;                  // gemm_pair_kernel: columns of a pair's tile (128..256 in steps of 16)
+  // Cluster variant only (rope_hd != 0): the rows of the output are [q heads | k heads | v heads]
+  // of an attention layer.  The tail rotates q and k (pairs (i, i + hd/2), the first rope_R of
+  // them, wpc-runtime/src/rope.rs:24-40), writes q to `out` and the rotated k and the v of every
+  // token into the cache page of its position (wpc-runtime/src/model.rs:464-475); the k and v
+  // columns of `out` are not written.
+  int rope_nh, rope_nkv, rope_hd, rope_R;
+  const float* rope_cos;       // [tokens, rope_R]
+  const float* rope_sin;
+  __nv_bfloat16* k_pages;      // [n_pages, nkv, PAGE, hd]
+  __nv_bfloat16* v_pages;
+  const int* page_table;       // [sequences, table_width]
+  int table_width;
+  const int* seq_of_token;
+  const int* positions;
+  int n_pages;
   int prefetch_weights;        // 1: the weight operand (A when swapped, else B) is never written while the
                                //    model runs, so its first stages may be fetched before the kernel
                                //    ahead in the stream has finished
@@ -361,6 +376,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   uint64_t* accum_empty = accum_full + 2;         // [2]: the epilogue has read the accumulator
   uint32_t* tmem_holder = (uint32_t*)(accum_empty + 2);
   int* flags = (int*)(tmem_holder + 1);          // [0]: a wait ran out, [1]: this CTA drew the last ticket
+  long long* s_rowbase = (long long*)(smem_raw + 512);   // [64] cache places of this CTA's token rows (rope_hd)
   uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + S::HEAD_BYTES + 1023) & ~(uintptr_t)1023);
   const int STAGES = p.stages;
   float* red_stage = (float*)(tiles + STAGES * S::STAGE_BYTES);    // [4][32][33], present where cut tiles add (see launch)
@@ -466,6 +482,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int q = warp & 3;
     const int r = q * 32 + lane;                        // row of the tile = TMEM lane
     const int et = threadIdx.x - 64;                    // 0..127 among the epilogue threads
+    if (CL && p.rope_hd && p.splits > 1) {
+      // where in the cache the token rows that this CTA will write go (rows rank, rank + S, ...):
+      // three dependent loads a row, done here so that they are over when the tail needs them
+      const int S = p.splits, my = (int)cluster_rank();
+      const int tiles_m = (p.M + BM - 1) / BM;
+      const int n0 = (blockIdx.x / S / tiles_m) * BN;
+      const int n_valid = min(BN, p.N - n0);
+      for (int k = et; my + k * S < n_valid; k += 128) {
+        const int tok = n0 + my + k * S;
+        const int pos = p.positions[tok], block = pos / WPC_PAGE;
+        const int page = block < p.table_width ? p.page_table[(size_t)p.seq_of_token[tok] * p.table_width + block] : -1;
+        s_rowbase[k] = (page >= 0 && page < p.n_pages) ? ((long long)page * p.rope_nkv * WPC_PAGE + pos % WPC_PAGE) : -1;
+      }
+    }
     int j = 0;
     WorkIter<BN, MT> work(p, CL);
     Work w;
@@ -707,27 +737,70 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       uint32_t peer[8];
 #pragma unroll
       for (int s2 = 0; s2 < 8; ++s2) peer[s2] = peer_smem(stage, (uint32_t)(s2 < S ? s2 : 0));
+      // With rope_hd: what this feature is (q, k or v; which head; which element), and a buffer
+      // behind the partial sums through which the two halves of a head exchange their values.
+      const int hd = p.rope_hd, half = hd >> 1;
+      const int nq = p.rope_nh * hd, nk = p.rope_nkv * hd;
+      const int kind = !hd ? 0 : (feat < nq ? 0 : (feat < nq + nk ? 1 : 2));       // q, k, v
+      const int d = hd ? feat % hd : 0;
+      const int kvh = hd ? (kind == 1 ? (feat - nq) / hd : (kind == 2 ? (feat - nq - nk) / hd : 0)) : 0;
+      const int pr = hd ? d % half : 0;                    // index of the pair within the head
+      const bool rotated = hd && kind < 2 && pr < p.rope_R;
+      float* xbuf = (float*)(tiles + BN * BM * 4);         // [4][128]
       // token rows my, my + S, ... are this CTA's; four of them in flight at a time
       for (int j0 = my; j0 < n_valid; j0 += 4 * S) {
         float v[4][8];
+        float cs[4], sn[4];
+        __nv_bfloat16* dst[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
           const int j = j0 + u * S;
 #pragma unroll
           for (int s2 = 0; s2 < 8; ++s2) v[u][s2] = (j < n_valid && s2 < S) ? ld_peer_f32(peer[s2] + (uint32_t)j * (BM * 4)) : 0.f;
+          cs[u] = 1.f; sn[u] = 0.f; dst[u] = nullptr;
+          if (hd && j < n_valid && feat < p.M) {
+            const int tok = n0 + j;
+            if (rotated) {
+              cs[u] = p.rope_cos[(size_t)tok * p.rope_R + pr];
+              sn[u] = p.rope_sin[(size_t)tok * p.rope_R + pr];
+            }
+            if (kind > 0) {
+              const long long base = s_rowbase[(j - my) / S];      // page * nkv * PAGE + place in the page
+              if (base >= 0)
+                dst[u] = (kind == 1 ? p.k_pages : p.v_pages) + ((size_t)base + (size_t)kvh * WPC_PAGE) * hd + d;
+              else if (p.status) atomicExch(p.status, WPC_ERR_BAD_ARGUMENT);
+            }
+          }
+        }
+        float val[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          float sum = v[u][0];
+#pragma unroll
+          for (int s2 = 1; s2 < 8; ++s2) sum += v[u][s2];   // in rank order; ranks beyond S hold zeros
+          val[u] = sum + bias;
+        }
+        if (hd) {
+          // x'_i = x_i c - x_{i+half} s;  x'_{i+half} = x_{i+half} c + x_i s  (rope.rs:36-39)
+#pragma unroll
+          for (int u = 0; u < 4; ++u) xbuf[u * BM + t] = val[u];
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const float other = xbuf[u * BM + (t ^ half)];
+            if (rotated) val[u] = d < half ? val[u] * cs[u] - other * sn[u] : val[u] * cs[u] + other * sn[u];
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");     // the buffer is written again in the next round
         }
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
           const int j = j0 + u * S;
           if (j < n_valid && feat < p.M) {
-            float sum = v[u][0];
-#pragma unroll
-            for (int s2 = 1; s2 < 8; ++s2) sum += v[u][s2];   // in rank order; ranks beyond S hold zeros
-            sum += bias;
             const size_t o = (size_t)(n0 + j) * p.ldc + feat;
-            if (p.accumulate) ((float*)p.out)[o] += sum;
-            else if (p.out_bf16) ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(sum);
-            else ((float*)p.out)[o] = sum;
+            if (hd && kind > 0) { if (dst[u]) *dst[u] = __float2bfloat16_rn(val[u]); }
+            else if (p.accumulate) ((float*)p.out)[o] += val[u];
+            else if (p.out_bf16) ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(val[u]);
+            else ((float*)p.out)[o] = val[u];
           }
         }
       }
@@ -1049,7 +1122,9 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, Params& p, cudaS
     const int kb_per = (p.k_blocks + p.splits - 1) / p.splits;
     if (stages > kb_per) stages = kb_per < 2 ? 2 : kb_per;
     if (stages > g_stage_limit) stages = g_stage_limit < 2 ? 2 : g_stage_limit;
-    if (S::total(stages) < S::HEAD_BYTES + 1024 + BN * BM * 4) stages = (BN * BM * 4 + S::STAGE_BYTES - 1) / S::STAGE_BYTES;
+    // the ring doubles as the place of the partial sums ([BN][128] floats) and of the tail's exchange buffer
+    constexpr int TAIL_BYTES = BN * BM * 4 + 4 * BM * 4;
+    if (stages * S::STAGE_BYTES < TAIL_BYTES) stages = (TAIL_BYTES + S::STAGE_BYTES - 1) / S::STAGE_BYTES;
     p.stages = stages;
     p.stream_k = 0;
     wpc::launch_clusters(gemm_tc_kernel<BN, SWAP, MT, CL>, dim3((unsigned)units), THREADS, S::total(stages), stream,
@@ -1147,7 +1222,7 @@ int wpc_gemm_tc(const void* a, int lda, int rows_a, const void* b, int ldb, int 
   if (tall == 2 && (bn < 128 || bn > 256 || bn % 16 || (gated && bn % 128))) return WPC_ERR_UNSUPPORTED;
   if (K <= 0 || (lda % 8) || (ldb % 8) || (((uintptr_t)a) & 15) || (((uintptr_t)b) & 15)) return WPC_ERR_UNSUPPORTED;
   if (accumulate && out_dtype != WPC_DTYPE_F32) return WPC_ERR_BAD_ARGUMENT;
-  Params p;
+  Params p = {};
   p.stages = 2;
   p.stream_k = 0;
   p.M = rows_a; p.N = rows_b; p.K = K;
@@ -1198,6 +1273,52 @@ int wpc_gemm_tc(const void* a, int lda, int rows_a, const void* b, int ldb, int 
       case 64: return launch<64, true>(ma, mb, p, stream);
       case 128: return launch<128, true>(ma, mb, p, stream);
     }
+  }
+  return WPC_ERR_UNSUPPORTED;
+}
+
+// The q/k/v projection of an attention layer for few tokens, with the rotation and the cache
+// write in the product's tail (cluster variant only: 2 <= splits <= 8):
+//   x [tokens <= 128, K] bfloat16, w [(nh + 2 nkv) * hd, K] bfloat16 (rows: q heads, k heads, v
+//   heads), bias float32 or null, out [tokens, (nh + 2 nkv) * hd] bfloat16 (row stride ldc).
+// q is rotated and written to its columns of out; k is rotated and, like v, written into the
+// page of its token's position; the k and v columns of out are left alone.  hd must be 16, 32,
+// 64 or 128, so that both halves of a head lie in one 128-feature tile.  cos, sin: float32
+// [tokens, R] (R <= hd / 2 pairs are rotated), or R = 0.
+int wpc_gemm_tc_rope_store(const void* w, int ldw, const void* x, int ldx, int tokens, int K, const float* bias, void* out,
+                           int ldc, int bn, int splits, int prefetch_weights, int nh, int nkv, int hd, int R,
+                           const float* cosv, const float* sinv, void* k_pages, void* v_pages, const int* page_table,
+                           int table_width, const int* seq_of_token, const int* positions, int n_pages, int* status,
+                           cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  const int features = (nh + 2 * nkv) * hd;
+  if ((hd != 16 && hd != 32 && hd != 64 && hd != 128) || nh < 1 || nkv < 1 || R < 0 || R > hd / 2 ||
+      (R > 0 && (!cosv || !sinv)) || tokens > 128 || splits < 2 || splits > 8)
+    return WPC_ERR_UNSUPPORTED;
+  if (K <= 0 || (ldw % 8) || (ldx % 8) || (((uintptr_t)w) & 15) || (((uintptr_t)x) & 15)) return WPC_ERR_UNSUPPORTED;
+  Params p = {};
+  p.M = features; p.N = tokens; p.K = K;
+  p.k_blocks = (K + BK - 1) / BK;
+  p.splits = splits > p.k_blocks ? p.k_blocks : splits;
+  if (p.splits < 2) return WPC_ERR_UNSUPPORTED;
+  p.bias = bias; p.out = out; p.ldc = ldc; p.out_bf16 = 1;
+  p.status = status;
+  p.prefetch_weights = prefetch_weights;
+  p.rope_nh = nh; p.rope_nkv = nkv; p.rope_hd = hd; p.rope_R = R;
+  p.rope_cos = cosv; p.rope_sin = sinv;
+  p.k_pages = (__nv_bfloat16*)k_pages; p.v_pages = (__nv_bfloat16*)v_pages;
+  p.page_table = page_table; p.table_width = table_width;
+  p.seq_of_token = seq_of_token; p.positions = positions; p.n_pages = n_pages;
+  CUtensorMap ma, mb;
+  int rc = tensor_map(w, features, K, ldw, BM, &ma);
+  if (rc) return rc;
+  rc = tensor_map(x, tokens, K, ldx, bn, &mb);
+  if (rc) return rc;
+  switch (bn) {
+    case 16: return launch<16, true, 1, true>(ma, mb, p, stream);
+    case 32: return launch<32, true, 1, true>(ma, mb, p, stream);
+    case 64: return launch<64, true, 1, true>(ma, mb, p, stream);
+    case 128: return launch<128, true, 1, true>(ma, mb, p, stream);
   }
   return WPC_ERR_UNSUPPORTED;
 }
@@ -1322,7 +1443,7 @@ extern "C" int wpc_linear_few_tokens_static(const void* x, int ldx, int tokens, 
   cudaError_t e = cudaMemsetAsync(counters, 0, 8192, stream);
   if (e != cudaSuccess) return (int)e;
 
-  Params p;
+  Params p = {};
   p.stages = 2;
   p.stream_k = 0;
   p.M = features; p.N = tokens; p.K = K;

@@ -423,6 +423,44 @@ def qk_rope_kv_store(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim:
         k_pages.shape[0], _p(None), _stream()))
 
 
+FUSE_ROPE_STORE = True     # few tokens: the q/k/v product rotates and writes the cache in its tail
+
+
+def linear_qk_rope_kv_store(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], n_heads: int,
+                            n_kv_heads: int, head_dim: int, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
+                            k_pages: torch.Tensor, v_pages: torch.Tensor, page_table: torch.Tensor,
+                            seq_of_token: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
+    """qkv = x w^T + bias with q and k rotated and k, v appended to the cache: `linear`
+    followed by `qk_rope_kv_store`, or, with few tokens in bfloat16, one kernel that does the
+    rotation and the cache write in the product's tail (csrc/gemm_tc.cu).  Only the q columns
+    of the result are meant to be read."""
+    M, K = x.shape
+    N = w.shape[0]
+    if (FUSE_ROPE_STORE and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and k_pages.dtype == torch.bfloat16
+            and head_dim in (16, 32, 64, 128) and 0 < M <= 128 and N == (n_heads + 2 * n_kv_heads) * head_dim
+            and K % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
+            and w.data_ptr() % 16 == 0 and x.stride(1) == 1 and w.stride(1) == 1 and CLUSTER_SPLITS):
+        swap, bn, splits = plan_tensor_core_linear(M, N, K)
+        if swap and 2 <= splits <= 8:
+            _need(k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.shape == v_pages.shape
+                  and tuple(k_pages.shape[1:]) == (n_kv_heads, PAGE, head_dim),
+                  "pages must be contiguous [n_pages, n_kv_heads, PAGE, head_dim]")
+            _need(page_table.dtype == torch.int32 and page_table.is_contiguous(), "page_table must be contiguous int32")
+            if bias is not None:
+                _need(bias.dtype == torch.float32 and bias.numel() == N and bias.is_contiguous(), "bias must be float32 [N]")
+            R = 0 if cos is None else cos.shape[1]
+            out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+            _, _, status = workspace(x.device)
+            _check("gemm_tc_rope_store", library().wpc_gemm_tc_rope_store(
+                _p(w), w.stride(0), _p(x), x.stride(0), M, K, _p(bias), _p(out), out.stride(0), bn, splits, 1,
+                n_heads, n_kv_heads, head_dim, R, _p(cos), _p(sin), _p(k_pages), _p(v_pages), _p(page_table),
+                page_table.shape[1], _p(seq_of_token), _p(positions), k_pages.shape[0], _p(status), _stream()))
+            return out
+    qkv = linear(x, w, bias, static_weight=True)
+    qk_rope_kv_store(qkv, n_heads, n_kv_heads, head_dim, cos, sin, k_pages, v_pages, page_table, seq_of_token, positions)
+    return qkv
+
+
 def attention(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, k_pages: torch.Tensor,
               v_pages: torch.Tensor, page_table: torch.Tensor, cu_seqlens: torch.Tensor, ctx_lens: torch.Tensor,
               seq_of_token: torch.Tensor, positions: torch.Tensor, scale: float, window: Optional[int],

@@ -63,9 +63,9 @@ class GQAAttention(Mixer):
         if self.position is not None:
             cos, sin = self.position.tables(ctx)
         if cache.writes:
-            qkv = self.qkv.forward(h)
-            ops.qk_rope_kv_store(qkv, nh, nkv, hd, cos, sin, cache.k_pages, cache.v_pages,
-                                 cache.page_table, ctx.seq_of_token, ctx.positions)
+            qkv = ops.linear_qk_rope_kv_store(h, self.qkv.weight, self.qkv.bias, nh, nkv, hd, cos, sin,
+                                              cache.k_pages, cache.v_pages, cache.page_table,
+                                              ctx.seq_of_token, ctx.positions)
         else:
             # a layer that reads another layer's cache computes queries only
             qkv = self.q_proj.forward(h)
