@@ -201,10 +201,6 @@ decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* 
               int nh, int nkv, float scale_log2, int window, float* __restrict__ part_o,
               float* __restrict__ part_ml, int* __restrict__ counters, int smem_bytes) {
   pdl_trigger();
-  // Nothing of the cache is read before the kernel ahead has finished: copying pages of earlier
-  // positions ahead of this wait gave wrong results under CUDA graphs (cause not found), and
-  // it saved about a microsecond.
-  pdl_wait();
   extern __shared__ __align__(16) uint8_t smem_raw[];
   __nv_bfloat16* ks = (__nv_bfloat16*)smem_raw;                       // [DECODE_STAGES][PAGE][STRIDE]
   __nv_bfloat16* vs = ks + DECODE_STAGES * Cfg<HD>::PAGE_ELEMS;
@@ -279,6 +275,11 @@ decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* 
     const int* gtable = page_table + (size_t)b * table_width + blk0;
     const int n_seg = blk1 - blk0;
     for (int i = tid; i < min(n_seg, MAX_SEGMENT_PAGES); i += THREADS) s_pages[i] = gtable[i];
+    // Up to here only the step's lengths and page numbers were read, which the host wrote before
+    // the step's first kernel started.  Queries, keys and values come from the kernel ahead:
+    // nothing of them is read before it has finished (copying pages of earlier positions ahead
+    // of this wait gave wrong results under CUDA graphs, cause not found).
+    if (u == u0) pdl_wait();
     __syncthreads();
     auto page_of = [&](int blk) { const int i = blk - blk0; return i < MAX_SEGMENT_PAGES ? s_pages[i] : gtable[i]; };
 

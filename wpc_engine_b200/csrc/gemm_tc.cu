@@ -67,8 +67,6 @@ struct Params {
   int* counters;               // one ticket counter per tile, zero between launches
   int* status;                 // device error word (may be null)
   int stages;                  // depth of the operand ring (2..MAX_STAGES)
-  int stream_k;                // 1: every CTA takes an equal share of all k-blocks of all tiles (stream-K);
-                               //    tiles that are cut add their shares with red.add (needs accumulate)
   int pair_n;                  // gemm_pair_kernel: columns of a pair's tile (128..256 in steps of 16)
   // Cluster variant only (rope_hd != 0): the rows of the output are [q heads | k heads | v heads]
   // of an attention layer.  The tail rotates q and k (pairs (i, i + hd/2), the first rope_R of
@@ -301,15 +299,12 @@ struct Work {
   int tile_id, split, m0, n0, kb0, n_kb;
   bool partial;                // the range does not cover the tile's whole K
 };
-// The pieces of one CTA, in order.  Unit mode: (tile, K slice) units blockIdx.x, + gridDim.x, ...
-// with the M tile fastest, so that CTAs running side by side share weight tiles.  Stream-K
-// mode: the k-blocks of all tiles laid end to end, cut into gridDim.x equal shares.
+// The pieces of one CTA, in order: (tile, K slice) units blockIdx.x, + gridDim.x, ... with the
+// M tile fastest, so that CTAs running side by side share weight tiles.
 template <int BN, int MT = 1>
 struct WorkIter {
   int n_tiles, tiles_m, k_blocks, splits, kb_per;
-  int u, n_units, stride;      // unit mode
-  int g, g1;                   // stream-K mode
-  bool stream_k;
+  int u, n_units, stride;
   bool split_fastest;          // units count (tile, split) with the split fastest: the CTAs of a cluster share a tile
   __device__ WorkIter(const Params& p, bool split_fastest_ = false) {
     split_fastest = split_fastest_;
@@ -318,39 +313,23 @@ struct WorkIter {
     k_blocks = p.k_blocks;
     splits = p.splits;
     kb_per = (k_blocks + splits - 1) / splits;
-    stream_k = p.stream_k != 0;
     u = blockIdx.x;
     n_units = n_tiles * splits;
     stride = gridDim.x;
-    const long total = (long)n_tiles * k_blocks;
-    const long share = (total + gridDim.x - 1) / gridDim.x;
-    const long lo = share * blockIdx.x, hi = lo + share;
-    g = (int)(lo < total ? lo : total);
-    g1 = (int)(hi < total ? hi : total);
   }
   __device__ bool next(Work& w) {
-    if (!stream_k) {
-      if (u >= n_units) return false;
-      if (split_fastest) {
-        w.tile_id = u / splits;
-        w.split = u - w.tile_id * splits;
-      } else {
-        w.split = u / n_tiles;
-        w.tile_id = u - w.split * n_tiles;
-      }
-      w.kb0 = w.split * kb_per;
-      w.n_kb = max(min(k_blocks, w.kb0 + kb_per) - w.kb0, 0);
-      w.partial = splits > 1;
-      u += stride;
+    if (u >= n_units) return false;
+    if (split_fastest) {
+      w.tile_id = u / splits;
+      w.split = u - w.tile_id * splits;
     } else {
-      if (g >= g1) return false;
-      w.tile_id = g / k_blocks;
-      w.kb0 = g - w.tile_id * k_blocks;
-      w.n_kb = min(k_blocks - w.kb0, g1 - g);
-      w.partial = w.n_kb < k_blocks;
-      w.split = w.kb0 == 0 ? 0 : 1;      // only the share that starts the tile adds the bias
-      g += w.n_kb;
+      w.split = u / n_tiles;
+      w.tile_id = u - w.split * n_tiles;
     }
+    w.kb0 = w.split * kb_per;
+    w.n_kb = max(min(k_blocks, w.kb0 + kb_per) - w.kb0, 0);
+    w.partial = splits > 1;
+    u += stride;
     const int tile_n = w.tile_id / tiles_m, tile_m = w.tile_id - tile_n * tiles_m;
     w.m0 = tile_m * MT * BM;
     w.n0 = tile_n * BN;
@@ -1126,7 +1105,6 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, Params& p, cudaS
     constexpr int TAIL_BYTES = BN * BM * 4 + 4 * BM * 4;
     if (stages * S::STAGE_BYTES < TAIL_BYTES) stages = (TAIL_BYTES + S::STAGE_BYTES - 1) / S::STAGE_BYTES;
     p.stages = stages;
-    p.stream_k = 0;
     wpc::launch_clusters(gemm_tc_kernel<BN, SWAP, MT, CL>, dim3((unsigned)units), THREADS, S::total(stages), stream,
                          (unsigned)p.splits, ma, mb, p);
     return launch_status();
@@ -1141,15 +1119,11 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, Params& p, cudaS
   if (!persistent && stages > kb_per) stages = kb_per < 2 ? 2 : kb_per;
   if (stages > g_stage_limit) stages = g_stage_limit < 2 ? 2 : g_stage_limit;
   p.stages = stages;
-  // Stream-K (equal shares of all k-blocks) is implemented but off: on B200 the red.adds of the
-  // cut tiles cost more than the idle half of a second wave (33.5 ms against 31.3 ms for a
-  // 2,048-token prefill of the 7B shape).
-  p.stream_k = 0;
   dim3 grid(persistent ? 148 : (unsigned)units);
   // cut tiles of the normal arrangement that add into the output turn their blocks around in
   // shared memory first (see the epilogue): room for [4][32][33] floats behind the ring
   constexpr int RED_STAGE_BYTES = 4 * 32 * 33 * 4;
-  const bool red_stage = !SWAP && p.accumulate && (p.splits > 1 || p.stream_k);
+  const bool red_stage = !SWAP && p.accumulate && p.splits > 1;
   if (red_stage && S::total(stages) + RED_STAGE_BYTES > S::total(S::max_stages(1))) p.stages = --stages;
   // A product over many tokens does not start ahead of the kernel before it: measured on B200,
   // CTAs of these long kernels that become resident early (as SMs happen to fall free) run the
@@ -1224,7 +1198,6 @@ int wpc_gemm_tc(const void* a, int lda, int rows_a, const void* b, int ldb, int 
   if (accumulate && out_dtype != WPC_DTYPE_F32) return WPC_ERR_BAD_ARGUMENT;
   Params p = {};
   p.stages = 2;
-  p.stream_k = 0;
   p.M = rows_a; p.N = rows_b; p.K = K;
   p.k_blocks = (K + BK - 1) / BK;
   p.splits = splits < 1 ? 1 : (splits > p.k_blocks ? p.k_blocks : splits);
@@ -1445,7 +1418,6 @@ extern "C" int wpc_linear_few_tokens_static(const void* x, int ldx, int tokens, 
 
   Params p = {};
   p.stages = 2;
-  p.stream_k = 0;
   p.M = features; p.N = tokens; p.K = K;
   p.k_blocks = k_blocks;
   p.splits = splits;
