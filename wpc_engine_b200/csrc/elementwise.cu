@@ -54,7 +54,6 @@ template <typename To, int VPT>
 __global__ void rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ gain,
                                    float eps, To* __restrict__ out, int H) {
   pdl_trigger();
-  pdl_wait();
   __shared__ float red[32];
   const float4* row = (const float4*)(x + (size_t)blockIdx.x * H);
   const float4* g4 = (const float4*)gain;
@@ -62,12 +61,18 @@ __global__ void rmsnorm_vec_kernel(const float* __restrict__ x, const float* __r
   const int n4 = H / 4;
   float4 v[VPT], g[VPT];
   float ss = 0.f;
+  // the gain is a model parameter: it is fetched while the kernel ahead is still finishing
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int i = threadIdx.x + k * blockDim.x;
+    if (i < n4) g[k] = g4[i];
+  }
+  pdl_wait();
 #pragma unroll
   for (int k = 0; k < VPT; ++k) {
     const int i = threadIdx.x + k * blockDim.x;
     if (i < n4) {
       v[k] = row[i];
-      g[k] = g4[i];
       ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
     }
   }

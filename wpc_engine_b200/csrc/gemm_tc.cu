@@ -384,6 +384,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   if (warp == 0) {
     if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");     // the descriptors themselves
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
       int it = 0;                                   // k-blocks loaded so far: position in the ring
       bool ok = true;
       WorkIter<BN, MT> work(p, CL);
@@ -457,13 +459,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
   } else {
     // ---- epilogue: warps 2..5 read lanes 32*(warp % 4) .. +31 of the accumulator ----
-    pdl_wait();                                         // the output, the scratch and the tickets are shared
     const int q = warp & 3;
     const int r = q * 32 + lane;                        // row of the tile = TMEM lane
     const int et = threadIdx.x - 64;                    // 0..127 among the epilogue threads
     if (CL && p.rope_hd && p.splits > 1) {
       // where in the cache the token rows that this CTA will write go (rows rank, rank + S, ...):
-      // three dependent loads a row, done here so that they are over when the tail needs them
+      // three dependent loads a row, done here so that they are over when the tail needs them.
+      // Positions and page numbers are the step's inputs, written by the host before its first
+      // kernel started: they may be read ahead of the dependency wait.
       const int S = p.splits, my = (int)cluster_rank();
       const int tiles_m = (p.M + BM - 1) / BM;
       const int n0 = (blockIdx.x / S / tiles_m) * BN;
@@ -475,6 +478,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         s_rowbase[k] = (page >= 0 && page < p.n_pages) ? ((long long)page * p.rope_nkv * WPC_PAGE + pos % WPC_PAGE) : -1;
       }
     }
+    pdl_wait();                                         // the output, the scratch and the tickets are shared
     int j = 0;
     WorkIter<BN, MT> work(p, CL);
     Work w;
