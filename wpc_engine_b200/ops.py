@@ -518,6 +518,11 @@ def plan_decode_ctas(n_seqs: int, n_kv_heads: int, max_ctx_len: int, window: Opt
     pairs = max(n_seqs * n_kv_heads, 1)
     if per_pair:
         return max(1, min(pairs * per_pair, 1024))
+    if 3 * _SMS // 2 <= pairs <= 2 * _SMS:
+        # nearly two pairs to an SM: a CTA to a pair, so that equally long sequences need no
+        # combining at all (64 sequences x 4 KV heads of 4,000 positions: 91 against 99 us);
+        # with fewer pairs than that, fewer CTAs would stream too little (192 CTAs: 90 against 77 us)
+        return pairs
     return max(1, min(2 * _SMS, pairs * max(blocks // 4, 1)))
 
 
