@@ -322,7 +322,9 @@ def test_silu_mul_groups(dtype, inner, group):
 # ---- prefill attention on tcgen05 against the plain reference and the mma.sync twin ---------------
 @pytest.mark.parametrize("nh,nkv,hd", [(28, 4, 128), (14, 2, 64), (4, 4, 128), (3, 1, 64), (16, 1, 128)])
 @pytest.mark.parametrize("window", [None, 100])
-def test_attention_prefill_tcgen05(nh, nkv, hd, window):
+@pytest.mark.parametrize("tiles", [1, 2])
+def test_attention_prefill_tcgen05(nh, nkv, hd, window, tiles, monkeypatch):
+    monkeypatch.setattr(ops, "PREFILL_ATTENTION_TILES", tiles)
     lens, new = [300, 5, 131, 700, 64], [300, 5, 31, 190, 1]
     qkv, kp, vp, table, seq, pos = paged_case(torch.bfloat16, nh, nkv, hd, lens, new, seed=11)
     cu = torch.tensor(np.concatenate([[0], np.cumsum(new)]), dtype=torch.int32, device=DEV)

@@ -66,7 +66,7 @@ int wpc_attention_prefill_tc_supports(int nh, int nkv, int hd);
 int wpc_attention_prefill_tc(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                              const void* v_pages, const int* page_table, int table_width, const int* cu_seqlens,
                              const int* ctx_lens, int B, int max_new, int nh, int nkv, int hd, float scale,
-                             int window, int* status, cudaStream_t stream);
+                             int window, int* status, int n_pages, int tiles, cudaStream_t stream);
 
 int wpc_sample(const float* logits, int n_rows, int V, const int* slots, long long* seq_state, float temperature,
                const int* banned, int n_banned, int* out, cudaStream_t stream);

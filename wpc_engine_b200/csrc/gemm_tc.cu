@@ -43,6 +43,7 @@
 
 #include "api.h"
 #include "common.cuh"
+#include "tensor_map.h"
 
 namespace wpc {
 namespace tc {
@@ -1056,7 +1057,7 @@ struct MapKeyHash {
 // A tensor map for a row-major bfloat16 matrix [rows, cols] with row stride ld elements,
 // copied in boxes of box_rows x 64 with the 128-byte swizzle.  Encoded maps are kept: the
 // same weights are multiplied step after step.
-static int tensor_map(const void* ptr, int rows, int cols, int ld, int box_rows, CUtensorMap* out) {
+int tensor_map(const void* ptr, int rows, int cols, int ld, int box_rows, CUtensorMap* out) {
   static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
   static std::mutex mu;
   const MapKey key{ptr, rows, cols, ld, box_rows};

@@ -423,6 +423,7 @@ def qk_rope_kv_store(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim:
         k_pages.shape[0], _p(None), _stream()))
 
 
+PREFILL_ATTENTION_TILES = 1     # row tiles of 128 rows to a CTA of the tcgen05 prefill attention (1 or 2)
 FUSE_ROPE_STORE = True     # few tokens: the q/k/v product rotates and writes the cache in its tail
 
 
@@ -498,7 +499,8 @@ def attention(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, k_p
         _check("attention_prefill_tc", library().wpc_attention_prefill_tc(
             _p(q), q.stride(0), _p(out), out.stride(0), _p(k_pages), _p(v_pages), _p(page_table),
             page_table.shape[1], _p(cu_seqlens), _p(ctx_lens), B, max_new_tokens, n_heads, n_kv_heads, head_dim,
-            ctypes.c_float(scale), int(window or 0), _p(status), _stream()))
+            ctypes.c_float(scale), int(window or 0), _p(status), k_pages.shape[0], PREFILL_ATTENTION_TILES,
+            _stream()))
     else:
         _check("attention_prefill", library().wpc_attention_prefill(
             _p(q), q.stride(0), _p(out), out.stride(0), _p(k_pages), _p(v_pages), _p(page_table),
