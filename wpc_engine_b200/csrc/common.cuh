@@ -126,7 +126,8 @@ inline void launch_clusters(void (*kernel)(KArgs...), dim3 grid, dim3 block, siz
   attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = pdl_enabled() ? 2 : 1;
+  cfg.numAttrs = (pdl_enabled() && !pdl_skip_next()) ? 2 : 1;
+  pdl_skip_next() = 0;
   const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
   if (e != cudaSuccess) last_launch_error() = (int)e;
 }
