@@ -490,3 +490,42 @@ def test_linear_qk_rope_kv_store_fused(nh, nkv, hd, K, new, monkeypatch):
         untouched[int(table[b, p_ // 64]), p_ % 64] = False
     assert torch.equal(k1.cpu()[untouched[:, None, :].expand(-1, nkv, -1)], kp.cpu()[untouched[:, None, :].expand(-1, nkv, -1)])
     assert torch.equal(v1.cpu()[untouched[:, None, :].expand(-1, nkv, -1)], vp.cpu()[untouched[:, None, :].expand(-1, nkv, -1)])
+
+
+@pytest.mark.parametrize("nh,nkv,hd,K", [(28, 4, 128, 512), (14, 2, 64, 896), (3, 1, 64, 520), (7, 1, 128, 264)])
+@pytest.mark.parametrize("new", [[256], [300, 212], [40, 600, 3, 125]])
+def test_linear_qk_rope_kv_store_fused_many_tokens(nh, nkv, hd, K, new, monkeypatch):
+    """The same with many tokens: the pair kernel's epilogue rotates and writes the cache."""
+    lens = [n + off for n, off in zip(new, [70, 5, 130, 64])]
+    T = sum(new)
+    _, kp, vp, table, seq, pos = paged_case(torch.bfloat16, nh, nkv, hd, lens, new, seed=17)
+    N = (nh + 2 * nkv) * hd
+    x, w = rnd((T, K), torch.bfloat16, 94), rnd((N, K), torch.bfloat16, 95, 0.05)
+    bias = rnd((N,), seed=96)
+    inv = torch.tensor(np.power(1e4, -2.0 * np.arange(hd // 2) / hd), dtype=torch.float64, device=DEV)
+    cos, sin = ops.rope_angles(pos, inv)
+    swap, bn, splits = ops.plan_tensor_core_linear(T, N, K)
+    if not (not swap and splits == 1 and ops.pair_tiles(T, N, swap, bn)):
+        pytest.skip("this size does not run in pair tiles")
+    k1, v1 = kp.clone(), vp.clone()
+    q1 = ops.linear_qk_rope_kv_store(x, w, bias, nh, nkv, hd, cos, sin, k1, v1, table, seq, pos)
+    assert ops.device_status() == 0
+    monkeypatch.setattr(ops, "FUSE_ROPE_STORE", False)
+    k2, v2 = kp.clone(), vp.clone()
+    q2 = ops.linear_qk_rope_kv_store(x, w, bias, nh, nkv, hd, cos, sin, k2, v2, table, seq, pos)
+    mag = q2.float().abs().max().item()
+    nq = nh * hd
+    assert (q1[:, :nq].float() - q2[:, :nq].float()).abs().max().item() <= 1.6e-2 * mag
+    assert (k1.float() - k2.float()).abs().max().item() <= 1.6e-2 * mag
+    assert (v1.float() - v2.float()).abs().max().item() <= 1.6e-2 * mag
+    # against torch on a sample of rows (the whole product in float32 on the CPU would be slow)
+    rows = sorted(set([0, 1, T // 2, T - 1]))
+    qkv3 = ref.linear(x.cpu()[rows], w.cpu(), bias.cpu(), out_dtype=torch.float32)
+    k3, v3 = kp.cpu().float(), vp.cpu().float()
+    ref.qk_rope_kv_store(qkv3, nh, nkv, hd, cos.cpu()[rows], sin.cpu()[rows], k3, v3, table.cpu(), seq.cpu()[rows], pos.cpu()[rows])
+    assert (q1[rows, :nq].cpu().float() - qkv3[:, :nq]).abs().max().item() <= 1.2e-2 * mag
+    for i, t in enumerate(rows):
+        b, p_ = int(seq[t]), int(pos[t])
+        page = int(table[b, p_ // 64])
+        assert (k1[page, :, p_ % 64].cpu().float() - k3[page, :, p_ % 64]).abs().max().item() <= 1.2e-2 * mag
+        assert (v1[page, :, p_ % 64].cpu().float() - v3[page, :, p_ % 64]).abs().max().item() <= 1.2e-2 * mag

@@ -857,6 +857,7 @@ __device__ __forceinline__ void tmem_dealloc_pair(uint32_t addr, int cols) {
   asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
 }
 
+template <bool ROPE>      // ROPE: the epilogue of the q/k/v projection (rotation and cache write), see there
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
   pdl_trigger();
@@ -976,6 +977,74 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
               v[jj] = g / (1.0f + expf(-g)) * u;
             }
             if (row < p.M && c < n_valid) store_row32(p, row, (n0 + c) / 2 + 32 * k, 32, v);
+          }
+        }
+      } else if (ROPE && ok) {
+        // The q/k/v projection: the columns are [q heads | k heads | v heads] of width hd (64 or
+        // 128, so that a head lies inside the tile).  This thread's token row: q and k are rotated
+        // (pairs (i, i + hd/2), the first rope_R of them, rope.rs:24-40); q goes to `out`, the
+        // rotated k and v into the page of the token's position (model.rs:464-475).
+        const int hd = p.rope_hd, half = hd >> 1;
+        const int nq = p.rope_nh * hd, nk = p.rope_nkv * hd;
+        long long base = -1;                               // page * nkv * PAGE + place in the page
+        const bool in_m = row < p.M;
+        if (in_m) {
+          const int pos = p.positions[row], block = pos / WPC_PAGE;
+          const int page = block < p.table_width ? p.page_table[(size_t)p.seq_of_token[row] * p.table_width + block] : -1;
+          if (page >= 0 && page < p.n_pages) base = (long long)page * p.rope_nkv * WPC_PAGE + pos % WPC_PAGE;
+          else if (n0 + PN > nq && p.status) atomicExch(p.status, WPC_ERR_BAD_ARGUMENT);
+        }
+        // a block of 32 pairs at a time: its cosines and sines serve every head of the tile
+        for (int pb = 0; pb < half; pb += 32) {
+          float cs[32], sn[32];
+#pragma unroll
+          for (int jj = 0; jj < 32; ++jj) {
+            const bool rot = in_m && pb + jj < p.rope_R;
+            cs[jj] = rot ? p.rope_cos[(size_t)row * p.rope_R + pb + jj] : 1.f;
+            sn[jj] = rot ? p.rope_sin[(size_t)row * p.rope_R + pb + jj] : 0.f;
+          }
+          for (int h0 = 0; h0 < n_valid; h0 += hd) {       // heads of the tile
+            const int feat0 = n0 + h0;                     // first feature of the head
+            const int kind = feat0 < nq ? 0 : (feat0 < nq + nk ? 1 : 2);
+            uint32_t ua[32], ub[32];
+            if (have_acc) {
+              tmem_ld32(lane_addr + h0 + pb, ua);
+              tmem_ld32(lane_addr + h0 + half + pb, ub);
+              tmem_ld_wait();
+            }
+            float va[32], vb[32];
+#pragma unroll
+            for (int jj = 0; jj < 32; ++jj) {
+              const float a = (have_acc ? __uint_as_float(ua[jj]) : 0.f) + (p.bias ? p.bias[feat0 + pb + jj] : 0.f);
+              const float bq = (have_acc ? __uint_as_float(ub[jj]) : 0.f) + (p.bias ? p.bias[feat0 + half + pb + jj] : 0.f);
+              if (kind < 2) {
+                va[jj] = a * cs[jj] - bq * sn[jj];
+                vb[jj] = bq * cs[jj] + a * sn[jj];
+              } else {
+                va[jj] = a;
+                vb[jj] = bq;
+              }
+            }
+            if (!in_m) continue;
+            if (kind == 0) {
+              store_row32(p, row, feat0 + pb, 32, va);
+              store_row32(p, row, feat0 + half + pb, 32, vb);
+            } else if (base >= 0) {
+              const int kvh = (kind == 1 ? feat0 - nq : feat0 - nq - nk) / hd;
+              __nv_bfloat16* dst = (kind == 1 ? p.k_pages : p.v_pages) + ((size_t)base + (size_t)kvh * WPC_PAGE) * hd;
+#pragma unroll
+              for (int jj = 0; jj < 32; jj += 8) {
+                uint4 oa, ob;
+                __nv_bfloat162 t0 = __floats2bfloat162_rn(va[jj], va[jj + 1]), t1 = __floats2bfloat162_rn(va[jj + 2], va[jj + 3]);
+                __nv_bfloat162 t2 = __floats2bfloat162_rn(va[jj + 4], va[jj + 5]), t3 = __floats2bfloat162_rn(va[jj + 6], va[jj + 7]);
+                oa.x = *(uint32_t*)&t0; oa.y = *(uint32_t*)&t1; oa.z = *(uint32_t*)&t2; oa.w = *(uint32_t*)&t3;
+                t0 = __floats2bfloat162_rn(vb[jj], vb[jj + 1]); t1 = __floats2bfloat162_rn(vb[jj + 2], vb[jj + 3]);
+                t2 = __floats2bfloat162_rn(vb[jj + 4], vb[jj + 5]); t3 = __floats2bfloat162_rn(vb[jj + 6], vb[jj + 7]);
+                ob.x = *(uint32_t*)&t0; ob.y = *(uint32_t*)&t1; ob.z = *(uint32_t*)&t2; ob.w = *(uint32_t*)&t3;
+                *(uint4*)(dst + pb + jj) = oa;
+                *(uint4*)(dst + half + pb + jj) = ob;
+              }
+            }
           }
         }
       } else if (ok) {
@@ -1141,10 +1210,11 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, Params& p, cudaS
   return launch_status();
 }
 
+template <bool ROPE>
 static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, Params& p, cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM);
+    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<ROPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
@@ -1153,7 +1223,7 @@ static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, Params& p, 
   const unsigned pairs = (unsigned)(n_tiles < 74 ? n_tiles : 74);
   p.stages = PAIR_STAGES;
   if (p.M >= 1024) wpc::pdl_skip_next() = 1;          // as in launch(): long kernels do not start early
-  wpc::launch_clusters(gemm_pair_kernel, dim3(2 * pairs), THREADS, PAIR_SMEM, stream, 2u, ma, mb, p);
+  wpc::launch_clusters(gemm_pair_kernel<ROPE>, dim3(2 * pairs), THREADS, PAIR_SMEM, stream, 2u, ma, mb, p);
   return launch_status();
 }
 
@@ -1227,7 +1297,7 @@ int wpc_gemm_tc(const void* a, int lda, int rows_a, const void* b, int ldb, int 
   if (rc) return rc;
   if (!swap && tall == 2) {
     p.pair_n = bn;
-    return launch_pair(ma, mb, p, stream);
+    return launch_pair<false>(ma, mb, p, stream);
   }
   if (!swap && tall) {
     if (bn == 256) return launch<256, false, 2>(ma, mb, p, stream);
@@ -1255,9 +1325,10 @@ int wpc_gemm_tc(const void* a, int lda, int rows_a, const void* b, int ldb, int 
   return WPC_ERR_UNSUPPORTED;
 }
 
-// The q/k/v projection of an attention layer for few tokens, with the rotation and the cache
-// write in the product's tail (cluster variant only: 2 <= splits <= 8):
-//   x [tokens <= 128, K] bfloat16, w [(nh + 2 nkv) * hd, K] bfloat16 (rows: q heads, k heads, v
+// The q/k/v projection of an attention layer with the rotation and the cache write in the
+// product's epilogue.  Few tokens (bn 16..128): the cluster variant, 2 <= splits <= 8, tokens
+// <= 128.  Many tokens (bn = 256): the pair kernel, hd 64 or 128.
+//   x [tokens, K] bfloat16, w [(nh + 2 nkv) * hd, K] bfloat16 (rows: q heads, k heads, v
 //   heads), bias float32 or null, out [tokens, (nh + 2 nkv) * hd] bfloat16 (row stride ldc).
 // q is rotated and written to its columns of out; k is rotated and, like v, written into the
 // page of its token's position; the k and v columns of out are left alone.  hd must be 16, 32,
@@ -1270,15 +1341,15 @@ int wpc_gemm_tc_rope_store(const void* w, int ldw, const void* x, int ldx, int t
                            cudaStream_t stream) {
   if (tokens <= 0) return 0;
   const int features = (nh + 2 * nkv) * hd;
+  const bool many = bn == 256;                       // many tokens: the pair kernel (splits is ignored)
   if ((hd != 16 && hd != 32 && hd != 64 && hd != 128) || nh < 1 || nkv < 1 || R < 0 || R > hd / 2 ||
-      (R > 0 && (!cosv || !sinv)) || tokens > 128 || splits < 2 || splits > 8)
+      (R > 0 && (!cosv || !sinv)))
     return WPC_ERR_UNSUPPORTED;
+  if (many ? (hd < 64) : (tokens > 128 || splits < 2 || splits > 8)) return WPC_ERR_UNSUPPORTED;
   if (K <= 0 || (ldw % 8) || (ldx % 8) || (((uintptr_t)w) & 15) || (((uintptr_t)x) & 15)) return WPC_ERR_UNSUPPORTED;
   Params p = {};
-  p.M = features; p.N = tokens; p.K = K;
   p.k_blocks = (K + BK - 1) / BK;
-  p.splits = splits > p.k_blocks ? p.k_blocks : splits;
-  if (p.splits < 2) return WPC_ERR_UNSUPPORTED;
+  p.K = K;
   p.bias = bias; p.out = out; p.ldc = ldc; p.out_bf16 = 1;
   p.status = status;
   p.prefetch_weights = prefetch_weights;
@@ -1287,6 +1358,19 @@ int wpc_gemm_tc_rope_store(const void* w, int ldw, const void* x, int ldx, int t
   p.k_pages = (__nv_bfloat16*)k_pages; p.v_pages = (__nv_bfloat16*)v_pages;
   p.page_table = page_table; p.table_width = table_width;
   p.seq_of_token = seq_of_token; p.positions = positions; p.n_pages = n_pages;
+  if (many) {
+    // normal arrangement: A = tokens, B = weights, 256 x 256 tiles on pairs of SMs
+    p.M = tokens; p.N = features; p.splits = 1; p.pair_n = 256;
+    CUtensorMap ma, mb;
+    int rc = tensor_map(x, tokens, K, ldx, BM, &ma);
+    if (rc) return rc;
+    rc = tensor_map(w, features, K, ldw, BM, &mb);
+    if (rc) return rc;
+    return launch_pair<true>(ma, mb, p, stream);
+  }
+  p.M = features; p.N = tokens;
+  p.splits = splits > p.k_blocks ? p.k_blocks : splits;
+  if (p.splits < 2) return WPC_ERR_UNSUPPORTED;
   CUtensorMap ma, mb;
   int rc = tensor_map(w, features, K, ldw, BM, &ma);
   if (rc) return rc;

@@ -438,11 +438,15 @@ def linear_qk_rope_kv_store(x: torch.Tensor, w: torch.Tensor, bias: Optional[tor
     M, K = x.shape
     N = w.shape[0]
     if (FUSE_ROPE_STORE and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and k_pages.dtype == torch.bfloat16
-            and head_dim in (16, 32, 64, 128) and 0 < M <= 128 and N == (n_heads + 2 * n_kv_heads) * head_dim
+            and head_dim in (16, 32, 64, 128) and M > 0 and N == (n_heads + 2 * n_kv_heads) * head_dim
             and K % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
-            and w.data_ptr() % 16 == 0 and x.stride(1) == 1 and w.stride(1) == 1 and CLUSTER_SPLITS):
+            and w.data_ptr() % 16 == 0 and x.stride(1) == 1 and w.stride(1) == 1):
         swap, bn, splits = plan_tensor_core_linear(M, N, K)
-        if swap and 2 <= splits <= 8:
+        few = swap and CLUSTER_SPLITS and 2 <= splits <= 8                  # the cluster variant's tail
+        many = (not swap) and splits == 1 and head_dim >= 64 and pair_tiles(M, N, swap, bn)   # the pair kernel's epilogue
+        if few or many:
+            if many:
+                bn = 256
             _need(k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.shape == v_pages.shape
                   and tuple(k_pages.shape[1:]) == (n_kv_heads, PAGE, head_dim),
                   "pages must be contiguous [n_pages, n_kv_heads, PAGE, head_dim]")
