@@ -278,3 +278,43 @@ def test_medium_model_graphs_and_dependent_launch_change_nothing(tmp_path_factor
     # the same kernels either way: only the order of the red.add shares may differ
     assert np.abs(fast - slow).max() <= 2e-2 * scale
     assert np.abs(fast - full).max() <= 6e-2 * scale and np.abs(slow - full).max() <= 6e-2 * scale
+
+
+def test_medium_model_long_prompt_whole_and_in_chunks(tmp_path_factory):
+    """A prompt long enough for the many-token kernels (256-row tiles on pairs of SMs, the
+    q/k/v product that rotates and writes the cache in its epilogue, tcgen05 attention with
+    a window): whole, in two chunks, and with its tail token by token, in bfloat16 against
+    the float32 path."""
+    from conftest import make_folder
+    from wpc_engine_b200 import SequenceStep, ops
+    raw = dict(architectures=["Qwen2ForCausalLM"], num_hidden_layers=2, hidden_size=1024, num_attention_heads=8,
+               num_key_value_heads=2, intermediate_size=2816, vocab_size=3000, rope_theta=1e6, rms_norm_eps=1e-6,
+               max_position_embeddings=4096, tie_word_embeddings=False, use_sliding_window=True,
+               sliding_window=300, max_window_layers=1)
+    folder = make_folder(tmp_path_factory, raw, 37, torch.bfloat16)
+    req = random_tokens(3000, 2100, 4242)
+    want = [0, 5, 1023, 1024, 1791, 1792, 2047, 2099]
+
+    def run(dtype, cuts):
+        eng = Engine.from_folder(folder, dtype=dtype, max_tokens=4096)
+        slot = eng.open_sequence()
+        rows = []
+        for lo, hi in zip(cuts[:-1], cuts[1:]):
+            w = [p - lo for p in want if lo <= p < hi]
+            out = eng.step([SequenceStep(slot, req[lo:hi], want=w)])
+            if w:
+                rows.append(out.float().cpu().numpy())
+        eng.close_sequence(slot)
+        eng.cache.check()
+        assert ops.device_status() == 0
+        return np.concatenate(rows)
+
+    whole = run("bfloat16", [0, 2100])
+    halves = run("bfloat16", [0, 1792, 2100])
+    tail = run("bfloat16", [0, 2090] + list(range(2091, 2101)))
+    full = run("float32", [0, 2100])
+    scale = np.abs(full).max()
+    assert np.abs(whole - full).max() <= 6e-2 * scale
+    assert np.abs(halves - full).max() <= 6e-2 * scale
+    assert np.abs(tail - full).max() <= 6e-2 * scale
+    assert np.abs(whole - halves).max() <= 3e-2 * scale and np.abs(whole - tail).max() <= 3e-2 * scale
