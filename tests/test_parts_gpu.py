@@ -1,6 +1,8 @@
 """Each part of a layer alone on the GPU against the plain implementation's function for it,
-at sizes of its own, and a toy architecture with a mixer that keeps a state of fixed size per
-sequence: registered, built, loaded and stepped from the test, without a change to the
+at sizes of its own, and two toy architectures: one with a mixer that keeps a state of fixed
+size per sequence (and a layer scheduled twice), one with a feed-forward that routes each token
+to one of several experts in some of its layers and with a position encoding of its own.  Both
+are registered, built, written, loaded and stepped from the tests, without a change to the
 library's files."""
 import dataclasses
 import json
@@ -239,3 +241,152 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path, dtype):
         eng.cache.check()
     finally:
         wpc.unregister_architecture("ToyRunningMeanLM")
+
+
+# ---- a second toy architecture: a feed-forward with routing and another position encoding -----------
+from wpc_engine_b200 import ops as _ops
+from wpc_engine_b200.parts import FeedForward, PositionEncoding
+
+
+class RoutedFeedForward(FeedForward):
+    """Each token goes to the one expert (a SwiGLU of the library) whose router logit is
+    greatest; the expert's output is scaled by the softmax weight of that logit.  Router logits
+    and softmax in float32.  A toy: the grouping by expert uses torch indexing, whose shapes
+    depend on the data, so it cannot be captured into a graph."""
+    graph_safe = False
+
+    def __init__(self, width, inner, n_experts):
+        self.width = width
+        self.router = Linear(width, n_experts)
+        self.experts = [SwiGLU(width, inner) for _ in range(n_experts)]
+
+    def subparts(self):
+        parts = {"router": self.router}
+        parts.update({f"experts.{e}": x for e, x in enumerate(self.experts)})
+        return parts
+
+    def forward(self, ctx, h, residual):
+        logits = _ops.linear(h, self.router.weight, out_dtype=torch.float32)
+        prob = torch.softmax(logits.float(), dim=-1)
+        top = prob.argmax(dim=-1)
+        out = torch.zeros((h.shape[0], self.width), dtype=torch.float32, device=h.device)
+        for e, expert in enumerate(self.experts):
+            idx = (top == e).nonzero().flatten()
+            if idx.numel():
+                acc = torch.zeros((idx.numel(), self.width), dtype=torch.float32, device=h.device)
+                expert.forward(ctx, h[idx].contiguous(), acc)          # adds its output into acc
+                out[idx] = acc * prob[idx, e].unsqueeze(1)
+        return out                                                       # the block adds it to the residual
+
+
+class ScaledRotary(PositionEncoding):
+    """Rotation by (position / factor) * theta^(-2i/head_dim): positions stretched by a factor,
+    angles in float64 on the device like the library's own encoding."""
+
+    def __init__(self, head_dim, theta, factor):
+        i = np.arange(head_dim // 2, dtype=np.float64)
+        self._inv = np.power(np.float64(theta), -(2.0 * i) / head_dim) / np.float64(factor)
+        self._dev = None
+
+    def tables(self, ctx):
+        key = ("scaled_rotary", id(self))
+        if key not in ctx.shared:
+            if self._dev is None:
+                self._dev = torch.from_numpy(self._inv.copy()).to(ctx.positions.device)
+            ctx.shared[key] = _ops.rope_angles(ctx.positions, self._dev)
+        return ctx.shared[key]
+
+
+@dataclasses.dataclass(frozen=True)
+class RoutedConfig:
+    vocab_size: int
+    width: int
+    n_layers: int
+    n_heads: int
+    n_kv_heads: int
+    inner: int
+    n_experts: int
+    theta: float
+    factor: float
+    eps: float
+
+    @classmethod
+    def from_dict(cls, raw):
+        return cls(**{f.name: raw[f.name] for f in dataclasses.fields(cls)})
+
+    def to_dict(self):
+        return dict(dataclasses.asdict(self), architectures=["ToyRoutedLM"])
+
+
+def build_routed(c: RoutedConfig):
+    hd = c.width // c.n_heads
+    pos = ScaledRotary(hd, c.theta, c.factor)                  # one object for all layers: tables are shared
+    blocks = []
+    for layer in range(c.n_layers):
+        # odd layers route, even layers have the dense feed-forward: parts are chosen layer by layer
+        ffn = RoutedFeedForward(c.width, c.inner, c.n_experts) if layer % 2 else SwiGLU(c.width, c.inner)
+        blocks.append(PreNormBlock(RMSNorm(c.width, c.eps), GQAAttention(c.width, c.n_heads, c.n_kv_heads, hd, pos, qkv_bias=False),
+                                   RMSNorm(c.width, c.eps), ffn, names=("ln1", "attn", "ln2", "ffn")))
+    emb = Embedding(c.vocab_size, c.width)
+    return DecoderModel(c, emb, blocks, RMSNorm(c.width, c.eps), OutputHead(c.vocab_size, c.width),
+                        names={"embedding": "wte", "blocks": "h.{}", "final_norm": "ln_f", "head": "head"})
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_routed_feed_forward_part_alone(dtype):
+    """The toy routed feed-forward against a float64 restatement: the right expert, the right weight."""
+    part = RoutedFeedForward(48, 80, 3)
+    ts = {"router.weight": rnd((3, 48), 61, 0.5)}
+    for e in range(3):
+        ts[f"experts.{e}.gate_proj.weight"] = rnd((80, 48), 62 + 3 * e, 0.1)
+        ts[f"experts.{e}.up_proj.weight"] = rnd((80, 48), 63 + 3 * e, 0.1)
+        ts[f"experts.{e}.down_proj.weight"] = rnd((48, 80), 64 + 3 * e, 0.1)
+    ts = {k: v.to(dtype) for k, v in ts.items()}
+    bind(part, ts, dtype)
+    h = rnd((11, 48), 75).to(dtype)
+    out = part.forward(make_ctx(dtype, [11], [0]), h.to(DEV), None).cpu().numpy()
+    f = lambda t: t.float().numpy().astype(np.float64)
+    logits = f(h) @ f(ts["router.weight"]).T
+    prob = np.exp(logits - logits.max(-1, keepdims=True))
+    prob /= prob.sum(-1, keepdims=True)
+    assert len(set(prob.argmax(-1).tolist())) > 1, "the case is meant to use several experts"
+    want = np.zeros((11, 48))
+    for t in range(11):
+        e = int(prob[t].argmax())
+        want[t] = prob[t, e] * P.swiglu(f(h[t:t + 1]), f(ts[f"experts.{e}.gate_proj.weight"]),
+                                        f(ts[f"experts.{e}.up_proj.weight"]), f(ts[f"experts.{e}.down_proj.weight"]))[0]
+    assert np.abs(out - want).max() <= tol(dtype) * np.abs(want).max()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_routed_model_with_another_position_encoding(tmp_path, dtype):
+    """Registered, built, written, loaded and stepped from here: whole prompts, the tail token by
+    token, an unequal batch and generation agree, and stretching the positions changes the result."""
+    wpc.register_architecture("ToyRoutedLM", RoutedConfig, build_routed)
+    try:
+        cfg = RoutedConfig(vocab_size=70, width=48, n_layers=3, n_heads=3, n_kv_heads=1, inner=56, n_experts=3,
+                           theta=10000.0, factor=4.0, eps=1e-5)
+        folder = wpc.write_random_model(str(tmp_path / "routed"), cfg, 5, getattr(torch, dtype))
+        eng = wpc.Engine.from_folder(folder, dtype=dtype, max_tokens=1024, max_sequences=4)
+        toks = np.random.default_rng(1).integers(0, 70, size=40).tolist()
+        from helpers import run_batch, run_tail_one_by_one, run_whole
+        whole = run_whole(eng, toks)
+        tail = run_tail_one_by_one(eng, toks, tail=12)
+        batch = run_batch(eng, [toks, toks[:13]], [25, 4])
+        t = 2e-5 if dtype == "float32" else 5e-2
+        scale = np.abs(whole).max()
+        assert np.abs(tail - whole).max() <= t * scale
+        assert np.abs(batch[0] - whole).max() <= t * scale and np.abs(batch[1] - whole[:13]).max() <= t * scale
+        out = wpc.generate(eng, [toks[:4], toks[:9]], wpc.GenerationOptions(max_tokens=5))
+        assert [len(o) for o in out] == [5, 5]
+        eng.cache.check()
+        # the same weights with unstretched positions give other logits from the second token on
+        other = dataclasses.replace(cfg, factor=1.0)
+        with open(os.path.join(folder, "config.json"), "w") as fjson:
+            json.dump(other.to_dict(), fjson)
+        eng2 = wpc.Engine.from_folder(folder, dtype=dtype, max_tokens=1024, max_sequences=4)
+        whole2 = run_whole(eng2, toks)
+        assert np.abs(whole2[0] - whole[0]).max() <= t * scale          # position 0 is not rotated either way
+        assert np.abs(whole2[5:] - whole[5:]).max() > 1e-3 * scale
+    finally:
+        wpc.unregister_architecture("ToyRoutedLM")
