@@ -161,6 +161,8 @@ def linear_plain(x, w, bias=None, out_dtype=None, residual=None) -> torch.Tensor
 
 
 _SMS = 148
+# Switches between kernels for the same product.  The defaults are the measured best on B200;
+# the tests flip them to reach the kernels that the defaults leave for other sizes.
 PAIR_TILES = True         # many tokens: 256 x 256 tiles on pairs of SMs (tcgen05 cta_group::2)
 CLUSTER_SPLITS = True     # the CTAs that split one tile's K form a cluster and add up through shared memory
 # Products that add into the float32 residual with few tokens and a short K keep the older
@@ -270,7 +272,7 @@ def pair_tiles(M: int, N: int, swap: bool, bn: int) -> bool:
     return bool(PAIR_TILES and not swap and bn == 256 and M >= 256 and (M % 256 == 0 or M % 256 > 128))
 
 
-PAIR_WIDTHS = (256,)
+PAIR_WIDTHS = (256,)      # tile widths that pair_tile_width may choose from (the kernel takes 128..256 in steps of 16)
 
 
 def pair_tile_width(M: int, N: int) -> int:
@@ -424,7 +426,7 @@ def qk_rope_kv_store(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim:
 
 
 PREFILL_ATTENTION_TILES = 1     # row tiles of 128 rows to a CTA of the tcgen05 prefill attention (1 or 2)
-FUSE_ROPE_STORE = True     # few tokens: the q/k/v product rotates and writes the cache in its tail
+FUSE_ROPE_STORE = True     # the q/k/v product rotates and writes the cache itself (cluster tail, pair epilogue)
 
 
 def linear_qk_rope_kv_store(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], n_heads: int,
