@@ -394,7 +394,8 @@ decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* 
       }
       __syncthreads();
       if (s_last) {
-        __threadfence();
+        // (every writer fenced its partial results before it took its ticket, and the copies below
+        // read through L2, where those results are: no fence is needed on this side)
         // All partial results of the pair come into shared memory with one burst of cp.async
         // (loads through registers would go a few at a time, each batch a trip to L2), in
         // chunks of as many parts as fit; a warp per row turns maxima and sums into weights.
