@@ -28,7 +28,8 @@
 // tickets: every CTA of a tile writes its partial sums to scratch memory and takes a ticket;
 // the CTA that draws the last ticket adds them in slice order and runs the epilogue.  Nobody
 // waits for anybody.  (3) When the product is added to a float32 output anyway, the slices
-// add their shares with red.global.add (normal arrangement).
+// may add their shares with red.global.add (split products of the normal arrangement; in the
+// swapped one the caller chooses it for few tokens and a short K, see ops.py).
 // Every wait on an mbarrier is bounded: when it runs out the kernel records
 // WPC_ERR_DEVICE_WAIT in `status`, lets its copies land, frees its tensor memory and returns.
 // The cluster barriers are hardware barriers that every thread of every CTA reaches on every
