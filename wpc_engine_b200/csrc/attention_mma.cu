@@ -190,10 +190,13 @@ __device__ __forceinline__ void load_q(uint32_t (&qf)[HD / 16][4], const __nv_bf
 // part_o: [(CTAs + pairs), 16, HD] float32; part_ml: [(CTAs + pairs), 16, 2]; the partial of CTA
 // c for pair k lives at slot c + k (consecutive pairs share at most one CTA, so slots are unique).
 constexpr int MAX_DECODE_SEQS = 1024;
-constexpr int DECODE_STAGES = 3;
+// Pages in the ring of a decode CTA: 3 with two CTAs to an SM; 6 when there are so few CTAs that
+// each has an SM to itself (few sequences), so that all of a CTA's pages are on their way at once.
+constexpr int DECODE_STAGES_SHARED = 3;
+constexpr int DECODE_STAGES_ALONE = 6;
 constexpr int MAX_SEGMENT_PAGES = 512;
 
-template <int HD>
+template <int HD, int DECODE_STAGES>
 __global__ void __launch_bounds__(THREADS)
 decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* __restrict__ out, int out_stride,
               const __nv_bfloat16* __restrict__ k_pages, const __nv_bfloat16* __restrict__ v_pages,
@@ -584,28 +587,43 @@ prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16*
   }
 }
 
+template <int HD, int STAGES>
+static int launch_decode_stages(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+                                const void* v_pages, const int* page_table, int table_width, const int* ctx_lens, int B,
+                                int nh, int nkv, float scale, int window, int n_ctas, float* part_o, float* part_ml,
+                                int* counters, cudaStream_t stream) {
+  // shared memory: the page buffers, reused for the merge of the warps and for the combine
+  const int merge_bytes = (4 * 16 * HD + 2 * 4 * 16) * (int)sizeof(float);
+  const int combine_bytes = (2 * 16 * n_ctas + 16 + 16 * HD) * (int)sizeof(float);   // weights and room for one part
+  int smem = STAGES * 2 * Cfg<HD>::PAGE_ELEMS * 2;
+  if (merge_bytes > smem) smem = merge_bytes;
+  if (combine_bytes > smem) smem = combine_bytes;
+  static int configured = 0;
+  if (configured < smem) {
+    cudaError_t e = cudaFuncSetAttribute(decode_kernel<HD, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = smem;
+  }
+  wpc::launch(decode_kernel<HD, STAGES>, dim3(n_ctas), THREADS, smem, stream, 
+      (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pages,
+      (const __nv_bfloat16*)v_pages, page_table, table_width, ctx_lens, B, nh, nkv, scale * LOG2E, window,
+      part_o, part_ml, counters, smem);
+  return launch_status();
+}
+
 template <int HD>
 static int launch_decode(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                          const void* v_pages, const int* page_table, int table_width, const int* ctx_lens, int B,
                          int nh, int nkv, float scale, int window, int n_ctas, float* part_o, float* part_ml,
                          int* counters, cudaStream_t stream) {
-  // shared memory: the page buffers, reused for the merge of the warps and for the combine
-  const int merge_bytes = (4 * 16 * HD + 2 * 4 * 16) * (int)sizeof(float);
-  const int combine_bytes = (2 * 16 * n_ctas + 16 + 16 * HD) * (int)sizeof(float);   // weights and room for one part
-  int smem = DECODE_STAGES * 2 * Cfg<HD>::PAGE_ELEMS * 2;
-  if (merge_bytes > smem) smem = merge_bytes;
-  if (combine_bytes > smem) smem = combine_bytes;
-  static int configured = 0;
-  if (configured < smem) {
-    cudaError_t e = cudaFuncSetAttribute(decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return (int)e;
-    configured = smem;
-  }
-  wpc::launch(decode_kernel<HD>, dim3(n_ctas), THREADS, smem, stream, 
-      (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pages,
-      (const __nv_bfloat16*)v_pages, page_table, table_width, ctx_lens, B, nh, nkv, scale * LOG2E, window,
-      part_o, part_ml, counters, smem);
-  return launch_status();
+  // with at most a CTA to an SM the ring takes all the shared memory it can use
+  if (n_ctas <= 148 && DECODE_STAGES_ALONE * 2 * Cfg<HD>::PAGE_ELEMS * 2 <= 220 * 1024)
+    return launch_decode_stages<HD, DECODE_STAGES_ALONE>(q, q_stride, out, out_stride, k_pages, v_pages, page_table,
+                                                         table_width, ctx_lens, B, nh, nkv, scale, window, n_ctas,
+                                                         part_o, part_ml, counters, stream);
+  return launch_decode_stages<HD, DECODE_STAGES_SHARED>(q, q_stride, out, out_stride, k_pages, v_pages, page_table,
+                                                        table_width, ctx_lens, B, nh, nkv, scale, window, n_ctas,
+                                                        part_o, part_ml, counters, stream);
 }
 
 template <int HD>

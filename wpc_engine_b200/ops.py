@@ -531,7 +531,29 @@ def plan_decode_ctas(n_seqs: int, n_kv_heads: int, max_ctx_len: int, window: Opt
         # combining at all (64 sequences x 4 KV heads of 4,000 positions: 91 against 99 us);
         # with fewer pairs than that, fewer CTAs would stream too little (192 CTAs: 90 against 77 us)
         return pairs
-    return max(1, min(2 * _SMS, pairs * max(blocks // 4, 1)))
+    # Otherwise the count with the least estimated time (microseconds, fitted to measurements at
+    # the 7B shape: a page takes a CTA 1.05 us when it has an SM and a deep ring to itself, 1.5 us
+    # when two share an SM and its bandwidth, which also costs about 2 us at the start; combining
+    # the parts of a pair costs about 3 + 0.12 per part).  When all sequences are about equally long, a share of pages that
+    # divides a pair's pages keeps every CTA inside one pair; a CTA that straddles two pairs
+    # fills its ring, merges and takes a ticket twice (about 8 us).  One sequence of 4,000
+    # positions: 84 CTAs of 3 pages, 14 us, against 60 CTAs of 4 or 5 pages, 18 us.
+    def estimate(n, per, aligned):
+        page, start = (1.05, 0.0) if n <= _SMS else (1.5, 2.0)
+        parts = -(-blocks // per)
+        return start + per * page + (3.0 + 0.12 * parts if parts > 1 else 0.0) + (0.0 if aligned else 8.0) + 0.002 * n
+
+    units = pairs * blocks
+    target = max(1, min(2 * _SMS, pairs * max(blocks // 4, 1)))
+    best_n, best_t = target, estimate(target, -(-units // target), False)
+    for per in range(1, blocks + 1):
+        if blocks % per == 0:
+            n = pairs * (blocks // per)
+            if n <= 2 * _SMS:
+                t = estimate(n, per, True)
+                if t < best_t:
+                    best_n, best_t = n, t
+    return best_n
 
 
 def attention_plain(q, n_heads, n_kv_heads, head_dim, k_pages, v_pages, page_table, seq_of_token, positions,
