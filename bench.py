@@ -44,10 +44,11 @@ def peaks():
     try:
         with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
             m = json.load(f)
-        hbm = float(m.get("hbm_gbs", hbm))
-        tf = float(m.get("bf16_tflops", tf))
-        src = "measured"
-    except (OSError, ValueError):
+        got = [k for k in ("hbm_gbs", "bf16_tflops") if isinstance(m.get(k), (int, float)) and m[k] > 0]
+        hbm = float(m["hbm_gbs"]) if "hbm_gbs" in got else hbm
+        tf = float(m["bf16_tflops"]) if "bf16_tflops" in got else tf       # the burst figure: the larger denominator
+        src = "measured" if len(got) == 2 else ("fallback" if not got else "measured " + got[0] + ", fallback for the other")
+    except (OSError, ValueError, TypeError, AttributeError):
         pass
     return hbm, tf, src
 
