@@ -3,7 +3,8 @@
 they mean there.  The reference tokenizes `--prompt TEXT`; this library takes token ids, so
 the prompt is `--prompt-ids "1,2,3;4,5"` (`;` separates the requests of a batch).  Added:
 `--temperature`, `--seed`, `--stop-ids`, `--dtype`, `--random-weights` (with `--config FILE`,
-writes a model folder into `--model` first).  `--arch` names the architecture or `auto`
+writes a model folder into `--model` first), `--max-seq-len`, `--print-logits K`, `--max-batch`,
+`--cache-tokens`.  `--arch` names the architecture or `auto`
 (config.json decides, main.rs:69-82).  Standard output carries one JSON line per request;
 diagnostics go to standard error in the reference's wording (main.rs:100-104, 294, 309, 424,
 429).
@@ -43,6 +44,11 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--config", help="config.json for --random-weights")
     ap.add_argument("--max-batch", type=int, default=None)
     ap.add_argument("--cache-tokens", type=int, default=None, help="positions the cache holds (default: what fits the prompts)")
+    ap.add_argument("--max-seq-len", type=int, default=None,
+                    help="longest sequence (prompt plus generated tokens) that is accepted; default: the model's "
+                         "max_position_embeddings")
+    ap.add_argument("--print-logits", type=int, default=0, metavar="K",
+                    help="also print the K greatest next-token logits after each prompt, one JSON line per request")
     return ap
 
 
@@ -74,6 +80,13 @@ def main(argv=None) -> int:
         write_random_model(args.model, cfg, args.seed, torch.bfloat16 if dtype == "bfloat16" else torch.float32)
         print(f"wrote random weights (seed {args.seed}) to {args.model}", file=sys.stderr)
 
+    if args.max_seq_len is not None:
+        for i, p in enumerate(prompts):
+            if len(p) + args.max_tokens > args.max_seq_len:
+                print(f"error: request {i} needs {len(p)} + {args.max_tokens} positions, --max-seq-len is {args.max_seq_len}",
+                      file=sys.stderr)
+                return 2
+
     raw = read_config_json(args.model)
     if args.arch != "auto":
         raw = dict(raw, architectures=[args.arch]) if args.arch[:1].isupper() else dict(raw, architectures=[], model_type=args.arch)
@@ -94,6 +107,16 @@ def main(argv=None) -> int:
         else stop_ids_of_folder(args.model)
     if stop:
         print(f"stop tokens: {stop}", file=sys.stderr)
+    if args.print_logits > 0:
+        from . import SequenceStep
+        for i, p in enumerate(prompts):
+            slot = engine.open_sequence()
+            try:
+                row = engine.step([SequenceStep(slot, p, want=[len(p) - 1])])[0].float()
+            finally:
+                engine.close_sequence(slot)
+            vals, ids = torch.topk(row, min(args.print_logits, row.numel()))
+            print(json.dumps({"request": i, "top_logits": [[int(t), float(v)] for t, v in zip(ids.tolist(), vals.tolist())]}))
     opts = GenerationOptions(max_tokens=args.max_tokens, temperature=args.temperature, seed=args.seed,
                              stop_token_ids=stop, banned_token_ids=banned_from_env(), max_batch=args.max_batch)
     t1 = time.time()
