@@ -3,6 +3,7 @@
 a second at 2,048 tokens, at the Qwen2.5-7B shape with random bfloat16 weights on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--layers L]
+    python bench.py --shape 0.5b|32b        # the two other measured shapes, each with its own workload
 
 Prints one JSON line.  `value` is device-timed decode tokens a second (CUDA events around K
 single-token steps of the engine, sampling included); `e2e` is the same through the Python
@@ -34,6 +35,20 @@ SHAPE_7B = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidd
                 rope_theta=1000000.0, rms_norm_eps=1e-6, max_position_embeddings=32768,
                 use_sliding_window=False, tie_word_embeddings=False)
 FULL_LAYERS = 28
+# The other shapes that are measured, each with the workload it is quoted on: a batch of
+# prompts through generate(), then a fixed number of single-token steps.
+OTHER_SHAPES = {
+    "0.5b": dict(name="Qwen2.5-0.5B shape", batch=16, prompt_lens=(64, 1024), decode_steps=256,
+                 raw=dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidden_layers=24, hidden_size=896,
+                          num_attention_heads=14, num_key_value_heads=2, intermediate_size=4864, vocab_size=151936,
+                          rope_theta=1000000.0, rms_norm_eps=1e-6, max_position_embeddings=32768,
+                          use_sliding_window=False, tie_word_embeddings=True)),
+    "32b": dict(name="Qwen2.5-32B shape", batch=8, prompt_lens=(1024, 1024), decode_steps=512,
+                raw=dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidden_layers=64, hidden_size=5120,
+                         num_attention_heads=40, num_key_value_heads=8, intermediate_size=27648, vocab_size=152064,
+                         rope_theta=1000000.0, rms_norm_eps=1e-6, max_position_embeddings=32768,
+                         use_sliding_window=False, tie_word_embeddings=False)),
+}
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
 BATCH = 8
@@ -120,13 +135,83 @@ def prefill_flops(cfg, layers, T):
     return linear + attn + 2 * cfg.vocab_size * h
 
 
+def other_shape(args):
+    """One of OTHER_SHAPES through generate(): unequal prompts prefilled in one step, then the
+    workload's number of single-token steps, host token ids in and out.  The first call warms up
+    (kernels compile, graphs are captured); the second is timed by generate()'s own clocks."""
+    import torch
+    import wpc_engine_b200 as wpc
+    from wpc_engine_b200 import ops
+    from wpc_engine_b200.cache import PAGE
+
+    torch.cuda.set_device(0)
+    hbm_peak, tf_peak, peak_src = peaks()
+    w = OTHER_SHAPES[args.shape]
+    full = w["raw"]["num_hidden_layers"]
+    layers = args.layers if args.layers is not None else full
+    cfg = wpc.Qwen2Config.from_dict(dict(w["raw"], num_hidden_layers=layers))
+    batch, steps = w["batch"], w["decode_steps"]
+    gen = torch.Generator().manual_seed(0)
+    lo, hi = w["prompt_lens"]
+    lens = [lo] * batch if lo == hi else torch.randint(lo, hi + 1, (batch,), generator=gen).tolist()
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=gen).tolist() for n in lens]
+    need = sum((n + steps + PAGE) // PAGE * PAGE for n in lens)
+    engine = wpc.Engine.from_random(cfg, seed=0, dtype="bfloat16", device="cuda:0", max_tokens=need + PAGE,
+                                    max_sequences=batch + 1)
+    opts = wpc.GenerationOptions(max_tokens=steps + 1)       # the first token comes from the prefill step
+    wpc.generate(engine, prompts, opts, stats={})
+    stats = {}
+    l0 = ops.launch_count + engine.graph_launches
+    with ClockSampler() as clocks:
+        wpc.generate(engine, prompts, opts, stats=stats)
+    launches = ops.launch_count + engine.graph_launches - l0
+    n_steps = len(stats["decode_step_s"])
+    secs = stats["decode_s"]
+    value = stats["decode_tokens"] / secs
+    tail = min(args.steps, n_steps)
+    mean_ctx = sum(lens) / batch + (n_steps + 1) / 2
+    step_bytes = weight_bytes(cfg, layers) + batch * mean_ctx * kv_bytes_per_token(cfg, layers)
+    achieved = step_bytes / (secs / n_steps) / 1e9
+    T = stats["prefill_tokens"]
+    pre_flops = sum(prefill_flops(cfg, layers, n) for n in lens)
+    from wpc_engine_b200.engine.batch import StepLayout
+    lay = StepLayout(batch, batch, batch, (max(lens) + steps + PAGE) // PAGE, 1)
+    line = {
+        "metric": f"decode tokens/s at batch {batch} ({w['name']}, bf16), through generate()",
+        "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": n_steps, "warmup": n_steps + 1,
+        "ms_per_step": secs / n_steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: random N(0, 0.02) weights, uniform random token ids",
+        "config": {"model": w["name"], "global_batch": batch, "seq_len": max(lens) + steps,
+                   "parallelism": "single GPU", "layers": layers, "layers_of_shape": full,
+                   "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+                   "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
+                   "prompt_len_min": min(lens), "prompt_len_max": max(lens), "prefill_tokens": T,
+                   "decode_steps": n_steps, "l2": "inputs larger than L2 (weights), no flush",
+                   "cuda_graphs": engine.use_graphs},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": lay.total * 4 + batch * 4,
+                "d2h_bytes_per_step": batch * 4,
+                "last_steps_value": sum(stats["decode_step_tokens"][-tail:]) / sum(stats["decode_step_s"][-tail:]),
+                "last_steps": tail},
+        "gpu_launches": launches,
+        "prefill": {"value": T / stats["prefill_s"], "tokens": T, "ms": stats["prefill_s"] * 1e3,
+                    "frac": pre_flops / stats["prefill_s"] / (tf_peak * 1e12)},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
+                     "peaks": peak_src},
+        "clocks": clocks.summary(), "impl": "ours",
+    }
+    print(json.dumps(line))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the shape has (named in config)")
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the shape has (named in config)")
+    ap.add_argument("--shape", default="7b", choices=["7b"] + sorted(OTHER_SHAPES),
+                    help="7b: the headline; the others run their own workload through generate()")
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64")
     args = ap.parse_args()
 
@@ -140,6 +225,10 @@ def main():
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.shape != "7b":
+        return other_shape(args)
+    if args.layers is None:
+        args.layers = FULL_LAYERS
 
     import torch
     import wpc_engine_b200 as wpc

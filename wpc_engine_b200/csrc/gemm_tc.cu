@@ -152,10 +152,14 @@ __device__ __forceinline__ uint32_t peer_smem(uint32_t addr, uint32_t rank) {
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
   return r;
 }
-__device__ __forceinline__ float ld_peer_f32(uint32_t addr) {
-  float v;
-  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
-  return v;
+__device__ __forceinline__ void st_peer_f32(uint32_t addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ void cluster_arrive() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait() {
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
 __device__ __forceinline__ void tmem_alloc(uint32_t* holder, int cols) {
@@ -238,10 +242,14 @@ struct Smem {
   static constexpr int HEAD_BYTES = 1024;
   static constexpr int TMEM_COLS = BN <= 32 ? 32 : BN <= 64 ? 64 : BN <= 128 ? 128 : 256;   // a power of two
   static constexpr int total(int stages) { return HEAD_BYTES + 1024 /* alignment slack */ + stages * STAGE_BYTES; }
-  static constexpr int max_stages(int ctas_per_sm) {
-    int s = (SMEM_LIMIT / ctas_per_sm - HEAD_BYTES - 1024 - 1024 /* per-CTA reserve */) / STAGE_BYTES;
+  static constexpr int max_stages(int ctas_per_sm, int extra_bytes = 0) {
+    int s = (SMEM_LIMIT / ctas_per_sm - HEAD_BYTES - 1024 - 1024 /* per-CTA reserve */ - extra_bytes) / STAGE_BYTES;
     return s > MAX_STAGES ? MAX_STAGES : (s < 2 ? 2 : s);
   }
+  // Cluster variant: behind the ring, the partial sums that the ranks of the cluster send to this
+  // CTA, [rank][row of this CTA][128] floats (at most BN + 7 rows in all), and the [4][128]
+  // floats through which the two halves of a head exchange their values.
+  static constexpr int RECV_BYTES = (BN + 7 + 4) * BM * 4;
 };
 
 __device__ __forceinline__ void store_row32(const Params& p, int row, int col0, int n_cols, const float (&v)[32]) {
@@ -342,9 +350,14 @@ struct WorkIter {
 // MT = 2: the tile is 256 rows of A by BN; the two 128-row halves are two MMAs that share the B
 // tile in shared memory (a third less operand traffic per flop) and fill both accumulators, so
 // the epilogue does not overlap the next tile.
-// CL (swapped arrangement, split K): the CTAs that share a tile form a thread-block cluster and add
-// their partial sums through distributed shared memory, in rank order; each CTA writes its
-// share of the tile's token rows.  No scratch, no tickets, no atomics.
+// CL (swapped arrangement, split K): the CTAs that share a tile form a thread-block cluster.  Token
+// row j of the tile belongs to rank j % S: every rank writes its partial sums of that row
+// straight into the owner's shared memory (writes to a peer need no answer), one cluster barrier
+// makes them visible, and the owner adds them up in rank order and writes the row.  No scratch,
+// no tickets, no atomics.  The epilogue warps run this whole path once before the dependency
+// wait, with every store switched off: a kernel runs each of its instructions once, so on the
+// first pass every line of code comes from L2 or beyond, and a dry pass while the warps
+// have nothing to do takes those misses off the critical path.
 template <int BN, bool SWAP, int MT, bool CL>
 __global__ void __launch_bounds__(THREADS, (BN <= 64 ? 2 : 1))     // narrow tiles run two CTAs to an SM
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
@@ -383,6 +396,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   __syncthreads();
   fence_after_sync();
   const uint32_t tmem_base = *tmem_holder;
+  // Cluster variant: a rank may write into a peer's shared memory only once every CTA of the
+  // cluster runs.  This comes before the dependency wait, while the kernel before still runs.
+  if (CL && p.splits > 1) cluster_sync_all();
 
   if (warp == 0) {
     if (lane == 0) {
@@ -425,6 +441,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
       }
     }
+    __syncwarp();
+    if (CL && p.splits > 1) { cluster_arrive(); cluster_wait(); }    // see the epilogue warps
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc = instr_desc(BN);
@@ -459,6 +477,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         umma_commit(accum_full + b);    // arrives when everything issued above has finished
       }
     }
+    __syncwarp();
+    if (CL && p.splits > 1) { cluster_arrive(); cluster_wait(); }
   } else {
     // ---- epilogue: warps 2..5 read lanes 32*(warp % 4) .. +31 of the accumulator ----
     const int q = warp & 3;
@@ -480,6 +500,132 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         s_rowbase[k] = (page >= 0 && page < p.n_pages) ? ((long long)page * p.rope_nkv * WPC_PAGE + pos % WPC_PAGE) : -1;
       }
     }
+    if (CL && p.splits > 1) {
+      // ---- cluster variant: one unit of work; see the comment above the kernel ----
+      asm volatile("bar.sync 1, 128;" ::: "memory");     // s_rowbase is complete
+      const int S = p.splits, my = (int)cluster_rank(), kmax = (BN + S - 1) / S;
+      WorkIter<BN, MT> work(p, true);
+      Work w;
+      work.next(w);
+      const int m0 = w.m0, n0 = w.n0;
+      const int n_valid = min(BN, p.N - n0);
+      const int feat = m0 + r;                           // this thread's feature: row of the tile = TMEM lane
+      const bool in_range = feat < p.M;
+      // With rope_hd: what this feature is (q, k or v; which head; which element)
+      const int hd = p.rope_hd, half = hd >> 1;
+      const int nq = p.rope_nh * hd, nk = p.rope_nkv * hd;
+      const int kind = !hd ? 0 : (feat < nq ? 0 : (feat < nq + nk ? 1 : 2));       // q, k, v
+      const int d = hd ? feat % hd : 0;
+      const int kvh = hd ? (kind == 1 ? (feat - nq) / hd : (kind == 2 ? (feat - nq - nk) / hd : 0)) : 0;
+      const int pr = hd ? d % half : 0;                   // index of the pair within the head
+      const bool rotated = hd && kind < 2 && pr < p.rope_R;
+      const float* recv = red_stage + r;                  // [rank][row of this CTA][128] received sums
+      float* xbuf = red_stage + S * kmax * BM;            // [4][128]
+      const uint32_t mine = smem_u32(red_stage) + (uint32_t)((my * kmax) * BM + r) * 4;
+      // Token rows my, my + S, ... are this CTA's, four of them at a time.  What a round needs
+      // from global memory is fetched a round ahead: for the first round, before the MMAs end.
+      float bias = 0.f, cs[4], sn[4], old[4];
+      __nv_bfloat16* dst[4];
+      auto fetch = [&](int j0) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int j = j0 + u * S;
+          cs[u] = 1.f; sn[u] = 0.f; old[u] = 0.f; dst[u] = nullptr;
+          if (in_range && j < n_valid) {
+            const int tok = n0 + j;
+            if (rotated) {
+              // past L1: the dry pass may have read these before the kernel that writes them ended
+              cs[u] = __ldcg(p.rope_cos + (size_t)tok * p.rope_R + pr);
+              sn[u] = __ldcg(p.rope_sin + (size_t)tok * p.rope_R + pr);
+            }
+            if (hd && kind > 0) {
+              const long long base = s_rowbase[(j - my) / S];      // page * nkv * PAGE + place in the page
+              if (base >= 0)
+                dst[u] = (kind == 1 ? p.k_pages : p.v_pages) + ((size_t)base + (size_t)kvh * WPC_PAGE) * hd + d;
+              else if (p.status) atomicExch(p.status, WPC_ERR_BAD_ARGUMENT);
+            } else if (!hd && p.accumulate) {
+              old[u] = __ldcg((const float*)p.out + (size_t)tok * p.ldc + feat);   // only this thread writes it
+            }
+          }
+        }
+      };
+      const int passes = p.k_blocks > 0 ? 2 : 1;          // always 2; the compiler must keep one copy of the body
+#pragma unroll 1
+      for (int pass = 0; pass < passes; ++pass) {
+        const bool dry = pass + 1 < passes;               // the pass that only brings the code in
+        if (!dry) pdl_wait();                             // the output and the inputs of fetch() are shared
+        if (in_range && p.bias) bias = p.bias[feat];
+        fetch(my);
+        bool ok = true;
+        if (!dry) {
+          ok = mbar_wait(accum_full, 0);
+          ok = __all_sync(0xffffffffu, ok);               // tcgen05.ld needs the whole warp on one path
+          if (!ok) atomicExch(flags, 1);
+          fence_after_sync();
+        }
+        const bool have_acc = w.n_kb > 0 && ok;
+        // the dry pass reads the accumulator that this variant never fills
+        const uint32_t lane_addr = tmem_base + (dry ? S::TMEM_COLS : 0) + ((uint32_t)(q * 32) << 16);
+        for (int c = 0; c < n_valid; c += 32) {
+          uint32_t v[32];
+          if (BN >= 32) tmem_ld32(lane_addr + c, v); else tmem_ld16(lane_addr + c, v);
+          tmem_ld_wait();
+          const int nc = min(32, n_valid - c);
+          int owner = c % S, k = c / S;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (j < nc && !dry)
+              st_peer_f32(peer_smem(mine + (uint32_t)k * (BM * 4), (uint32_t)owner), have_acc ? __uint_as_float(v[j]) : 0.f);
+            if (++owner == S) { owner = 0; ++k; }
+          }
+        }
+        if (!dry) {
+          fence_before_sync();
+          mbar_arrive(accum_empty);
+          cluster_arrive();                               // this rank's sums are on their way
+          cluster_wait();                                 // every rank's sums for this CTA's rows have arrived
+        }
+        for (int j0 = my; j0 < n_valid; j0 += 4 * S) {
+          float val[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int j = j0 + u * S;
+            float sum = 0.f;
+            if (j < n_valid) {
+              const float* row = recv + ((j - my) / S) * BM;
+              sum = row[0];
+              for (int s2 = 1; s2 < S; ++s2) sum += row[s2 * kmax * BM];     // in rank order
+            }
+            val[u] = sum + bias;
+          }
+          if (hd) {
+            // x'_i = x_i c - x_{i+half} s;  x'_{i+half} = x_{i+half} c + x_i s  (rope.rs:36-39)
+#pragma unroll
+            for (int u = 0; u < 4; ++u) xbuf[u * BM + r] = val[u];
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const float other = xbuf[u * BM + (r ^ half)];
+              if (rotated) val[u] = d < half ? val[u] * cs[u] - other * sn[u] : val[u] * cs[u] + other * sn[u];
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");     // the buffer is written again in the next round
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int j = j0 + u * S;
+            if (j < n_valid && in_range && !dry) {
+              const size_t o = (size_t)(n0 + j) * p.ldc + feat;
+              if (hd && kind > 0) { if (dst[u]) *dst[u] = __float2bfloat16_rn(val[u]); }
+              else if (p.accumulate) ((float*)p.out)[o] = old[u] + val[u];
+              else if (p.out_bf16) ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(val[u]);
+              else ((float*)p.out)[o] = val[u];
+            }
+          }
+          if (j0 + 4 * S < n_valid) fetch(j0 + 4 * S);
+        }
+      }
+      // Nothing reads a peer's shared memory: the CTA may leave when its own rows are written.
+    } else {
     pdl_wait();                                         // the output, the scratch and the tickets are shared
     int j = 0;
     WorkIter<BN, MT> work(p, CL);
@@ -499,23 +645,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const uint32_t lane_addr = tmem_base + (MT == 1 ? b : half) * S::TMEM_COLS + ((uint32_t)(q * 32) << 16);
 
       bool run_epilogue = ok;
-      if (CL && p.splits > 1) {
-        // this slice's sums go to shared memory as [token][feature of the tile] (the operand ring is
-        // free: every MMA has finished); the cluster adds them up after the barrier below
-        run_epilogue = false;
-        float* stage = (float*)tiles;
-        for (int c = 0; c < n_valid; c += 32) {
-          uint32_t v[32];
-          if (have_acc) {
-            if (BN >= 32) tmem_ld32(lane_addr + c, v); else tmem_ld16(lane_addr + c, v);
-            tmem_ld_wait();
-          }
-          const int nc = min(32, n_valid - c);
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (j < nc) stage[(c + j) * BM + r] = have_acc ? __uint_as_float(v[j]) : 0.f;
-        }
-      } else if (w.partial && p.accumulate) {
+      if (w.partial && p.accumulate) {
         // Every slice adds its share straight into the float32 output with red.global.add: no
         // scratch, no tickets, no fences.  The order in which the slices arrive is not fixed,
         // so the sum may differ in its last bits from run to run.
@@ -701,97 +831,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       mbar_arrive(accum_empty + b);
       if (!ok) break;
     }
+    }
   }
 
   fence_before_sync();
   __syncthreads();
-  if (CL && p.splits > 1) {
-    // Every thread of every CTA of the cluster comes here, whatever happened above.
-    cluster_sync_all();                                   // the partial sums of all ranks are in shared memory
-    if (warp >= 2) {
-      const int S = p.splits;
-      const int t = threadIdx.x - 64;                     // feature within the tile
-      const int tile_id = blockIdx.x / S, my = (int)cluster_rank();
-      const int tiles_m = (p.M + BM - 1) / BM;
-      const int tile_n = tile_id / tiles_m, tile_m = tile_id - tile_n * tiles_m;
-      const int m0 = tile_m * BM, n0 = tile_n * BN;
-      const int n_valid = min(BN, p.N - n0);
-      const int feat = m0 + t;
-      const float bias = (p.bias && feat < p.M) ? p.bias[feat] : 0.f;
-      const uint32_t stage = smem_u32(tiles) + (uint32_t)t * 4;
-      uint32_t peer[8];
-#pragma unroll
-      for (int s2 = 0; s2 < 8; ++s2) peer[s2] = peer_smem(stage, (uint32_t)(s2 < S ? s2 : 0));
-      // With rope_hd: what this feature is (q, k or v; which head; which element), and a buffer
-      // behind the partial sums through which the two halves of a head exchange their values.
-      const int hd = p.rope_hd, half = hd >> 1;
-      const int nq = p.rope_nh * hd, nk = p.rope_nkv * hd;
-      const int kind = !hd ? 0 : (feat < nq ? 0 : (feat < nq + nk ? 1 : 2));       // q, k, v
-      const int d = hd ? feat % hd : 0;
-      const int kvh = hd ? (kind == 1 ? (feat - nq) / hd : (kind == 2 ? (feat - nq - nk) / hd : 0)) : 0;
-      const int pr = hd ? d % half : 0;                    // index of the pair within the head
-      const bool rotated = hd && kind < 2 && pr < p.rope_R;
-      float* xbuf = (float*)(tiles + BN * BM * 4);         // [4][128]
-      // token rows my, my + S, ... are this CTA's; four of them in flight at a time
-      for (int j0 = my; j0 < n_valid; j0 += 4 * S) {
-        float v[4][8];
-        float cs[4], sn[4];
-        __nv_bfloat16* dst[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int j = j0 + u * S;
-#pragma unroll
-          for (int s2 = 0; s2 < 8; ++s2) v[u][s2] = (j < n_valid && s2 < S) ? ld_peer_f32(peer[s2] + (uint32_t)j * (BM * 4)) : 0.f;
-          cs[u] = 1.f; sn[u] = 0.f; dst[u] = nullptr;
-          if (hd && j < n_valid && feat < p.M) {
-            const int tok = n0 + j;
-            if (rotated) {
-              cs[u] = p.rope_cos[(size_t)tok * p.rope_R + pr];
-              sn[u] = p.rope_sin[(size_t)tok * p.rope_R + pr];
-            }
-            if (kind > 0) {
-              const long long base = s_rowbase[(j - my) / S];      // page * nkv * PAGE + place in the page
-              if (base >= 0)
-                dst[u] = (kind == 1 ? p.k_pages : p.v_pages) + ((size_t)base + (size_t)kvh * WPC_PAGE) * hd + d;
-              else if (p.status) atomicExch(p.status, WPC_ERR_BAD_ARGUMENT);
-            }
-          }
-        }
-        float val[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          float sum = v[u][0];
-#pragma unroll
-          for (int s2 = 1; s2 < 8; ++s2) sum += v[u][s2];   // in rank order; ranks beyond S hold zeros
-          val[u] = sum + bias;
-        }
-        if (hd) {
-          // x'_i = x_i c - x_{i+half} s;  x'_{i+half} = x_{i+half} c + x_i s  (rope.rs:36-39)
-#pragma unroll
-          for (int u = 0; u < 4; ++u) xbuf[u * BM + t] = val[u];
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const float other = xbuf[u * BM + (t ^ half)];
-            if (rotated) val[u] = d < half ? val[u] * cs[u] - other * sn[u] : val[u] * cs[u] + other * sn[u];
-          }
-          asm volatile("bar.sync 1, 128;" ::: "memory");     // the buffer is written again in the next round
-        }
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int j = j0 + u * S;
-          if (j < n_valid && feat < p.M) {
-            const size_t o = (size_t)(n0 + j) * p.ldc + feat;
-            if (hd && kind > 0) { if (dst[u]) *dst[u] = __float2bfloat16_rn(val[u]); }
-            else if (p.accumulate) ((float*)p.out)[o] += val[u];
-            else if (p.out_bf16) ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(val[u]);
-            else ((float*)p.out)[o] = val[u];
-          }
-        }
-      }
-    }
-    cluster_sync_all();                                   // no peer reads this CTA's shared memory any more
-  }
   if (flags[0]) {
     // a wait ran out: give copies in flight time to land before shared memory goes away
     if (threadIdx.x == 0 && p.status) atomicExch(p.status, WPC_ERR_DEVICE_WAIT);
@@ -1172,16 +1216,14 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, Params& p, cudaS
     if (p.splits < 2 || p.splits > 8) return WPC_ERR_UNSUPPORTED;
     // a ring so short that two CTAs fit on an SM: more clusters then run side by side (the
     // clusters of a GPC's SMs leave fewer SMs idle), and all of them must stream at once
-    int stages = S::max_stages(2);
+    int stages = S::max_stages(BN <= 64 ? 2 : 1, S::RECV_BYTES);
     const int kb_per = (p.k_blocks + p.splits - 1) / p.splits;
     if (stages > kb_per) stages = kb_per < 2 ? 2 : kb_per;
     if (stages > g_stage_limit) stages = g_stage_limit < 2 ? 2 : g_stage_limit;
-    // the ring doubles as the place of the partial sums ([BN][128] floats) and of the tail's exchange buffer
-    constexpr int TAIL_BYTES = BN * BM * 4 + 4 * BM * 4;
-    if (stages * S::STAGE_BYTES < TAIL_BYTES) stages = (TAIL_BYTES + S::STAGE_BYTES - 1) / S::STAGE_BYTES;
     p.stages = stages;
-    wpc::launch_clusters(gemm_tc_kernel<BN, SWAP, MT, CL>, dim3((unsigned)units), THREADS, S::total(stages), stream,
-                         (unsigned)p.splits, ma, mb, p);
+    // behind the ring: the sums that the other ranks send (see Smem::RECV_BYTES)
+    wpc::launch_clusters(gemm_tc_kernel<BN, SWAP, MT, CL>, dim3((unsigned)units), THREADS, S::total(stages) + S::RECV_BYTES,
+                         stream, (unsigned)p.splits, ma, mb, p);
     return launch_status();
   }
   // Many tiles in the normal arrangement: one persistent CTA per SM walks the tiles, its
@@ -1388,8 +1430,9 @@ int wpc_gemm_tc_rope_store(const void* w, int ldw, const void* x, int ldx, int t
 
 // How many clusters of `splits` CTAs of the swapped kernel with tile width bn the device can
 // hold at once (0 if the sizes are not supported); -1 on a CUDA error.  The runtime's answer is
-// for one CTA to an SM; the kernel keeps its ring so short that two fit (see launch), and
-// measured on B200 twice as many clusters then run side by side, so the answer is doubled.
+// for one CTA to an SM; up to a tile width of 64 the kernel keeps its ring so short that two fit
+// (see launch), and measured on B200 twice as many clusters then run side by side, so the answer
+// is doubled there.
 int wpc_gemm_tc_cluster_capacity(int bn, int splits) {
   if (splits < 2 || splits > 8) return 0;
   cudaLaunchConfig_t cfg = {};
@@ -1407,7 +1450,7 @@ int wpc_gemm_tc_cluster_capacity(int bn, int splits) {
 #define WPC_CAP(BN_)                                                                                              \
   {                                                                                                               \
     using S = Smem<BN_, 1>;                                                                                       \
-    cfg.dynamicSmemBytes = S::total(S::max_stages(2));                                                            \
+    cfg.dynamicSmemBytes = S::total(S::max_stages(BN_ <= 64 ? 2 : 1, S::RECV_BYTES)) + S::RECV_BYTES;             \
     e = cudaFuncSetAttribute(gemm_tc_kernel<BN_, true, 1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,     \
                              S::total(S::max_stages(1)));                                                         \
     if (e == cudaSuccess) e = cudaOccupancyMaxActiveClusters(&n, gemm_tc_kernel<BN_, true, 1, true>, &cfg);       \
@@ -1421,7 +1464,7 @@ int wpc_gemm_tc_cluster_capacity(int bn, int splits) {
   }
 #undef WPC_CAP
   if (e != cudaSuccess) { cudaGetLastError(); return -1; }
-  return 2 * n;
+  return bn <= 64 ? 2 * n : n;
 }
 
 }  // extern "C"
