@@ -283,6 +283,50 @@ def test_attention_decode_splits(nh, nkv, hd, window, splits):
     close(got.cpu(), want, torch.bfloat16)
 
 
+@pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 16), (3, 1, 32), (4, 2, 48), (14, 2, 64), (28, 4, 128), (8, 1, 128), (2, 2, 80)])
+@pytest.mark.parametrize("window", [None, 100])
+@pytest.mark.parametrize("cluster", [2, 3, 8])
+def test_attention_decode_clusters(nh, nkv, hd, window, cluster):
+    """A cluster of CTAs to each (sequence, kv head) pair: ranks without pages (a sequence of one
+    page among eight ranks), shares that do not divide, every length at once."""
+    lens, new = [1, 64, 65, 700, 333, 128, 1000], [1] * 7
+    qkv, kp, vp, table, seq, pos = paged_case(torch.bfloat16, nh, nkv, hd, lens, new, seed=19)
+    cu = torch.arange(8, dtype=torch.int32, device=DEV)
+    ctx = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(hd)
+    got = ops.attention(qkv, nh, nkv, hd, kp, vp, table, cu, ctx, seq, pos, scale, window, 1, max(lens), cluster=cluster)
+    again = ops.attention(qkv, nh, nkv, hd, kp, vp, table, cu, ctx, seq, pos, scale, window, 1, max(lens), cluster=cluster)
+    want = ref.attention_plain(qkv.cpu(), nh, nkv, hd, kp.cpu(), vp.cpu(), table.cpu(), seq.cpu(), pos.cpu(),
+                               scale, window)
+    close(got.cpu(), want, torch.bfloat16)
+    assert torch.equal(got, again)              # ranks are added in order: the same bits every run
+
+
+def test_attention_decode_cluster_finds_one_far_key():
+    """One key among thousands is made to stand out; whichever rank holds its page, the output is
+    that key's value."""
+    nh, nkv, hd = 28, 4, 128
+    lens = [4000, 3000]
+    qkv, kp, vp, table, seq, pos = paged_case(torch.bfloat16, nh, nkv, hd, lens, [1, 1], seed=23)
+    cu = torch.arange(3, dtype=torch.int32, device=DEV)
+    ctx = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    for far in (0, 63, 64, 1999, 2999):
+        kp2 = kp.clone()
+        for b in range(2):
+            page = int(table[b, far // 64])
+            kp2[page, :, far % 64, :] = 0
+            kp2[page, :, far % 64, 0] = 40.0
+        q2 = qkv.clone()
+        q2[:, : nh * hd] = 0
+        q2[:, 0 : nh * hd : hd] = 40.0                      # every head asks for element 0
+        got = ops.attention(q2, nh, nkv, hd, kp2, vp, table, cu, ctx, seq, pos, 1.0, None, 1, max(lens), cluster=8)
+        for b in range(2):
+            page = int(table[b, far // 64])
+            want = vp[page, :, far % 64, :].float()            # [nkv, hd]
+            out = got[b].float().view(nkv, nh // nkv, hd)
+            assert (out - want[:, None, :]).abs().max().item() <= 2e-2 * want.abs().max().item() + 1e-3, (far, b)
+
+
 def test_attention_prefill_window_edges():
     """A window's edge: the key just outside the window is made huge; it must not be seen, and
     the key just inside must."""

@@ -467,6 +467,173 @@ decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* 
   }
 }
 
+// ---- decode, a cluster to a pair ------------------------------------------------------------------
+// When the (sequence, kv head) pairs are few and about equally long, the CTAs of a pair form a
+// thread-block cluster of C ranks; rank r takes the r-th share of the pages that the pair's
+// query sees.  The partial results do not go through global memory: every rank writes its
+// unnormalised outputs for the r'-th share of the pair's n_rep * HD output elements straight
+// into rank r''s shared memory, and its running maxima and sums into every rank's; one
+// cluster barrier makes them visible, and every rank then normalises and writes its share of
+// the output, adding the ranks in order.  No scratch, no tickets, no second pass.
+constexpr int CLUSTER_DECODE_MAX_OUT = 1024;      // n_rep * HD that the receive buffer takes
+
+template <int HD, int DECODE_STAGES>
+__global__ void __launch_bounds__(THREADS)
+decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* __restrict__ out, int out_stride,
+                      const __nv_bfloat16* __restrict__ k_pages, const __nv_bfloat16* __restrict__ v_pages,
+                      const int* __restrict__ page_table, int table_width, const int* __restrict__ ctx_lens, int B,
+                      int nh, int nkv, float scale_log2, int window, int C) {
+  pdl_trigger();
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  __nv_bfloat16* ks = (__nv_bfloat16*)smem_raw;                       // [DECODE_STAGES][PAGE][STRIDE]
+  __nv_bfloat16* vs = ks + DECODE_STAGES * Cfg<HD>::PAGE_ELEMS;
+  __shared__ int s_pages[MAX_SEGMENT_PAGES];                          // page numbers of this rank's share
+  __shared__ float s_recv_o[CLUSTER_DECODE_MAX_OUT + 8];              // [rank][element of this rank's share]
+  __shared__ float s_recv_ml[8 * 16 * 2];                             // [rank][row][maximum, sum]
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n_rep = nh / nkv;
+  const size_t page_elems = (size_t)nkv * PAGE * HD;
+  const int rank = (int)cluster_rank();
+  const int pair = blockIdx.x / C, b = pair / nkv, g = pair - b * nkv;
+  cluster_sync_all();                       // every rank runs: its shared memory may be written
+
+  const int L = ctx_lens[b];
+  const int pos = L - 1;
+  const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const int nb = pos >= 0 ? pos / PAGE - lo / PAGE + 1 : 0;           // pages that the query sees
+  const int base = nb / C, extra = nb - base * C;                     // the first `extra` ranks take a page more
+  const int blk0 = lo / PAGE + rank * base + min(rank, extra), blk1 = blk0 + base + (rank < extra ? 1 : 0);
+  const int* gtable = page_table + (size_t)b * table_width + blk0;
+  const int n_seg = blk1 - blk0;
+  for (int i = tid; i < min(n_seg, MAX_SEGMENT_PAGES); i += THREADS) s_pages[i] = gtable[i];
+  // Up to here only the step's lengths and page numbers were read, which the host wrote before
+  // the step's first kernel started.  Queries, keys and values come from the kernel ahead.
+  pdl_wait();
+  __syncthreads();
+  auto page_of = [&](int blk) { const int i = blk - blk0; return i < MAX_SEGMENT_PAGES ? s_pages[i] : gtable[i]; };
+
+#pragma unroll
+  for (int i = 0; i < DECODE_STAGES - 1; ++i) {
+    if (blk0 + i < blk1) {
+      const size_t src = (size_t)max(page_of(blk0 + i), 0) * page_elems + (size_t)g * PAGE * HD;
+      load_page<HD>(ks + i * Cfg<HD>::PAGE_ELEMS, k_pages + src, tid);
+      load_page<HD>(vs + i * Cfg<HD>::PAGE_ELEMS, v_pages + src, tid);
+    }
+    cp_async_commit();
+  }
+  const int r_lo = lane >> 2, r_hi = r_lo + 8;                        // rows = heads of the group
+  const __nv_bfloat16* qtok = q + (size_t)b * q_stride + (size_t)g * n_rep * HD;
+  uint32_t qf[HD / 16][4];
+  load_q<HD>(qf, r_lo < n_rep ? qtok + r_lo * HD : nullptr, r_hi < n_rep ? qtok + r_hi * HD : nullptr, lane);
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float o[HD / 8][4];
+#pragma unroll
+  for (int d = 0; d < HD / 8; ++d)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[d][i] = 0.f;
+  for (int blk = blk0; blk < blk1; ++blk) {
+    const int buf = (blk - blk0) % DECODE_STAGES;
+    if (blk + DECODE_STAGES - 1 < blk1) {
+      const int nbuf = (buf + DECODE_STAGES - 1) % DECODE_STAGES;
+      const size_t src = (size_t)max(page_of(blk + DECODE_STAGES - 1), 0) * page_elems + (size_t)g * PAGE * HD;
+      load_page<HD>(ks + nbuf * Cfg<HD>::PAGE_ELEMS, k_pages + src, tid);
+      load_page<HD>(vs + nbuf * Cfg<HD>::PAGE_ELEMS, v_pages + src, tid);
+    }
+    cp_async_commit();
+    cp_async_wait<DECODE_STAGES - 1>();
+    __syncthreads();
+    const int key0 = warp * 16;                                       // this warp's quarter of the page
+    const int abs0 = blk * PAGE + key0;
+    if (abs0 <= pos && abs0 + 15 >= lo) {
+      float s[2][4];
+      scores<HD, 2>(qf, ks + buf * Cfg<HD>::PAGE_ELEMS, key0, s, lane);
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int kabs = abs0 + nt * 8 + (lane & 3) * 2 + (i & 1);
+          s[nt][i] = (kabs >= lo && kabs <= pos) ? s[nt][i] * scale_log2 : -INFINITY;
+        }
+      softmax_step<HD, 2>(s, m, l, o);
+      uint32_t pf[1][4];
+      to_fragments<2>(s, pf);
+      weighted_values<HD, 2>(pf, vs + buf * Cfg<HD>::PAGE_ELEMS, key0, o, lane);
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+
+  // ---- merge the four warps (each saw a quarter of every page) through shared memory ----
+  float* so = (float*)smem_raw;                         // [4][16][HD]
+  float* sm = so + 4 * 16 * HD;                         // [4][16]
+  float* sl = sm + 4 * 16;                              // [4][16]
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+    l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+  }
+#pragma unroll
+  for (int d = 0; d < HD / 8; ++d) {
+    const int c = d * 8 + (lane & 3) * 2;
+    so[(warp * 16 + r_lo) * HD + c] = o[d][0];
+    so[(warp * 16 + r_lo) * HD + c + 1] = o[d][1];
+    so[(warp * 16 + r_hi) * HD + c] = o[d][2];
+    so[(warp * 16 + r_hi) * HD + c + 1] = o[d][3];
+  }
+  if ((lane & 3) == 0) {
+    sm[warp * 16 + r_lo] = m[0];
+    sm[warp * 16 + r_hi] = m[1];
+    sl[warp * 16 + r_lo] = l[0];
+    sl[warp * 16 + r_hi] = l[1];
+  }
+  __syncthreads();
+  // ---- this rank's partial result goes to the ranks that own its elements ----
+  const int n_out = n_rep * HD, share = (n_out + C - 1) / C;
+  const uint32_t recv_o = smem_u32(s_recv_o), recv_ml = smem_u32(s_recv_ml);
+  for (int e = tid; e < n_out; e += THREADS) {
+    const int row = e / HD, d = e - row * HD;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, sm[w * 16 + row]);
+    float acc = 0.f, Lsum = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = sm[w * 16 + row];
+      const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
+      acc += f * so[(w * 16 + row) * HD + d];
+      Lsum += f * sl[w * 16 + row];
+    }
+    const int owner = e / share, idx = e - owner * share;
+    st_peer_f32(peer_smem(recv_o + (uint32_t)(rank * share + idx) * 4, (uint32_t)owner), acc);
+    if (d == 0) {
+      for (int c = 0; c < C; ++c) {
+        const uint32_t at = peer_smem(recv_ml + (uint32_t)((rank * 16 + row) * 2) * 4, (uint32_t)c);
+        st_peer_f32(at, M);
+        st_peer_f32(at + 4, Lsum);
+      }
+    }
+  }
+  cluster_arrive();
+  cluster_wait();                            // every rank's results for this rank's share have arrived
+  for (int t = tid; t < share; t += THREADS) {
+    const int e = rank * share + t;
+    if (e < n_out) {
+      const int row = e / HD, d = e - row * HD;
+      float M = -INFINITY;
+      for (int c = 0; c < C; ++c) M = fmaxf(M, s_recv_ml[(c * 16 + row) * 2]);
+      float num = 0.f, den = 0.f;
+      for (int c = 0; c < C; ++c) {                        // in rank order
+        const float mc = s_recv_ml[(c * 16 + row) * 2];
+        const float f = (mc == -INFINITY) ? 0.f : exp2f(mc - M);
+        num += f * s_recv_o[c * share + t];
+        den += f * s_recv_ml[(c * 16 + row) * 2 + 1];
+      }
+      out[(size_t)b * out_stride + (size_t)(g * n_rep + row) * HD + d] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+    }
+  }
+}
+
 // ---- prefill ------------------------------------------------------------------------------------
 template <int HD>
 __global__ void __launch_bounds__(THREADS)
@@ -626,6 +793,65 @@ static int launch_decode(const void* q, int q_stride, void* out, int out_stride,
                                                         part_o, part_ml, counters, stream);
 }
 
+template <int HD, int STAGES>
+static int launch_decode_cluster_stages(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+                                        const void* v_pages, const int* page_table, int table_width,
+                                        const int* ctx_lens, int B, int nh, int nkv, float scale, int window,
+                                        int cluster, cudaStream_t stream) {
+  const int merge_bytes = (4 * 16 * HD + 2 * 4 * 16) * (int)sizeof(float);
+  int smem = STAGES * 2 * Cfg<HD>::PAGE_ELEMS * 2;
+  if (merge_bytes > smem) smem = merge_bytes;
+  static int configured = 0;
+  if (configured < smem) {
+    cudaError_t e = cudaFuncSetAttribute(decode_cluster_kernel<HD, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = smem;
+  }
+  wpc::launch_clusters(decode_cluster_kernel<HD, STAGES>, dim3((unsigned)(B * nkv * cluster)), THREADS, smem, stream,
+                       (unsigned)cluster, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride,
+                       (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, page_table, table_width, ctx_lens,
+                       B, nh, nkv, scale * LOG2E, window, cluster);
+  return launch_status();
+}
+
+template <int HD>
+static int launch_decode_cluster(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+                                 const void* v_pages, const int* page_table, int table_width, const int* ctx_lens,
+                                 int B, int nh, int nkv, float scale, int window, int cluster, cudaStream_t stream) {
+  if (B * nkv * cluster <= 148 && DECODE_STAGES_ALONE * 2 * Cfg<HD>::PAGE_ELEMS * 2 <= 215 * 1024)
+    return launch_decode_cluster_stages<HD, DECODE_STAGES_ALONE>(q, q_stride, out, out_stride, k_pages, v_pages,
+                                                                 page_table, table_width, ctx_lens, B, nh, nkv, scale,
+                                                                 window, cluster, stream);
+  return launch_decode_cluster_stages<HD, DECODE_STAGES_SHARED>(q, q_stride, out, out_stride, k_pages, v_pages,
+                                                                page_table, table_width, ctx_lens, B, nh, nkv, scale,
+                                                                window, cluster, stream);
+}
+
+// How many clusters of `cluster` CTAs of the cluster decode kernel the device holds at once, by
+// the runtime's count for this device's GPCs (a cluster lives inside one GPC, and the number
+// of SMs that a GPC has differs from chip to chip); -1 on a CUDA error.
+template <int HD, int STAGES>
+static int decode_cluster_capacity(int cluster) {
+  const int smem = STAGES * 2 * Cfg<HD>::PAGE_ELEMS * 2;
+  cudaError_t e = cudaFuncSetAttribute(decode_cluster_kernel<HD, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) { cudaGetLastError(); return -1; }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(cluster * 148));
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)cluster;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  e = cudaOccupancyMaxActiveClusters(&n, decode_cluster_kernel<HD, STAGES>, &cfg);
+  if (e != cudaSuccess) { cudaGetLastError(); return -1; }
+  return n;
+}
+
 template <int HD>
 static int launch_prefill(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                           const void* v_pages, const int* page_table, int table_width, const int* cu_seqlens,
@@ -687,6 +913,30 @@ int wpc_attention_decode(const void* q, int q_stride, void* out, int out_stride,
   WPC_DISPATCH_HD(hd, fa::launch_decode<HD>(q, q_stride, out, out_stride, k_pages, v_pages, page_table, table_width,
                                            ctx_lens, B, nh, nkv, scale, window, n_ctas, part_o, part_ml, counters,
                                            stream));
+}
+
+// The same with a thread-block cluster of `cluster` CTAs (2..8) to each (sequence, kv head) pair,
+// which share the pair's pages and add up through one another's shared memory; for few pairs
+// of about equal lengths.  Needs (nh / nkv) * hd <= 1024 and at most 1024 CTAs.
+int wpc_attention_decode_cluster(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+                                 const void* v_pages, const int* page_table, int table_width, const int* ctx_lens,
+                                 int B, int nh, int nkv, int hd, float scale, int window, int cluster,
+                                 cudaStream_t stream) {
+  if (B <= 0) return 0;
+  if (!wpc_attention_mma_supports(nh, nkv, hd) || (q_stride % 2) || (out_stride % 2) ||
+      (nh / nkv) * hd > fa::CLUSTER_DECODE_MAX_OUT)
+    return WPC_ERR_UNSUPPORTED;
+  if (cluster < 2 || cluster > 8 || (long)B * nkv * cluster > 1024) return WPC_ERR_BAD_ARGUMENT;
+  WPC_DISPATCH_HD(hd, fa::launch_decode_cluster<HD>(q, q_stride, out, out_stride, k_pages, v_pages, page_table,
+                                                   table_width, ctx_lens, B, nh, nkv, scale, window, cluster, stream));
+}
+
+// Clusters of `cluster` CTAs of the cluster decode kernel that run at once: with the short ring
+// (two CTAs to an SM) or, `alone`, with the long one.
+int wpc_attention_decode_cluster_capacity(int hd, int cluster, int alone) {
+  if (cluster < 2 || cluster > 8) return 0;
+  if (alone) { WPC_DISPATCH_HD(hd, fa::decode_cluster_capacity<HD, fa::DECODE_STAGES_ALONE>(cluster)); }
+  WPC_DISPATCH_HD(hd, fa::decode_cluster_capacity<HD, fa::DECODE_STAGES_SHARED>(cluster));
 }
 
 int wpc_attention_prefill(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,

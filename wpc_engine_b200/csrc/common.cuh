@@ -69,6 +69,33 @@ __host__ __device__ __forceinline__ uint64_t mix64(uint64_t z) {
   return z ^ (z >> 31);
 }
 
+// ---- thread-block clusters: a barrier over all threads of all CTAs, and stores into a peer's shared memory ----
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// the address, in the cluster's shared window, of this CTA's shared address `addr` in CTA `rank`
+__device__ __forceinline__ uint32_t peer_smem(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+// (a peer may be written once it runs: after a cluster barrier at the start of the kernel)
+__device__ __forceinline__ void st_peer_f32(uint32_t addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+// The barrier in two halves: what a thread wrote before it arrived, peers see after their wait.
+__device__ __forceinline__ void cluster_arrive() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait() {
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 // ---- programmatic dependent launch ---------------------------------------------------------------
 // Every kernel of this library starts with pdl_trigger() and calls pdl_wait() before it touches
 // memory that an earlier kernel of the stream may have written.  Launched with the attribute

@@ -472,12 +472,13 @@ def attention(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, k_p
               v_pages: torch.Tensor, page_table: torch.Tensor, cu_seqlens: torch.Tensor, ctx_lens: torch.Tensor,
               seq_of_token: torch.Tensor, positions: torch.Tensor, scale: float, window: Optional[int],
               max_new_tokens: int, max_ctx_len: int, splits: Optional[int] = None,
-              mma_only: bool = False) -> torch.Tensor:
+              mma_only: bool = False, cluster: Optional[int] = None) -> torch.Tensor:
     """softmax(q . k * scale) . v over the cached positions that each query sees: 0..its own,
     or the last `window` of them.  q: the first n_heads*head_dim columns of each row.
 
     bfloat16 with a head size that is a multiple of 16 up to 128 runs on the tensor cores: the
-    split-KV kernel when every sequence brings one token (csrc/attention_mma.cu); otherwise the
+    split-KV kernel when every sequence brings one token (csrc/attention_mma.cu; `splits` forces
+    about that many CTAs to a pair, `cluster` a cluster of that size to a pair, 0 none); otherwise the
     tcgen05 kernel for head sizes 64 and 128 (csrc/attention_tc.cu) and the mma.sync kernel for
     the others (or with `mma_only`).  Everything else runs the plain kernel."""
     if q.dtype != torch.bfloat16 or not library().wpc_attention_mma_supports(n_heads, n_kv_heads, head_dim):
@@ -490,6 +491,14 @@ def attention(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, k_p
     out = torch.empty((T, n_heads * head_dim), dtype=q.dtype, device=q.device)
     if max_new_tokens == 1 and B <= 1024 and B * n_kv_heads <= _WORKSPACE_COUNTERS:
         _need(T == B, "one token per sequence expected")
+        if cluster is None:
+            cluster = 0 if splits else plan_decode_cluster(B, n_kv_heads, n_heads, head_dim, max_ctx_len, window)
+        if cluster:
+            _check("attention_decode_cluster", library().wpc_attention_decode_cluster(
+                _p(q), q.stride(0), _p(out), out.stride(0), _p(k_pages), _p(v_pages), _p(page_table),
+                page_table.shape[1], _p(ctx_lens), B, n_heads, n_kv_heads, head_dim, ctypes.c_float(scale),
+                int(window or 0), int(cluster), _stream()))
+            return out
         n_ctas = plan_decode_ctas(B, n_kv_heads, max_ctx_len, window, splits)
         slots = n_ctas + B * n_kv_heads
         part_o = torch.empty((slots * 16 * head_dim,), dtype=torch.float32, device=q.device)
@@ -516,7 +525,7 @@ def attention(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, k_p
 
 
 def plan_decode_ctas(n_seqs: int, n_kv_heads: int, max_ctx_len: int, window: Optional[int],
-                     per_pair: Optional[int] = None) -> int:
+                     per_pair: Optional[int] = None, with_estimate: bool = False):
     """How many CTAs share the pages of a decode step: two to an SM (an SM takes in only so
     many bytes a second, so all of them should stream), fewer when there are not even four
     pages of work for each.  `per_pair` forces about that many CTAs per (sequence, kv head)."""
@@ -527,6 +536,8 @@ def plan_decode_ctas(n_seqs: int, n_kv_heads: int, max_ctx_len: int, window: Opt
     if per_pair:
         return max(1, min(pairs * per_pair, 1024))
     if 3 * _SMS // 2 <= pairs <= 2 * _SMS:
+        if with_estimate:
+            return pairs, 2.0 + 1.5 * blocks
         # nearly two pairs to an SM: a CTA to a pair, so that equally long sequences need no
         # combining at all (64 sequences x 4 KV heads of 4,000 positions: 91 against 99 us);
         # with fewer pairs than that, fewer CTAs would stream too little (192 CTAs: 90 against 77 us)
@@ -534,14 +545,15 @@ def plan_decode_ctas(n_seqs: int, n_kv_heads: int, max_ctx_len: int, window: Opt
     # Otherwise the count with the least estimated time (microseconds, fitted to measurements at
     # the 7B shape: a page takes a CTA 1.05 us when it has an SM and a deep ring to itself, 1.5 us
     # when two share an SM and its bandwidth, which also costs about 2 us at the start; combining
-    # the parts of a pair costs about 3 + 0.12 per part).  When all sequences are about equally long, a share of pages that
+    # the parts of a pair costs about 7 + 0.12 per part: partial results to L2, a ticket, and the
+    # last CTA's pass over all parts, 1.1 + 5.0 us with 8 parts, behind the slowest CTA's pages).  When all sequences are about equally long, a share of pages that
     # divides a pair's pages keeps every CTA inside one pair; a CTA that straddles two pairs
     # fills its ring, merges and takes a ticket twice (about 8 us).  One sequence of 4,000
     # positions: 84 CTAs of 3 pages, 14 us, against 60 CTAs of 4 or 5 pages, 18 us.
     def estimate(n, per, aligned):
         page, start = (1.05, 0.0) if n <= _SMS else (1.5, 2.0)
         parts = -(-blocks // per)
-        return start + per * page + (3.0 + 0.12 * parts if parts > 1 else 0.0) + (0.0 if aligned else 8.0) + 0.002 * n
+        return start + per * page + (7.0 + 0.12 * parts if parts > 1 else 0.0) + (0.0 if aligned else 8.0) + 0.002 * n
 
     units = pairs * blocks
     target = max(1, min(2 * _SMS, pairs * max(blocks // 4, 1)))
@@ -553,7 +565,57 @@ def plan_decode_ctas(n_seqs: int, n_kv_heads: int, max_ctx_len: int, window: Opt
                 t = estimate(n, per, True)
                 if t < best_t:
                     best_n, best_t = n, t
+    if with_estimate:
+        return best_n, best_t
     return best_n
+
+
+# Decode attention with a thread-block cluster to each (sequence, kv head) pair (see
+# csrc/attention_mma.cu): on, and the sizes it takes.
+CLUSTER_DECODE = True
+CLUSTER_DECODE_MAX_OUT = 1024
+_decode_cluster_capacity: dict = {}
+
+
+def decode_cluster_capacity(head_dim: int, cluster: int, alone: bool) -> int:
+    """Clusters of `cluster` CTAs of the cluster decode kernel that this device runs at once
+    (a cluster lives inside one GPC, and chips differ in the SMs that their GPCs have)."""
+    key = (head_dim, cluster, alone)
+    if key not in _decode_cluster_capacity:
+        _decode_cluster_capacity[key] = max(0, int(library().wpc_attention_decode_cluster_capacity(
+            head_dim, cluster, int(alone))))
+    return _decode_cluster_capacity[key]
+
+
+def plan_decode_cluster(n_seqs: int, n_kv_heads: int, n_heads: int, head_dim: int, max_ctx_len: int,
+                        window: Optional[int]) -> int:
+    """The size of the clusters (2..8) if a decode step should run with a cluster to a pair, else
+    0.  The estimate is that of plan_decode_ctas, with 3.5 us for the exchange through shared
+    memory in place of tickets and combining (measured at the 7B shape, 8 sequences of 4,000
+    positions: clusters of 7 take 20.3 us, 256 CTAs with tickets 24.8).  Every pair gets the
+    same number of CTAs and all clusters must run at once, with a tenth of the device's
+    capacity to spare: clusters are placed while CTAs of the kernel before still hold their
+    SMs, and one that finds no room in any GPC waits for the others to end (32 clusters of 8
+    where 33 fit: 28 to 32 us in most launches, 18 us in the others)."""
+    pairs = max(n_seqs * n_kv_heads, 1)
+    if not CLUSTER_DECODE or (n_heads // n_kv_heads) * head_dim > CLUSTER_DECODE_MAX_OUT or pairs > _SMS:
+        return 0
+    blocks = (max_ctx_len + PAGE - 1) // PAGE
+    if window:
+        blocks = min(blocks, (window + PAGE - 1) // PAGE + 1)
+    best_c, best_t = 0, plan_decode_ctas(n_seqs, n_kv_heads, max_ctx_len, window, with_estimate=True)[1]
+    for c in range(2, 9):
+        n = pairs * c
+        if n > 2 * _SMS or c > blocks:
+            break
+        alone = n <= _SMS
+        if pairs * 1.1 > decode_cluster_capacity(head_dim, c, alone):
+            continue
+        page, start = (1.05, 0.0) if alone else (1.5, 2.0)
+        t = start + -(-blocks // c) * page + 3.5 + 0.002 * n
+        if t < best_t:
+            best_c, best_t = c, t
+    return best_c
 
 
 def attention_plain(q, n_heads, n_kv_heads, head_dim, k_pages, v_pages, page_table, seq_of_token, positions,
