@@ -1274,7 +1274,8 @@ int wpc_gemm_tc_workspace(int rows_a, int rows_b, int bn, int splits, size_t* sc
 // gated = 1: the weights hold gate and up rows interleaved in blocks of 64 features (64 gate
 // rows, then the 64 up rows of the same features); out is [tokens, features / 2] bfloat16 =
 // silu(gate) * up.  Needs no split and no bias, and bn >= 128 in the normal arrangement.
-// tall = 1 (normal arrangement, bn 256, no split): 256 x 256 tiles on one SM, see the kernel;
+// tall = 1 (no split; normal arrangement with bn 256, or swapped with bn 128): tiles of 256 rows
+// of a on one SM, see the kernel;
 // tall = 2: 256 x bn tiles on pairs of SMs (gemm_pair_kernel), bn 128..256 in steps of 16.
 // prefetch_weights = 1 promises that the weights are not written by earlier work still in
 // flight on the stream (model parameters): their first tiles are then fetched before the
@@ -1285,7 +1286,8 @@ int wpc_gemm_tc(const void* a, int lda, int rows_a, const void* b, int ldb, int 
                 int prefetch_weights, int tall, int cluster, cudaStream_t stream) {
   if (rows_a <= 0 || rows_b <= 0) return 0;
   if (cluster && (!swap || splits < 2 || splits > 8 || gated)) return WPC_ERR_UNSUPPORTED;
-  if (tall && (swap || splits > 1 || tall > 2 || (tall == 1 && bn != 256))) return WPC_ERR_UNSUPPORTED;
+  if (tall && swap && (tall != 1 || splits > 1 || cluster || bn != 128)) return WPC_ERR_UNSUPPORTED;
+  if (tall && !swap && (splits > 1 || tall > 2 || (tall == 1 && bn != 256))) return WPC_ERR_UNSUPPORTED;
   if (tall == 2 && (bn < 128 || bn > 256 || bn % 16 || (gated && bn % 128))) return WPC_ERR_UNSUPPORTED;
   if (K <= 0 || (lda % 8) || (ldb % 8) || (((uintptr_t)a) & 15) || (((uintptr_t)b) & 15)) return WPC_ERR_UNSUPPORTED;
   if (accumulate && out_dtype != WPC_DTYPE_F32) return WPC_ERR_BAD_ARGUMENT;
@@ -1325,6 +1327,8 @@ int wpc_gemm_tc(const void* a, int lda, int rows_a, const void* b, int ldb, int 
       case 128: return launch<128, false>(ma, mb, p, stream);
       case 256: return launch<256, false>(ma, mb, p, stream);
     }
+  } else if (tall) {
+    if (bn == 128) return launch<128, true, 2>(ma, mb, p, stream);
   } else if (cluster) {
     switch (bn) {
       case 16: return launch<16, true, 1, true>(ma, mb, p, stream);
