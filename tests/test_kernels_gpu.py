@@ -285,7 +285,7 @@ def test_attention_decode_splits(nh, nkv, hd, window, splits):
 
 @pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 16), (3, 1, 32), (4, 2, 48), (14, 2, 64), (28, 4, 128), (8, 1, 128), (2, 2, 80)])
 @pytest.mark.parametrize("window", [None, 100])
-@pytest.mark.parametrize("cluster", [2, 3, 8])
+@pytest.mark.parametrize("cluster", [2, 3, 8, 16])
 def test_attention_decode_clusters(nh, nkv, hd, window, cluster):
     """A cluster of CTAs to each (sequence, kv head) pair: ranks without pages (a sequence of one
     page among eight ranks), shares that do not divide, every length at once."""

@@ -469,13 +469,15 @@ decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* 
 
 // ---- decode, a cluster to a pair ------------------------------------------------------------------
 // When the (sequence, kv head) pairs are few and about equally long, the CTAs of a pair form a
-// thread-block cluster of C ranks; rank r takes the r-th share of the pages that the pair's
+// thread-block cluster of C ranks (up to 16); rank r takes the r-th share of the pages that the pair's
 // query sees.  The partial results do not go through global memory: every rank writes its
 // unnormalised outputs for the r'-th share of the pair's n_rep * HD output elements straight
 // into rank r''s shared memory, and its running maxima and sums into every rank's; one
 // cluster barrier makes them visible, and every rank then normalises and writes its share of
 // the output, adding the ranks in order.  No scratch, no tickets, no second pass.
 constexpr int CLUSTER_DECODE_MAX_OUT = 1024;      // n_rep * HD that the receive buffer takes
+constexpr int CLUSTER_DECODE_MAX_RANKS = 16;      // beyond 8 a cluster needs the kernel's consent (see the launch)
+constexpr int CLUSTER_SEGMENT_PAGES = 256;        // page numbers of a rank's share kept in shared memory
 
 template <int HD, int DECODE_STAGES>
 __global__ void __launch_bounds__(THREADS)
@@ -487,9 +489,9 @@ decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bf
   extern __shared__ __align__(16) uint8_t smem_raw[];
   __nv_bfloat16* ks = (__nv_bfloat16*)smem_raw;                       // [DECODE_STAGES][PAGE][STRIDE]
   __nv_bfloat16* vs = ks + DECODE_STAGES * Cfg<HD>::PAGE_ELEMS;
-  __shared__ int s_pages[MAX_SEGMENT_PAGES];                          // page numbers of this rank's share
-  __shared__ float s_recv_o[CLUSTER_DECODE_MAX_OUT + 8];              // [rank][element of this rank's share]
-  __shared__ float s_recv_ml[8 * 16 * 2];                             // [rank][row][maximum, sum]
+  __shared__ int s_pages[CLUSTER_SEGMENT_PAGES];                      // page numbers of this rank's share
+  __shared__ float s_recv_o[CLUSTER_DECODE_MAX_OUT + CLUSTER_DECODE_MAX_RANKS];   // [rank][element of this rank's share]
+  __shared__ float s_recv_ml[CLUSTER_DECODE_MAX_RANKS * 16 * 2];      // [rank][row][maximum, sum]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_rep = nh / nkv;
   const size_t page_elems = (size_t)nkv * PAGE * HD;
@@ -505,12 +507,12 @@ decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bf
   const int blk0 = lo / PAGE + rank * base + min(rank, extra), blk1 = blk0 + base + (rank < extra ? 1 : 0);
   const int* gtable = page_table + (size_t)b * table_width + blk0;
   const int n_seg = blk1 - blk0;
-  for (int i = tid; i < min(n_seg, MAX_SEGMENT_PAGES); i += THREADS) s_pages[i] = gtable[i];
+  for (int i = tid; i < min(n_seg, CLUSTER_SEGMENT_PAGES); i += THREADS) s_pages[i] = gtable[i];
   // Up to here only the step's lengths and page numbers were read, which the host wrote before
   // the step's first kernel started.  Queries, keys and values come from the kernel ahead.
   pdl_wait();
   __syncthreads();
-  auto page_of = [&](int blk) { const int i = blk - blk0; return i < MAX_SEGMENT_PAGES ? s_pages[i] : gtable[i]; };
+  auto page_of = [&](int blk) { const int i = blk - blk0; return i < CLUSTER_SEGMENT_PAGES ? s_pages[i] : gtable[i]; };
 
 #pragma unroll
   for (int i = 0; i < DECODE_STAGES - 1; ++i) {
@@ -804,6 +806,8 @@ static int launch_decode_cluster_stages(const void* q, int q_stride, void* out, 
   static int configured = 0;
   if (configured < smem) {
     cudaError_t e = cudaFuncSetAttribute(decode_cluster_kernel<HD, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e == cudaSuccess)      // clusters of more than 8 CTAs
+      e = cudaFuncSetAttribute(decode_cluster_kernel<HD, STAGES>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
     if (e != cudaSuccess) return (int)e;
     configured = smem;
   }
@@ -834,6 +838,8 @@ template <int HD, int STAGES>
 static int decode_cluster_capacity(int cluster) {
   const int smem = STAGES * 2 * Cfg<HD>::PAGE_ELEMS * 2;
   cudaError_t e = cudaFuncSetAttribute(decode_cluster_kernel<HD, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(decode_cluster_kernel<HD, STAGES>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
   if (e != cudaSuccess) { cudaGetLastError(); return -1; }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(cluster * 148));
@@ -915,7 +921,7 @@ int wpc_attention_decode(const void* q, int q_stride, void* out, int out_stride,
                                            stream));
 }
 
-// The same with a thread-block cluster of `cluster` CTAs (2..8) to each (sequence, kv head) pair,
+// The same with a thread-block cluster of `cluster` CTAs (2..16) to each (sequence, kv head) pair,
 // which share the pair's pages and add up through one another's shared memory; for few pairs
 // of about equal lengths.  Needs (nh / nkv) * hd <= 1024 and at most 1024 CTAs.
 int wpc_attention_decode_cluster(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
@@ -926,7 +932,7 @@ int wpc_attention_decode_cluster(const void* q, int q_stride, void* out, int out
   if (!wpc_attention_mma_supports(nh, nkv, hd) || (q_stride % 2) || (out_stride % 2) ||
       (nh / nkv) * hd > fa::CLUSTER_DECODE_MAX_OUT)
     return WPC_ERR_UNSUPPORTED;
-  if (cluster < 2 || cluster > 8 || (long)B * nkv * cluster > 1024) return WPC_ERR_BAD_ARGUMENT;
+  if (cluster < 2 || cluster > fa::CLUSTER_DECODE_MAX_RANKS || (long)B * nkv * cluster > 1024) return WPC_ERR_BAD_ARGUMENT;
   WPC_DISPATCH_HD(hd, fa::launch_decode_cluster<HD>(q, q_stride, out, out_stride, k_pages, v_pages, page_table,
                                                    table_width, ctx_lens, B, nh, nkv, scale, window, cluster, stream));
 }
@@ -934,7 +940,7 @@ int wpc_attention_decode_cluster(const void* q, int q_stride, void* out, int out
 // Clusters of `cluster` CTAs of the cluster decode kernel that run at once: with the short ring
 // (two CTAs to an SM) or, `alone`, with the long one.
 int wpc_attention_decode_cluster_capacity(int hd, int cluster, int alone) {
-  if (cluster < 2 || cluster > 8) return 0;
+  if (cluster < 2 || cluster > fa::CLUSTER_DECODE_MAX_RANKS) return 0;
   if (alone) { WPC_DISPATCH_HD(hd, fa::decode_cluster_capacity<HD, fa::DECODE_STAGES_ALONE>(cluster)); }
   WPC_DISPATCH_HD(hd, fa::decode_cluster_capacity<HD, fa::DECODE_STAGES_SHARED>(cluster));
 }

@@ -594,7 +594,7 @@ def decode_cluster_capacity(head_dim: int, cluster: int, alone: bool) -> int:
 
 def plan_decode_cluster(n_seqs: int, n_kv_heads: int, n_heads: int, head_dim: int, max_ctx_len: int,
                         window: Optional[int]) -> int:
-    """The size of the clusters (2..8) if a decode step should run with a cluster to a pair, else
+    """The size of the clusters (2..16) if a decode step should run with a cluster to a pair, else
     0.  The estimate is that of plan_decode_ctas, with 3.5 us for the exchange through shared
     memory in place of tickets and combining (measured at the 7B shape, 8 sequences of 4,000
     positions: clusters of 7 take 20.3 us, 256 CTAs with tickets 24.8).  Every pair gets the
@@ -609,7 +609,7 @@ def plan_decode_cluster(n_seqs: int, n_kv_heads: int, n_heads: int, head_dim: in
     if window:
         blocks = min(blocks, (window + PAGE - 1) // PAGE + 1)
     best_c, best_t = 0, plan_decode_ctas(n_seqs, n_kv_heads, max_ctx_len, window, with_estimate=True)[1]
-    for c in range(2, 9):
+    for c in range(2, 17):
         n = pairs * c
         if n > 2 * _SMS or c > blocks:
             break
