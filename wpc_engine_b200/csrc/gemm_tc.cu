@@ -21,10 +21,10 @@
 //            full when there are only a few tokens (decode), so the weights stream once at
 //            full width.
 // Split K, three ways.  (1) Swapped arrangement, the usual one for few tokens: the CTAs of a
-// tile form a thread-block cluster (2..8); each puts its partial sums into its shared memory,
-// and after a cluster barrier each adds up, in rank order, a share of the tile's token rows
-// from all peers through distributed shared memory and writes it.  No scratch, no atomics,
-// the same bits every run.  The ring is kept so short that two CTAs fit on an SM.  (2) With
+// tile form a thread-block cluster (2..8); every rank writes its partial sums of a token row
+// into the shared memory of the rank that owns the row (distributed shared memory), and after
+// one cluster barrier each rank adds up its rows in rank order and writes them.  No scratch, no
+// atomics, the same bits every run.  The ring is kept so short that two CTAs fit on an SM.  (2) With
 // tickets: every CTA of a tile writes its partial sums to scratch memory and takes a ticket;
 // the CTA that draws the last ticket adds them in slice order and runs the epilogue.  Nobody
 // waits for anybody.  (3) When the product is added to a float32 output anyway, the slices
@@ -33,7 +33,8 @@
 // Every wait on an mbarrier is bounded: when it runs out the kernel records
 // WPC_ERR_DEVICE_WAIT in `status`, lets its copies land, frees its tensor memory and returns.
 // The cluster barriers are hardware barriers that every thread of every CTA reaches on every
-// path (they stand after the roles join), so a CTA that gave up still arrives.
+// path (each role arrives when its loop ends, however it ended), so a CTA that gave up still
+// arrives.
 //
 // The math is the reference's y = W x + b (wpc-runtime/src/weights.rs:59-78) in bfloat16
 // inputs with float32 accumulation.
