@@ -41,6 +41,7 @@
 #include <cuda.h>
 
 #include <mutex>
+#include <type_traits>
 #include <unordered_map>
 
 #include "api.h"
@@ -498,26 +499,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const float* recv = red_stage + r;                  // [rank][row of this CTA][128] received sums
       float* xbuf = red_stage + S * kmax * BM;            // [4][128]
       const uint32_t mine = smem_u32(red_stage) + (uint32_t)((my * kmax) * BM + r) * 4;
-      // Token rows my, my + S, ... are this CTA's, four of them at a time.  What a round needs
-      // from global memory is fetched a round ahead: for the first round, before the MMAs end.
-      float bias = 0.f, cs[4], sn[4], old[4];
+      // Token rows my, my + S, ... are this CTA's, ROWS of them at a time: four where q and k are
+      // rotated, eight otherwise (64 tokens on 8 ranks are then one round; a round more costs
+      // about 2 us, most of it the trip to L2 for what it adds to).  What a round needs from
+      // global memory is fetched a round ahead: for the first round, before the MMAs end.
+      float bias = 0.f, cs[4], sn[4], old[8];
       __nv_bfloat16* dst[4];
-      auto fetch = [&](int j0) {
+      auto fetch = [&](auto rows_c, int j0) {
+        constexpr int ROWS = decltype(rows_c)::value;
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < ROWS; ++u) {
           const int j = j0 + u * S;
-          cs[u] = 1.f; sn[u] = 0.f; old[u] = 0.f; dst[u] = nullptr;
+          old[u] = 0.f;
+          if (ROWS == 4) { cs[u & 3] = 1.f; sn[u & 3] = 0.f; dst[u & 3] = nullptr; }
           if (in_range && j < n_valid) {
             const int tok = n0 + j;
-            if (rotated) {
+            if (ROWS == 4 && rotated) {
               // past L1: the dry pass may have read these before the kernel that writes them ended
-              cs[u] = __ldcg(p.rope_cos + (size_t)tok * p.rope_R + pr);
-              sn[u] = __ldcg(p.rope_sin + (size_t)tok * p.rope_R + pr);
+              cs[u & 3] = __ldcg(p.rope_cos + (size_t)tok * p.rope_R + pr);
+              sn[u & 3] = __ldcg(p.rope_sin + (size_t)tok * p.rope_R + pr);
             }
-            if (hd && kind > 0) {
+            if (ROWS == 4 && hd && kind > 0) {
               const long long base = s_rowbase[(j - my) / S];      // page * nkv * PAGE + place in the page
               if (base >= 0)
-                dst[u] = (kind == 1 ? p.k_pages : p.v_pages) + ((size_t)base + (size_t)kvh * WPC_PAGE) * hd + d;
+                dst[u & 3] = (kind == 1 ? p.k_pages : p.v_pages) + ((size_t)base + (size_t)kvh * WPC_PAGE) * hd + d;
               else if (p.status) atomicExch(p.status, WPC_ERR_BAD_ARGUMENT);
             } else if (!hd && p.accumulate) {
               old[u] = __ldcg((const float*)p.out + (size_t)tok * p.ldc + feat);   // only this thread writes it
@@ -525,13 +530,57 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           }
         }
       };
+      // the rounds of the tail: sums of the received slices in rank order, rotation, store
+      auto rounds = [&](auto rows_c, bool dry) {
+        constexpr int ROWS = decltype(rows_c)::value;
+        for (int j0 = my; j0 < n_valid; j0 += ROWS * S) {
+          float val[ROWS];
+#pragma unroll
+          for (int u = 0; u < ROWS; ++u) {
+            const int j = j0 + u * S;
+            float sum = 0.f;
+            if (j < n_valid) {
+              const float* row = recv + ((j - my) / S) * BM;
+              sum = row[0];
+              for (int s2 = 1; s2 < S; ++s2) sum += row[s2 * kmax * BM];     // in rank order
+            }
+            val[u] = sum + bias;
+          }
+          if (ROWS == 4 && hd) {
+            // x'_i = x_i c - x_{i+half} s;  x'_{i+half} = x_{i+half} c + x_i s  (rope.rs:36-39)
+#pragma unroll
+            for (int u = 0; u < ROWS; ++u) xbuf[(u & 3) * BM + r] = val[u];
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+#pragma unroll
+            for (int u = 0; u < ROWS; ++u) {
+              const float other = xbuf[(u & 3) * BM + (r ^ half)];
+              if (rotated) val[u] = d < half ? val[u] * cs[u & 3] - other * sn[u & 3] : val[u] * cs[u & 3] + other * sn[u & 3];
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");     // the buffer is written again in the next round
+          }
+#pragma unroll
+          for (int u = 0; u < ROWS; ++u) {
+            const int j = j0 + u * S;
+            if (j < n_valid && in_range && !dry) {
+              const size_t o = (size_t)(n0 + j) * p.ldc + feat;
+              if (ROWS == 4 && hd && kind > 0) { if (dst[u & 3]) *dst[u & 3] = __float2bfloat16_rn(val[u]); }
+              else if (p.accumulate) ((float*)p.out)[o] = old[u] + val[u];
+              else if (p.out_bf16) ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(val[u]);
+              else ((float*)p.out)[o] = val[u];
+            }
+          }
+          if (j0 + ROWS * S < n_valid) fetch(rows_c, j0 + ROWS * S);
+        }
+      };
+      const std::integral_constant<int, 4> four;
+      const std::integral_constant<int, 8> eight;
       const int passes = p.k_blocks > 0 ? 2 : 1;          // always 2; the compiler must keep one copy of the body
 #pragma unroll 1
       for (int pass = 0; pass < passes; ++pass) {
         const bool dry = pass + 1 < passes;               // the pass that only brings the code in
         if (!dry) pdl_wait();                             // the output and the inputs of fetch() are shared
         if (in_range && p.bias) bias = p.bias[feat];
-        fetch(my);
+        if (hd) fetch(four, my); else fetch(eight, my);
         bool ok = true;
         if (!dry) {
           ok = mbar_wait(accum_full, 0);
@@ -561,44 +610,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           cluster_arrive();                               // this rank's sums are on their way
           cluster_wait();                                 // every rank's sums for this CTA's rows have arrived
         }
-        for (int j0 = my; j0 < n_valid; j0 += 4 * S) {
-          float val[4];
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const int j = j0 + u * S;
-            float sum = 0.f;
-            if (j < n_valid) {
-              const float* row = recv + ((j - my) / S) * BM;
-              sum = row[0];
-              for (int s2 = 1; s2 < S; ++s2) sum += row[s2 * kmax * BM];     // in rank order
-            }
-            val[u] = sum + bias;
-          }
-          if (hd) {
-            // x'_i = x_i c - x_{i+half} s;  x'_{i+half} = x_{i+half} c + x_i s  (rope.rs:36-39)
-#pragma unroll
-            for (int u = 0; u < 4; ++u) xbuf[u * BM + r] = val[u];
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              const float other = xbuf[u * BM + (r ^ half)];
-              if (rotated) val[u] = d < half ? val[u] * cs[u] - other * sn[u] : val[u] * cs[u] + other * sn[u];
-            }
-            asm volatile("bar.sync 1, 128;" ::: "memory");     // the buffer is written again in the next round
-          }
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const int j = j0 + u * S;
-            if (j < n_valid && in_range && !dry) {
-              const size_t o = (size_t)(n0 + j) * p.ldc + feat;
-              if (hd && kind > 0) { if (dst[u]) *dst[u] = __float2bfloat16_rn(val[u]); }
-              else if (p.accumulate) ((float*)p.out)[o] = old[u] + val[u];
-              else if (p.out_bf16) ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(val[u]);
-              else ((float*)p.out)[o] = val[u];
-            }
-          }
-          if (j0 + 4 * S < n_valid) fetch(j0 + 4 * S);
-        }
+        if (hd) rounds(four, dry); else rounds(eight, dry);
       }
       // Nothing reads a peer's shared memory: the CTA may leave when its own rows are written.
     } else {
