@@ -224,9 +224,11 @@ struct Smem {
     return s > MAX_STAGES ? MAX_STAGES : (s < 2 ? 2 : s);
   }
   // Cluster variant: behind the ring, the partial sums that the ranks of the cluster send to this
-  // CTA, [rank][row of this CTA][128] floats (at most BN + 7 rows in all), and the [4][128]
-  // floats through which the two halves of a head exchange their values.
-  static constexpr int RECV_BYTES = (BN + 7 + 4) * BM * 4;
+  // CTA, [rank][feature][row of this CTA] floats, and the [4][128] floats through which the two
+  // halves of a head exchange their values.  Token rows belong to the ranks in groups of four
+  // (see the kernel), so a CTA has room for 4 * ceil(ceil(BN / 4) / ranks) rows from each rank.
+  __host__ __device__ static constexpr int recv_rows(int ranks) { return 4 * (((BN + 3) / 4 + ranks - 1) / ranks); }
+  __host__ __device__ static constexpr int recv_bytes(int ranks) { return (ranks * recv_rows(ranks) + 4) * BM * 4; }
 };
 
 __device__ __forceinline__ void store_row32(const Params& p, int row, int col0, int n_cols, const float (&v)[32]) {
@@ -327,11 +329,12 @@ struct WorkIter {
 // MT = 2: the tile is 256 rows of A by BN; the two 128-row halves are two MMAs that share the B
 // tile in shared memory (a third less operand traffic per flop) and fill both accumulators, so
 // the epilogue does not overlap the next tile.
-// CL (swapped arrangement, split K): the CTAs that share a tile form a thread-block cluster.  Token
-// row j of the tile belongs to rank j % S: every rank writes its partial sums of that row
-// straight into the owner's shared memory (writes to a peer need no answer), one cluster barrier
-// makes them visible, and the owner adds them up in rank order and writes the row.  No scratch,
-// no tickets, no atomics.  The epilogue warps run this whole path once before the dependency
+// CL (swapped arrangement, split K): the CTAs that share a tile form a thread-block cluster.  The
+// token rows of the tile belong to the ranks in groups of four (group i to rank i % S): every
+// rank writes its partial sums of a group straight into the owner's shared memory, 16 bytes a
+// thread (writes to a peer need no answer, but each is a packet between two SMs: one float at a
+// time, 64 tokens took 7 to 17 us), one cluster barrier makes them visible, and the owner adds
+// them up in rank order and writes the rows.  No scratch, no tickets, no atomics.  The epilogue warps run this whole path once before the dependency
 // wait, with every store switched off: a kernel runs each of its instructions once, so on the
 // first pass every line of code comes from L2 or beyond, and a dry pass while the warps
 // have nothing to do takes those misses off the critical path.
@@ -462,7 +465,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int r = q * 32 + lane;                        // row of the tile = TMEM lane
     const int et = threadIdx.x - 64;                    // 0..127 among the epilogue threads
     if (CL && p.rope_hd && p.splits > 1) {
-      // where in the cache the token rows that this CTA will write go (rows rank, rank + S, ...):
+      // where in the cache the token rows that this CTA will write go:
       // three dependent loads a row, done here so that they are over when the tail needs them.
       // Positions and page numbers are the step's inputs, written by the host before its first
       // kernel started: they may be read ahead of the dependency wait.
@@ -470,8 +473,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const int tiles_m = (p.M + BM - 1) / BM;
       const int n0 = (blockIdx.x / S / tiles_m) * BN;
       const int n_valid = min(BN, p.N - n0);
-      for (int k = et; my + k * S < n_valid; k += 128) {
-        const int tok = n0 + my + k * S;
+      for (int k = et; k < S::recv_rows(S); k += 128) {       // row k of this CTA: group k / 4 of its groups
+        const int j = ((k >> 2) * S + my) * 4 + (k & 3);
+        if (j >= n_valid) continue;
+        const int tok = n0 + j;
         const int pos = p.positions[tok], block = pos / WPC_PAGE;
         const int page = block < p.table_width ? p.page_table[(size_t)p.seq_of_token[tok] * p.table_width + block] : -1;
         s_rowbase[k] = (page >= 0 && page < p.n_pages) ? ((long long)page * p.rope_nkv * WPC_PAGE + pos % WPC_PAGE) : -1;
@@ -480,7 +485,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (CL && p.splits > 1) {
       // ---- cluster variant: one unit of work; see the comment above the kernel ----
       asm volatile("bar.sync 1, 128;" ::: "memory");     // s_rowbase is complete
-      const int S = p.splits, my = (int)cluster_rank(), kmax = (BN + S - 1) / S;
+      const int S = p.splits, my = (int)cluster_rank(), kmax = S::recv_rows(S);
       WorkIter<BN, MT> work(p, true);
       Work w;
       work.next(w);
@@ -496,20 +501,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const int kvh = hd ? (kind == 1 ? (feat - nq) / hd : (kind == 2 ? (feat - nq - nk) / hd : 0)) : 0;
       const int pr = hd ? d % half : 0;                   // index of the pair within the head
       const bool rotated = hd && kind < 2 && pr < p.rope_R;
-      const float* recv = red_stage + r;                  // [rank][row of this CTA][128] received sums
+      const float* recv = red_stage + r * kmax;           // [rank][feature][row of this CTA] received sums
       float* xbuf = red_stage + S * kmax * BM;            // [4][128]
-      const uint32_t mine = smem_u32(red_stage) + (uint32_t)((my * kmax) * BM + r) * 4;
-      // Token rows my, my + S, ... are this CTA's, ROWS of them at a time: four where q and k are
-      // rotated, eight otherwise (64 tokens on 8 ranks are then one round; a round more costs
-      // about 2 us, most of it the trip to L2 for what it adds to).  What a round needs from
+      const uint32_t mine = smem_u32(red_stage) + (uint32_t)((my * BM + r) * kmax) * 4;
+      // This CTA's groups of four token rows are my, my + S, ...; a round takes ROWS rows: a group
+      // where q and k are rotated, two otherwise (64 tokens on 8 ranks are then one round; a round
+      // more costs about 2 us, most of it the trip to L2 for what it adds to).  What a round needs from
       // global memory is fetched a round ahead: for the first round, before the MMAs end.
       float bias = 0.f, cs[4], sn[4], old[8];
       __nv_bfloat16* dst[4];
-      auto fetch = [&](auto rows_c, int j0) {
+      auto fetch = [&](auto rows_c, int k0) {
         constexpr int ROWS = decltype(rows_c)::value;
 #pragma unroll
         for (int u = 0; u < ROWS; ++u) {
-          const int j = j0 + u * S;
+          const int k = k0 + u, j = ((k >> 2) * S + my) * 4 + (k & 3);      // row k of this CTA is token j of the tile
           old[u] = 0.f;
           if (ROWS == 4) { cs[u & 3] = 1.f; sn[u & 3] = 0.f; dst[u & 3] = nullptr; }
           if (in_range && j < n_valid) {
@@ -520,7 +525,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               sn[u & 3] = __ldcg(p.rope_sin + (size_t)tok * p.rope_R + pr);
             }
             if (ROWS == 4 && hd && kind > 0) {
-              const long long base = s_rowbase[(j - my) / S];      // page * nkv * PAGE + place in the page
+              const long long base = s_rowbase[k];                 // page * nkv * PAGE + place in the page
               if (base >= 0)
                 dst[u & 3] = (kind == 1 ? p.k_pages : p.v_pages) + ((size_t)base + (size_t)kvh * WPC_PAGE) * hd + d;
               else if (p.status) atomicExch(p.status, WPC_ERR_BAD_ARGUMENT);
@@ -533,18 +538,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       // the rounds of the tail: sums of the received slices in rank order, rotation, store
       auto rounds = [&](auto rows_c, bool dry) {
         constexpr int ROWS = decltype(rows_c)::value;
-        for (int j0 = my; j0 < n_valid; j0 += ROWS * S) {
+        for (int k0 = 0; ((k0 >> 2) * S + my) * 4 < n_valid; k0 += ROWS) {
           float val[ROWS];
 #pragma unroll
-          for (int u = 0; u < ROWS; ++u) {
-            const int j = j0 + u * S;
-            float sum = 0.f;
-            if (j < n_valid) {
-              const float* row = recv + ((j - my) / S) * BM;
-              sum = row[0];
-              for (int s2 = 1; s2 < S; ++s2) sum += row[s2 * kmax * BM];     // in rank order
+          for (int g4 = 0; g4 < ROWS; g4 += 4) {
+            float4 sum = *(const float4*)(recv + k0 + g4);
+            for (int s2 = 1; s2 < S; ++s2) {                                   // in rank order
+              const float4 t = *(const float4*)(recv + s2 * kmax * BM + k0 + g4);
+              sum.x += t.x; sum.y += t.y; sum.z += t.z; sum.w += t.w;
             }
-            val[u] = sum + bias;
+            val[g4] = sum.x + bias; val[g4 + 1] = sum.y + bias; val[g4 + 2] = sum.z + bias; val[g4 + 3] = sum.w + bias;
           }
           if (ROWS == 4 && hd) {
             // x'_i = x_i c - x_{i+half} s;  x'_{i+half} = x_{i+half} c + x_i s  (rope.rs:36-39)
@@ -560,7 +563,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           }
 #pragma unroll
           for (int u = 0; u < ROWS; ++u) {
-            const int j = j0 + u * S;
+            const int k = k0 + u, j = ((k >> 2) * S + my) * 4 + (k & 3);
             if (j < n_valid && in_range && !dry) {
               const size_t o = (size_t)(n0 + j) * p.ldc + feat;
               if (ROWS == 4 && hd && kind > 0) { if (dst[u & 3]) *dst[u & 3] = __float2bfloat16_rn(val[u]); }
@@ -569,7 +572,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               else ((float*)p.out)[o] = val[u];
             }
           }
-          if (j0 + ROWS * S < n_valid) fetch(rows_c, j0 + ROWS * S);
+          if ((((k0 + ROWS) >> 2) * S + my) * 4 < n_valid) fetch(rows_c, k0 + ROWS);
         }
       };
       const std::integral_constant<int, 4> four;
@@ -580,7 +583,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const bool dry = pass + 1 < passes;               // the pass that only brings the code in
         if (!dry) pdl_wait();                             // the output and the inputs of fetch() are shared
         if (in_range && p.bias) bias = p.bias[feat];
-        if (hd) fetch(four, my); else fetch(eight, my);
+        if (hd) fetch(four, 0); else fetch(eight, 0);
         bool ok = true;
         if (!dry) {
           ok = mbar_wait(accum_full, 0);
@@ -595,13 +598,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           uint32_t v[32];
           if (BN >= 32) tmem_ld32(lane_addr + c, v); else tmem_ld16(lane_addr + c, v);
           tmem_ld_wait();
-          const int nc = min(32, n_valid - c);
-          int owner = c % S, k = c / S;
+          int owner = (c >> 2) % S, lg = (c >> 2) / S;        // the group of columns c .. c + 3: whose, and which of theirs
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            if (j < nc && !dry)
-              st_peer_f32(peer_smem(mine + (uint32_t)k * (BM * 4), (uint32_t)owner), have_acc ? __uint_as_float(v[j]) : 0.f);
-            if (++owner == S) { owner = 0; ++k; }
+          for (int j = 0; j < (BN >= 32 ? 32 : 16); j += 4) {
+            if (c + j < n_valid && !dry) {
+              const uint32_t at = peer_smem(mine + (uint32_t)lg * 16, (uint32_t)owner);
+              if (have_acc)
+                st_peer_f32x4(at, __uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+              else
+                st_peer_f32x4(at, 0.f, 0.f, 0.f, 0.f);
+            }
+            if (++owner == S) { owner = 0; ++lg; }
           }
         }
         if (!dry) {
@@ -1204,13 +1211,14 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, Params& p, cudaS
     if (p.splits < 2 || p.splits > 8) return WPC_ERR_UNSUPPORTED;
     // a ring so short that two CTAs fit on an SM: more clusters then run side by side (the
     // clusters of a GPC's SMs leave fewer SMs idle), and all of them must stream at once
-    int stages = S::max_stages(BN <= 64 ? 2 : 1, S::RECV_BYTES);
+    const int recv_bytes = S::recv_bytes(p.splits);
+    int stages = S::max_stages(BN <= 64 ? 2 : 1, recv_bytes);
     const int kb_per = (p.k_blocks + p.splits - 1) / p.splits;
     if (stages > kb_per) stages = kb_per < 2 ? 2 : kb_per;
     if (stages > g_stage_limit) stages = g_stage_limit < 2 ? 2 : g_stage_limit;
     p.stages = stages;
-    // behind the ring: the sums that the other ranks send (see Smem::RECV_BYTES)
-    wpc::launch_clusters(gemm_tc_kernel<BN, SWAP, MT, CL>, dim3((unsigned)units), THREADS, S::total(stages) + S::RECV_BYTES,
+    // behind the ring: the sums that the other ranks send (see Smem::recv_bytes)
+    wpc::launch_clusters(gemm_tc_kernel<BN, SWAP, MT, CL>, dim3((unsigned)units), THREADS, S::total(stages) + recv_bytes,
                          stream, (unsigned)p.splits, ma, mb, p);
     return launch_status();
   }
@@ -1442,7 +1450,7 @@ int wpc_gemm_tc_cluster_capacity(int bn, int splits) {
 #define WPC_CAP(BN_)                                                                                              \
   {                                                                                                               \
     using S = Smem<BN_, 1>;                                                                                       \
-    cfg.dynamicSmemBytes = S::total(S::max_stages(BN_ <= 64 ? 2 : 1, S::RECV_BYTES)) + S::RECV_BYTES;             \
+    cfg.dynamicSmemBytes = S::total(S::max_stages(BN_ <= 64 ? 2 : 1, S::recv_bytes(splits))) + S::recv_bytes(splits); \
     e = cudaFuncSetAttribute(gemm_tc_kernel<BN_, true, 1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,     \
                              S::total(S::max_stages(1)));                                                         \
     if (e == cudaSuccess) e = cudaOccupancyMaxActiveClusters(&n, gemm_tc_kernel<BN_, true, 1, true>, &cfg);       \
