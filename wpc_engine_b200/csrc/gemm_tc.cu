@@ -727,8 +727,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         } else {
           // rows of the tile: 64 gate features, then the 64 up rows of the same features; the
           // upper half hands its values to the lower half through shared memory (the operand
-          // stages are free: every MMA has finished)
-          float* xch = (float*)tiles;                          // [BN][64]
+          // stages are free: every MMA has finished).  The lower half works on all columns of a
+          // chunk at once, whether they hold tokens or not: a test per column would turn the
+          // chains of exp and division into branches that run one after the other (stamps of
+          // clock64 gave 85 ns a token, 2.6 us for 32 tokens).  The results of a chunk then pass
+          // through shared memory once more, so that a thread stores 16 bytes of a token's row
+          // (a store of one bfloat16 per thread and token took 50 ns each, 1.7 us for 32 tokens).
+          float* xch = (float*)tiles;                                          // [BN][64]
+          __nv_bfloat16* xo = (__nv_bfloat16*)(tiles + BN * 64 * 4);           // [32][64] a chunk's results
+          const bool wide = (p.ldc & 7) == 0 && (((uintptr_t)p.out) & 15) == 0;
+          constexpr int W = BN >= 32 ? 32 : 16;
           for (int c = 0; c < n_valid; c += 32) {
             uint32_t u32[32];
             if (have_acc) {
@@ -738,21 +746,36 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const int nc = min(32, n_valid - c);
             if (r >= 64) {
 #pragma unroll
-              for (int j = 0; j < 32; ++j)
+              for (int j = 0; j < W; ++j)
                 if (j < nc) xch[(c + j) * 64 + (r - 64)] = have_acc ? __uint_as_float(u32[j]) : 0.f;
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");
             if (r < 64) {
               const int feat = (m0 >> 1) + r;
-              if (feat < (p.M >> 1)) {
+              float res[W];
 #pragma unroll
-                for (int j = 0; j < 32; ++j)
-                  if (j < nc) {
-                    const float g = have_acc ? __uint_as_float(u32[j]) : 0.f;
-                    const float u = xch[(c + j) * 64 + r];
-                    ((__nv_bfloat16*)p.out)[(size_t)(n0 + c + j) * p.ldc + feat] =
-                        __float2bfloat16_rn(g / (1.0f + expf(-g)) * u);
-                  }
+              for (int j = 0; j < W; ++j) res[j] = xch[(c + j) * 64 + r];
+#pragma unroll
+              for (int j = 0; j < W; ++j) {
+                const float g = have_acc ? __uint_as_float(u32[j]) : 0.f;
+                // the quotient to 2 units in the last place of float32, far inside the bfloat16 that
+                // it becomes (the exact division has a slow path, a branch again)
+                res[j] *= __fdividef(g, 1.0f + expf(-g));
+              }
+              if (wide) {
+#pragma unroll
+                for (int j = 0; j < W; ++j) xo[j * 64 + r] = __float2bfloat16_rn(res[j]);
+                asm volatile("bar.sync 2, 64;" ::: "memory");                 // the two warps of the lower half
+                for (int piece = r; piece < nc * 8; piece += 64) {
+                  const int token = piece >> 3, part = piece & 7;
+                  *(uint4*)((__nv_bfloat16*)p.out + (size_t)(n0 + c + token) * p.ldc + (m0 >> 1) + part * 8) =
+                      *(const uint4*)(xo + token * 64 + part * 8);
+                }
+              } else if (feat < (p.M >> 1)) {
+#pragma unroll
+                for (int j = 0; j < W; ++j)
+                  if (j < nc)
+                    ((__nv_bfloat16*)p.out)[(size_t)(n0 + c + j) * p.ldc + feat] = __float2bfloat16_rn(res[j]);
               }
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");
