@@ -405,9 +405,12 @@ def test_attention_prefill_tcgen05_growing_maximum():
 # ---- few tokens, K split over the CTAs of a cluster that add up through shared memory -----------
 @pytest.mark.parametrize("M", [1, 7, 16, 33, 64, 100, 128])
 @pytest.mark.parametrize("N,K", [(128, 512), (200, 1032), (1000, 520), (3584, 3584), (130, 4104)])
-def test_few_token_linear_in_clusters(M, N, K):
+@pytest.mark.parametrize("red_tokens", [0, 32])
+def test_few_token_linear_in_clusters(M, N, K, red_tokens, monkeypatch):
     """Every split count that the plan may pick (2..8) and the three kinds of output, against the
-    plain float32 product; sizes that are no multiples of the tile (weights.rs:59-78)."""
+    plain float32 product; sizes that are no multiples of the tile (weights.rs:59-78).  The
+    product that adds into its output also by the older route (red.add from single CTAs)."""
+    monkeypatch.setattr(ops, "RED_MAX_TOKENS", red_tokens)
     swap, bn, splits = ops.plan_tensor_core_linear(M, N, K)
     assert swap
     x, w = rnd((M, K), torch.bfloat16, 71), rnd((N, K), torch.bfloat16, 72, 0.05)

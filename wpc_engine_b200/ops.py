@@ -165,13 +165,14 @@ _SMS = 148
 # the tests flip them to reach the kernels that the defaults leave for other sizes.
 PAIR_TILES = True         # many tokens: 256 x 256 tiles on pairs of SMs (tcgen05 cta_group::2)
 CLUSTER_SPLITS = True     # the CTAs that split one tile's K form a cluster and add up through shared memory
-# Products that add into the float32 residual with few tokens and a short K keep the older
-# scheme (one CTA to an SM, deep rings, the slices add their shares with red.global.add): the
-# whole matrix is prefetched into shared memory behind the kernel ahead, and a cluster, which
-# needs all its CTAs placed at once, starts later (o_proj of the 7B shape inside a step: 6.4
-# against 9.0 us at 8 tokens).  The atomics grow with the token count: from 64 tokens on the
-# cluster wins (25.5 against 14.8 us).
-RED_MAX_TOKENS = 32
+# Products that add into the float32 residual with at most RED_MAX_TOKENS tokens and a short K
+# take the older scheme (one CTA to an SM, deep rings, the slices add their shares with
+# red.global.add; the last bits of the sum then depend on the order of arrival).  Off: it won
+# for o_proj of the 7B shape (6.4 against 9.0 us at 8 tokens) while attention left SMs free
+# early for its CTAs to fetch their weights; since attention runs in clusters that end
+# together, the cluster product is faster (a step at batch 8: 3.15 against 3.18 ms, batch 1:
+# 2.87 against 2.91 ms).  The atomics grow with the token count (64 tokens: 25.5 against 14.8 us).
+RED_MAX_TOKENS = 0
 RED_MAX_K_BLOCKS = 64
 _WORKSPACE_FLOATS = 8 << 20        # 32 MiB of split-K partial sums
 _WORKSPACE_COUNTERS = 4096
