@@ -411,7 +411,6 @@ def test_few_token_linear_in_clusters(M, N, K, red_tokens, monkeypatch):
     plain float32 product; sizes that are no multiples of the tile (weights.rs:59-78).  The
     product that adds into its output also by the older route (red.add from single CTAs)."""
     monkeypatch.setattr(ops, "RED_MAX_TOKENS", red_tokens)
-    monkeypatch.setattr(ops, "RED_MAX_CTAS", 148)
     swap, bn, splits = ops.plan_tensor_core_linear(M, N, K)
     assert swap
     x, w = rnd((M, K), torch.bfloat16, 71), rnd((N, K), torch.bfloat16, 72, 0.05)

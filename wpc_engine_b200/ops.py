@@ -165,18 +165,18 @@ _SMS = 148
 # the tests flip them to reach the kernels that the defaults leave for other sizes.
 PAIR_TILES = True         # many tokens: 256 x 256 tiles on pairs of SMs (tcgen05 cta_group::2)
 CLUSTER_SPLITS = True     # the CTAs that split one tile's K form a cluster and add up through shared memory
-# Products that add into the float32 residual with at most RED_MAX_TOKENS tokens, a short K and
-# so few tiles that their CTAs cover at most half of the SMs take the older scheme: one CTA to
-# an SM, deep rings, the slices add their shares with red.global.add (the last bits of the sum
-# then depend on the order of arrival).  Such a product is all fixed cost, and the cluster's
-# tail is the longer one (o_proj of the 0.5B shape, 21 CTAs either way: a step of 16 sequences
-# takes 0.94 against 0.97 ms).  With more tiles the cluster product wins, two CTAs to an SM
-# beside the attention clusters that end together (o_proj of the 7B shape: a step at batch 8
-# 3.15 against 3.18 ms, batch 1 2.87 against 2.91 ms), and the atomics grow with the token
-# count (64 tokens: 25.5 against 14.8 us).
+# A cluster holds at most 8 slices of K.  A product that adds into the float32 residual with at
+# most RED_MAX_TOKENS tokens and so few tiles that its clusters would leave more than half of the
+# SMs idle takes the older scheme instead: up to 16 slices, one CTA to an SM, deep rings, the
+# slices add their shares with red.global.add (the last bits of the sum then depend on the
+# order of arrival).  Measured at the 0.5B shape, 16 sequences: down_proj (7 tiles) as 112 CTAs
+# against 56 in clusters, a step takes 0.84 against 0.94 ms; o_proj, 21 CTAs either way, 0.94
+# against 0.97 ms (the cluster's tail is the longer one).  With more tiles the cluster product
+# wins, two CTAs to an SM beside the attention clusters that end together (o_proj of the 7B
+# shape: a step at batch 8 3.15 against 3.18 ms, batch 1 2.87 against 2.91 ms), and the atomics
+# grow with the token count (64 tokens: 25.5 against 14.8 us).
 RED_MAX_TOKENS = 32
-RED_MAX_K_BLOCKS = 64
-RED_MAX_CTAS = 74
+RED_MAX_K_BLOCKS = 128
 _WORKSPACE_FLOATS = 8 << 20        # 32 MiB of split-K partial sums
 _WORKSPACE_COUNTERS = 4096
 _workspaces = {}
@@ -301,10 +301,10 @@ def _tensor_core_linear(x, w, bias, out, accumulate, static_weight=False) -> boo
     swap, bn, splits = plan_tensor_core_linear(M, N, K)
     cluster = bool(swap and CLUSTER_SPLITS and 2 <= splits <= 8)
     if cluster and accumulate and M <= RED_MAX_TOKENS and (K + 63) // 64 <= RED_MAX_K_BLOCKS:
-        # few tokens, short K, few tiles, added into float32: the slices add their shares with red.add
-        red_splits = _ticket_splits((N + 127) // 128, (K + 63) // 64, bn)
-        if ((N + 127) // 128) * red_splits <= RED_MAX_CTAS:
-            cluster, splits = False, red_splits
+        # few tokens, few tiles, added into float32: the slices add their shares with red.add
+        tiles = (N + 127) // 128
+        if tiles * splits * 2 <= _SMS:
+            cluster, splits = False, _ticket_splits(tiles, (K + 63) // 64, bn)
     tall = tall_tiles(M, N, swap, bn, splits, K, bool(accumulate))
     if tall:
         bn = tall
