@@ -490,7 +490,7 @@ decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bf
   __nv_bfloat16* ks = (__nv_bfloat16*)smem_raw;                       // [DECODE_STAGES][PAGE][STRIDE]
   __nv_bfloat16* vs = ks + DECODE_STAGES * Cfg<HD>::PAGE_ELEMS;
   __shared__ int s_pages[CLUSTER_SEGMENT_PAGES];                      // page numbers of this rank's share
-  __shared__ float s_recv_o[CLUSTER_DECODE_MAX_OUT + CLUSTER_DECODE_MAX_RANKS];   // [rank][element of this rank's share]
+  __shared__ __align__(16) float s_recv_o[CLUSTER_DECODE_MAX_OUT + 4 * CLUSTER_DECODE_MAX_RANKS];   // [rank][element of this rank's share]
   __shared__ float s_recv_ml[CLUSTER_DECODE_MAX_RANKS * 16 * 2];      // [rank][row][maximum, sum]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_rep = nh / nkv;
@@ -590,24 +590,27 @@ decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bf
     sl[warp * 16 + r_hi] = l[1];
   }
   __syncthreads();
-  // ---- this rank's partial result goes to the ranks that own its elements ----
-  const int n_out = n_rep * HD, share = (n_out + C - 1) / C;
+  // ---- this rank's partial result goes to the ranks that own its elements, 16 bytes a store ----
+  // (every store into a peer's shared memory is a packet between two SMs; the shares are
+  // multiples of four elements so that no store straddles two owners)
+  const int n_out = n_rep * HD, share = ((n_out + C - 1) / C + 3) & ~3;
   const uint32_t recv_o = smem_u32(s_recv_o), recv_ml = smem_u32(s_recv_ml);
-  for (int e = tid; e < n_out; e += THREADS) {
-    const int row = e / HD, d = e - row * HD;
+  for (int e = tid * 4; e < n_out; e += THREADS * 4) {
+    const int row = e / HD, d = e - row * HD;                  // four elements of one row: HD is a multiple of 16
     float M = -INFINITY;
 #pragma unroll
     for (int w = 0; w < 4; ++w) M = fmaxf(M, sm[w * 16 + row]);
-    float acc = 0.f, Lsum = 0.f;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f}, Lsum = 0.f;
 #pragma unroll
     for (int w = 0; w < 4; ++w) {
       const float mw = sm[w * 16 + row];
       const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
-      acc += f * so[(w * 16 + row) * HD + d];
+      const float4 ow = *(const float4*)(so + (w * 16 + row) * HD + d);
+      acc[0] += f * ow.x; acc[1] += f * ow.y; acc[2] += f * ow.z; acc[3] += f * ow.w;
       Lsum += f * sl[w * 16 + row];
     }
     const int owner = e / share, idx = e - owner * share;
-    st_peer_f32(peer_smem(recv_o + (uint32_t)(rank * share + idx) * 4, (uint32_t)owner), acc);
+    st_peer_f32x4(peer_smem(recv_o + (uint32_t)(rank * share + idx) * 4, (uint32_t)owner), acc[0], acc[1], acc[2], acc[3]);
     if (d == 0) {
       for (int c = 0; c < C; ++c) {
         const uint32_t at = peer_smem(recv_ml + (uint32_t)((rank * 16 + row) * 2) * 4, (uint32_t)c);
