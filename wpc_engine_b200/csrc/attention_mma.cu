@@ -491,7 +491,7 @@ decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bf
   __nv_bfloat16* vs = ks + DECODE_STAGES * Cfg<HD>::PAGE_ELEMS;
   __shared__ int s_pages[CLUSTER_SEGMENT_PAGES];                      // page numbers of this rank's share
   __shared__ __align__(16) float s_recv_o[CLUSTER_DECODE_MAX_OUT + 4 * CLUSTER_DECODE_MAX_RANKS];   // [rank][element of this rank's share]
-  __shared__ float s_recv_ml[CLUSTER_DECODE_MAX_RANKS * 16 * 2];      // [rank][row][maximum, sum]
+  __shared__ __align__(8) float s_recv_ml[CLUSTER_DECODE_MAX_RANKS * 16 * 2];      // [rank][row][maximum, sum]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_rep = nh / nkv;
   const size_t page_elems = (size_t)nkv * PAGE * HD;
@@ -613,9 +613,7 @@ decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bf
     st_peer_f32x4(peer_smem(recv_o + (uint32_t)(rank * share + idx) * 4, (uint32_t)owner), acc[0], acc[1], acc[2], acc[3]);
     if (d == 0) {
       for (int c = 0; c < C; ++c) {
-        const uint32_t at = peer_smem(recv_ml + (uint32_t)((rank * 16 + row) * 2) * 4, (uint32_t)c);
-        st_peer_f32(at, M);
-        st_peer_f32(at + 4, Lsum);
+        st_peer_f32x2(peer_smem(recv_ml + (uint32_t)((rank * 16 + row) * 2) * 4, (uint32_t)c), M, Lsum);
       }
     }
   }

@@ -84,9 +84,10 @@ __device__ __forceinline__ uint32_t peer_smem(uint32_t addr, uint32_t rank) {
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
   return r;
 }
-// (a peer may be written once it runs: after a cluster barrier at the start of the kernel)
-__device__ __forceinline__ void st_peer_f32(uint32_t addr, float v) {
-  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+// (a peer may be written once it runs: after a cluster barrier at the start of the kernel; every
+// store is a packet between two SMs, so the wide forms are the ones to use)
+__device__ __forceinline__ void st_peer_f32x2(uint32_t addr, float a, float b) {
+  asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(addr), "f"(a), "f"(b) : "memory");
 }
 __device__ __forceinline__ void st_peer_f32x4(uint32_t addr, float a, float b, float c, float d) {
   asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
