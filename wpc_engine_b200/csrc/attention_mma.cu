@@ -347,10 +347,8 @@ decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* 
 #pragma unroll
     for (int d = 0; d < HD / 8; ++d) {
       const int c = d * 8 + (lane & 3) * 2;
-      so[(warp * 16 + r_lo) * HD + c] = o[d][0];
-      so[(warp * 16 + r_lo) * HD + c + 1] = o[d][1];
-      so[(warp * 16 + r_hi) * HD + c] = o[d][2];
-      so[(warp * 16 + r_hi) * HD + c + 1] = o[d][3];
+      *(float2*)(so + (warp * 16 + r_lo) * HD + c) = make_float2(o[d][0], o[d][1]);
+      *(float2*)(so + (warp * 16 + r_hi) * HD + c) = make_float2(o[d][2], o[d][3]);
     }
     if ((lane & 3) == 0) {
       sm[warp * 16 + r_lo] = m[0];
@@ -578,10 +576,8 @@ decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bf
 #pragma unroll
   for (int d = 0; d < HD / 8; ++d) {
     const int c = d * 8 + (lane & 3) * 2;
-    so[(warp * 16 + r_lo) * HD + c] = o[d][0];
-    so[(warp * 16 + r_lo) * HD + c + 1] = o[d][1];
-    so[(warp * 16 + r_hi) * HD + c] = o[d][2];
-    so[(warp * 16 + r_hi) * HD + c + 1] = o[d][3];
+    *(float2*)(so + (warp * 16 + r_lo) * HD + c) = make_float2(o[d][0], o[d][1]);
+    *(float2*)(so + (warp * 16 + r_hi) * HD + c) = make_float2(o[d][2], o[d][3]);
   }
   if ((lane & 3) == 0) {
     sm[warp * 16 + r_lo] = m[0];
