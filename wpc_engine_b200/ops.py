@@ -536,23 +536,28 @@ def attention(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, k_p
 
 
 def plan_decode_ctas(n_seqs: int, n_kv_heads: int, max_ctx_len: int, window: Optional[int],
-                     per_pair: Optional[int] = None, with_estimate: bool = False):
-    """How many CTAs share the pages of a decode step: two to an SM (an SM takes in only so
-    many bytes a second, so all of them should stream), fewer when there are not even four
-    pages of work for each.  `per_pair` forces about that many CTAs per (sequence, kv head)."""
+                     per_pair: Optional[int] = None) -> int:
+    """How many CTAs share the pages of a decode step on the fixed grid (see _plan_decode)."""
+    return _plan_decode(n_seqs, n_kv_heads, max_ctx_len, window, per_pair)[0]
+
+
+def _plan_decode(n_seqs: int, n_kv_heads: int, max_ctx_len: int, window: Optional[int],
+                 per_pair: Optional[int] = None):
+    """(CTAs, estimated microseconds) for the pages of a decode step on the fixed grid: two CTAs
+    to an SM (an SM takes in only so many bytes a second, so all of them should stream), fewer
+    when there are not even four pages of work for each.  `per_pair` forces about that many
+    CTAs per (sequence, kv head)."""
     blocks = (max_ctx_len + PAGE - 1) // PAGE
     if window:
         blocks = min(blocks, (window + PAGE - 1) // PAGE + 1)
     pairs = max(n_seqs * n_kv_heads, 1)
     if per_pair:
-        return max(1, min(pairs * per_pair, 1024))
+        return max(1, min(pairs * per_pair, 1024)), 0.0
     if 3 * _SMS // 2 <= pairs <= 2 * _SMS:
-        if with_estimate:
-            return pairs, 2.0 + 1.5 * blocks
         # nearly two pairs to an SM: a CTA to a pair, so that equally long sequences need no
         # combining at all (64 sequences x 4 KV heads of 4,000 positions: 91 against 99 us);
         # with fewer pairs than that, fewer CTAs would stream too little (192 CTAs: 90 against 77 us)
-        return pairs
+        return pairs, 2.0 + 1.5 * blocks
     # Otherwise the count with the least estimated time (microseconds, fitted to measurements at
     # the 7B shape: a page takes a CTA 1.05 us when it has an SM and a deep ring to itself, 1.5 us
     # when two share an SM and its bandwidth, which also costs about 2 us at the start; combining
@@ -576,9 +581,7 @@ def plan_decode_ctas(n_seqs: int, n_kv_heads: int, max_ctx_len: int, window: Opt
                 t = estimate(n, per, True)
                 if t < best_t:
                     best_n, best_t = n, t
-    if with_estimate:
-        return best_n, best_t
-    return best_n
+    return best_n, best_t
 
 
 # Decode attention with a thread-block cluster to each (sequence, kv head) pair (see
@@ -614,7 +617,7 @@ def plan_decode_cluster(n_seqs: int, n_kv_heads: int, n_heads: int, head_dim: in
     blocks = (max_ctx_len + PAGE - 1) // PAGE
     if window:
         blocks = min(blocks, (window + PAGE - 1) // PAGE + 1)
-    best_c, best_t = 0, plan_decode_ctas(n_seqs, n_kv_heads, max_ctx_len, window, with_estimate=True)[1]
+    best_c, best_t = 0, _plan_decode(n_seqs, n_kv_heads, max_ctx_len, window)[1]
     for c in range(2, 17):
         n = pairs * c
         if n > 2 * _SMS or c > blocks:
