@@ -340,7 +340,7 @@ def test_attention_prefill_window_edges():
     close(got.cpu(), want, torch.bfloat16)
 
 
-@pytest.mark.parametrize("T,inner,K", [(1, 64, 96), (8, 256, 96), (50, 192, 72), (100, 320, 520), (100, 384, 520), (128, 1152, 256), (200, 256, 96),
+@pytest.mark.parametrize("T,inner,K", [(1, 64, 96), (8, 256, 96), (50, 192, 72), (100, 320, 520), (100, 384, 520), (128, 1152, 256), (16, 4864, 896), (5, 1024, 1032), (64, 640, 2056), (200, 256, 96),
                                        (300, 384, 520), (2048, 1024, 256), (8, 18944, 3584), (2048, 2304, 256), (4096, 1152, 128)])
 def test_gated_linear_fused_epilogue(T, inner, K):
     """silu(gate) * up applied by the product's epilogue (both arrangements) against the

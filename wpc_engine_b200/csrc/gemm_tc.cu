@@ -224,11 +224,11 @@ struct Smem {
     return s > MAX_STAGES ? MAX_STAGES : (s < 2 ? 2 : s);
   }
   // Cluster variant: behind the ring, the partial sums that the ranks of the cluster send to this
-  // CTA, [rank][feature][row of this CTA] floats, and the [4][128] floats through which the two
-  // halves of a head exchange their values.  Token rows belong to the ranks in groups of four
+  // CTA, [rank][feature][row of this CTA] floats, and the [8][128] floats through which the two
+  // halves of a head (or the gate and the up rows of a feature) exchange their values.  Token rows belong to the ranks in groups of four
   // (see the kernel), so a CTA has room for 4 * ceil(ceil(BN / 4) / ranks) rows from each rank.
   __host__ __device__ static constexpr int recv_rows(int ranks) { return 4 * (((BN + 3) / 4 + ranks - 1) / ranks); }
-  __host__ __device__ static constexpr int recv_bytes(int ranks) { return (ranks * recv_rows(ranks) + 4) * BM * 4; }
+  __host__ __device__ static constexpr int recv_bytes(int ranks) { return (ranks * recv_rows(ranks) + 8) * BM * 4; }
 };
 
 __device__ __forceinline__ void store_row32(const Params& p, int row, int col0, int n_cols, const float (&v)[32]) {
@@ -502,7 +502,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const int pr = hd ? d % half : 0;                   // index of the pair within the head
       const bool rotated = hd && kind < 2 && pr < p.rope_R;
       const float* recv = red_stage + r * kmax;           // [rank][feature][row of this CTA] received sums
-      float* xbuf = red_stage + S * kmax * BM;            // [4][128]
+      float* xbuf = red_stage + S * kmax * BM;            // [8][128]
       const uint32_t mine = smem_u32(red_stage) + (uint32_t)((my * BM + r) * kmax) * 4;
       // This CTA's groups of four token rows are my, my + S, ...; a round takes ROWS rows: a group
       // where q and k are rotated, two otherwise (64 tokens on 8 ranks are then one round; a round
@@ -548,6 +548,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               sum.x += t.x; sum.y += t.y; sum.z += t.z; sum.w += t.w;
             }
             val[g4] = sum.x + bias; val[g4 + 1] = sum.y + bias; val[g4 + 2] = sum.z + bias; val[g4 + 3] = sum.w + bias;
+          }
+          if (ROWS == 8 && p.gated) {
+            // rows 64..127 of the tile are the up rows of the features in rows 0..63: the upper
+            // half hands its sums over, the lower half writes silu(gate) * up (model.rs:527-531)
+#pragma unroll
+            for (int u = 0; u < ROWS; ++u) xbuf[u * BM + r] = val[u];
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (r < 64) {
+#pragma unroll
+              for (int u = 0; u < ROWS; ++u) val[u] = xbuf[u * BM + r + 64] * __fdividef(val[u], 1.0f + expf(-val[u]));
+#pragma unroll
+              for (int u = 0; u < ROWS; ++u) {
+                const int k = k0 + u, j = ((k >> 2) * S + my) * 4 + (k & 3);
+                if (j < n_valid && !dry)
+                  ((__nv_bfloat16*)p.out)[(size_t)(n0 + j) * p.ldc + (m0 >> 1) + r] = __float2bfloat16_rn(val[u]);
+              }
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");     // the buffer is written again in the next round
+            continue;
           }
           if (ROWS == 4 && hd) {
             // x'_i = x_i c - x_{i+half} s;  x'_{i+half} = x_{i+half} c + x_i s  (rope.rs:36-39)
@@ -1317,7 +1336,7 @@ int wpc_gemm_tc_workspace(int rows_a, int rows_b, int bn, int splits, size_t* sc
 // rows_a).  bn: the tile's extent along rows_b (16, 32, 64, 128; 256 without swap).
 // gated = 1: the weights hold gate and up rows interleaved in blocks of 64 features (64 gate
 // rows, then the 64 up rows of the same features); out is [tokens, features / 2] bfloat16 =
-// silu(gate) * up.  Needs no split and no bias, and bn >= 128 in the normal arrangement.
+// silu(gate) * up.  Needs no bias, no split except in clusters, and bn >= 128 in the normal arrangement.
 // tall = 1 (no split; normal arrangement with bn 256, or swapped with bn 128): tiles of 256 rows
 // of a on one SM, see the kernel;
 // tall = 2: 256 x bn tiles on pairs of SMs (gemm_pair_kernel), bn 128..256 in steps of 16.
@@ -1329,7 +1348,7 @@ int wpc_gemm_tc(const void* a, int lda, int rows_a, const void* b, int ldb, int 
                 float* scratch, size_t scratch_floats, int* counters, int n_counters, int* status,
                 int prefetch_weights, int tall, int cluster, cudaStream_t stream) {
   if (rows_a <= 0 || rows_b <= 0) return 0;
-  if (cluster && (!swap || splits < 2 || splits > 8 || gated)) return WPC_ERR_UNSUPPORTED;
+  if (cluster && (!swap || splits < 2 || splits > 8)) return WPC_ERR_UNSUPPORTED;
   if (tall && swap && (tall != 1 || splits > 1 || cluster || bn != 128)) return WPC_ERR_UNSUPPORTED;
   if (tall && !swap && (splits > 1 || tall > 2 || (tall == 1 && bn != 256))) return WPC_ERR_UNSUPPORTED;
   if (tall == 2 && (bn < 128 || bn > 256 || bn % 16 || (gated && bn % 128))) return WPC_ERR_UNSUPPORTED;
@@ -1345,7 +1364,7 @@ int wpc_gemm_tc(const void* a, int lda, int rows_a, const void* b, int ldb, int 
   p.gated = gated;
   p.scratch = scratch; p.counters = counters; p.status = status;
   p.prefetch_weights = prefetch_weights;
-  if (gated && (bn < (swap ? 16 : 128) || p.splits != 1 || accumulate || !p.out_bf16 || bias ||
+  if (gated && (bn < (swap ? 16 : 128) || (p.splits != 1 && !cluster) || accumulate || !p.out_bf16 || bias ||
                 (swap ? rows_a % BM : rows_b % 128)))
     return WPC_ERR_UNSUPPORTED;
   if (cluster && p.splits < 2) cluster = 0;

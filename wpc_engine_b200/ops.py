@@ -360,13 +360,21 @@ def gated_linear(x: torch.Tensor, w: torch.Tensor, inner: int, group: int, plain
             # twice (gate/up of the 7B shape at 128 tokens: 69.5 against 74.6 us; with 64 tokens
             # and less, two narrow tiles to an SM stream better: 53.8 against 63.2 us)
             tall = 1
+        # few tokens and fewer tiles than SMs (a small model): K is split over clusters, as in linear()
+        splits = 1
+        tiles, k_blocks = (2 * inner + 127) // 128, (K + 63) // 64
+        if swap and CLUSTER_SPLITS and not tall and tiles < _SMS:
+            for s in range(min(8, k_blocks // 4), 1, -1):
+                if tiles <= cluster_capacity(bn, s) and tiles * s <= 2 * _SMS:
+                    splits = s
+                    break
         out = torch.empty((M, inner), dtype=torch.bfloat16, device=x.device)
         scratch, counters, status = workspace(x.device)
         a, b = (w, x) if swap else (x, w)
         _check("gemm_tc", library().wpc_gemm_tc(
             _p(a), a.stride(0), a.shape[0], _p(b), b.stride(0), b.shape[0], K, _p(None), _p(out), _BF16,
-            out.stride(0), 0, 1, int(swap), bn, 1, _p(scratch), ctypes.c_size_t(scratch.numel()), _p(counters),
-            counters.numel(), _p(status), int(static_weight), int(tall), 0, _stream()))
+            out.stride(0), 0, 1, int(swap), bn, splits, _p(scratch), ctypes.c_size_t(scratch.numel()), _p(counters),
+            counters.numel(), _p(status), int(static_weight), int(tall), int(splits > 1), _stream()))
         return out
     return silu_mul(linear(x, w, plain=plain, static_weight=static_weight), inner, group)
 
