@@ -109,9 +109,9 @@ def rope(x, positions, theta):
 
 def linear(x, weight, bias=None):
     """wpc-runtime/src/weights.rs:59-78: y = W x (+ b), W is [out, in] row-major."""
-    y = x @ weight.astype(x.dtype).T
+    y = x @ weight.astype(x.dtype, copy=False).T
     if bias is not None:
-        y = y + bias.astype(x.dtype)
+        y = y + bias.astype(x.dtype, copy=False)
     return y
 
 
@@ -159,15 +159,28 @@ def layer_uses_window(config, layer):
     return layer >= config.get("max_window_layers", 0)
 
 
-def forward(config, tensors, tokens, dtype=np.float32):
+class _Converted:
+    """tensors[name] in another dtype, converted when it is asked for (a model of real size
+    would not fit twice in memory)."""
+
+    def __init__(self, tensors, dt):
+        self.tensors, self.dt = tensors, dt
+
+    def __getitem__(self, name):
+        return self.tensors[name].astype(self.dt, copy=False)
+
+
+def forward(config, tensors, tokens, dtype=np.float32, rows=None):
     """wpc-runtime/src/model.rs:419-547 for a whole sequence: logits [T, vocab] in `dtype`.
 
     Row t holds the logits for the token after position t.  The output head is the
     embedding table when tie_word_embeddings is true (its default, config.rs:18-19;
     model.rs:544-546 always takes that branch) and `lm_head.weight` when it is false.
+    `rows`: the positions whose logits are computed (all by default); the layers always run
+    on the whole sequence.
     """
     dt = np.dtype(dtype)
-    w = {k: v.astype(dt) for k, v in tensors.items()}
+    w = _Converted(tensors, dt)
     nh = config["num_attention_heads"]
     nkv = config["num_key_value_heads"]
     hd = head_dim_of(config)
@@ -177,7 +190,7 @@ def forward(config, tensors, tokens, dtype=np.float32):
     T = tokens.shape[0]
     positions = np.arange(T)
 
-    x = w["model.embed_tokens.weight"][tokens]                      # model.rs:429-430
+    x = tensors["model.embed_tokens.weight"][tokens].astype(dt)     # model.rs:429-430
     for l in range(config["num_hidden_layers"]):
         p = f"model.layers.{l}"
         n1 = rms_norm(x, w[f"{p}.input_layernorm.weight"], eps)     # model.rs:434-435
@@ -193,6 +206,8 @@ def forward(config, tensors, tokens, dtype=np.float32):
         n2 = rms_norm(x, w[f"{p}.post_attention_layernorm.weight"], eps)
         x = x + swiglu(n2, w[f"{p}.mlp.gate_proj.weight"], w[f"{p}.mlp.up_proj.weight"],
                        w[f"{p}.mlp.down_proj.weight"])              # model.rs:518-536
+    if rows is not None:
+        x = x[np.asarray(rows, dtype=np.int64)]
     xf = rms_norm(x, w["model.norm.weight"], eps)                   # model.rs:541-542
     tied = config.get("tie_word_embeddings", True)
     head = w["model.embed_tokens.weight"] if tied else w["lm_head.weight"]

@@ -139,3 +139,54 @@ def test_step_plan_layout():
         plan_step([SequenceStep(0, [1], want=[1])], [0], [[[0]]], 1)
     with pytest.raises(ValueError, match="at least one token"):
         plan_step([SequenceStep(0, [], want=[])], [0], [[[0]]], 1)
+
+
+def test_window_groups_are_sized_by_their_window_when_steps_are_bounded():
+    """With no step bringing a sequence more than 32 tokens, a group that keeps the last 40
+    positions never holds more than 3 pages of a sequence, whatever its length, and its pool is
+    that small; the group that keeps everything is sized by max_tokens.  Values may be narrower
+    or wider than keys."""
+    from wpc_engine_b200.cache.kv_cache import window_pages
+    specs = [KVSpec(2, 16), KVSpec(2, 16, 40), KVSpec(1, 32, None, v_head_dim=8)]
+    c = SequenceCache(specs, 64 * 50, torch.float32, "cpu", max_sequences=4, max_step_tokens=32)
+    full, windowed, narrow = (c.groups[c.layer_group[i]] for i in range(3))
+    assert window_pages(40, 32) == 3 and windowed.n_pages == 12 and full.n_pages == 50
+    assert narrow.k.shape == (1, 50, 1, PAGE, 32) and narrow.v.shape == (1, 50, 1, PAGE, 8)
+    slots = [c.open() for _ in range(4)]
+    for step in range(40):                       # every sequence grows to 1,280 positions, 32 a step
+        for s in slots[:1]:
+            c.reserve(s, 32)
+            assert sum(p >= 0 for p in windowed.tables[s]) <= 3
+            c.commit(s, 32)
+        c.check()
+    assert windowed.pool.n_held <= 3 and full.pool.n_held == 20
+    # what fits: the window group counts at most 3 pages a sequence, the full group all of them
+    assert c.fits([1280, 640, 640, 640]) and not c.fits([1280, 1280, 640, 64])      # 51 pages in the full group
+    assert not c.fits([1, 1, 1, 1, 1])                                               # five sequences, four slots
+    unbounded = SequenceCache(specs, 64 * 50, torch.float32, "cpu", max_sequences=4)
+    assert unbounded.groups[unbounded.layer_group[1]].n_pages == 50
+
+
+def test_a_model_without_keys_and_values_has_no_page_budget():
+    c = SequenceCache([StateSpec((4,)), None], 64, torch.float32, "cpu", max_sequences=3)
+    assert c.kv_groups() == [] and c.fits([10 ** 6, 10 ** 6, 5]) and not c.fits([1] * 4)
+    s = c.open()
+    assert c.reserve(s, 10 ** 6) == 0
+    c.commit(s, 10 ** 6)
+    c.close(s)
+    c.check()
+
+
+def test_a_step_that_did_not_run_gives_its_pages_back():
+    c = make_cache()
+    a = c.open()
+    c.reserve(a, 70)
+    c.commit(a, 70)
+    held = [g.pool.n_held for g in c.groups if isinstance(g, KVGroup)]
+    c.reserve(a, 300)
+    assert [g.pool.n_held for g in c.groups if isinstance(g, KVGroup)] != held
+    c.release_unused(a)
+    assert [g.pool.n_held for g in c.groups if isinstance(g, KVGroup)] == held and c.length(a) == 70
+    c.check()
+    c.close(a)
+    assert all(g.pool.n_held == 0 for g in c.groups if isinstance(g, KVGroup))

@@ -182,7 +182,7 @@ def test_errors_are_loud(engines):
     try:
         with pytest.raises(ValueError, match="token id outside"):
             eng.step([SequenceStep(slot, [256], want=[0])])
-        with pytest.raises(ValueError, match="max_position_embeddings"):
+        with pytest.raises(ValueError, match="longest sequence"):
             eng.step([SequenceStep(slot, [1] * 129, want=[0])])
         with pytest.raises(ValueError, match="twice"):
             eng.step([SequenceStep(slot, [1], want=[0]), SequenceStep(slot, [2], want=[0])])
@@ -318,36 +318,3 @@ def test_medium_model_long_prompt_whole_and_in_chunks(tmp_path_factory):
     assert np.abs(halves - full).max() <= 6e-2 * scale
     assert np.abs(tail - full).max() <= 6e-2 * scale
     assert np.abs(whole - halves).max() <= 3e-2 * scale and np.abs(whole - tail).max() <= 3e-2 * scale
-
-
-def test_real_layer_shape_bfloat16_against_float32():
-    """Two layers of the Qwen2.5-7B shape (28 heads over 4 KV heads of 128, 3,584 wide, 18,944
-    inside, 152,064 tokens, untied head) with random weights: an unequal batch of prompts and a
-    few single-token steps in bfloat16 (cluster products, pair tiles, tcgen05 attention, split
-    decode attention, graphs) against the float32 path on the same weights."""
-    from wpc_engine_b200 import Qwen2Config, SequenceStep, ops
-    cfg = Qwen2Config.from_dict(dict(
-        architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidden_layers=2, hidden_size=3584,
-        num_attention_heads=28, num_key_value_heads=4, intermediate_size=18944, vocab_size=152064,
-        rope_theta=1000000.0, rms_norm_eps=1e-6, max_position_embeddings=32768, tie_word_embeddings=False))
-    rng = np.random.default_rng(0)
-    reqs = [rng.integers(0, cfg.vocab_size, size=n).tolist() for n in (700, 40, 300)]
-
-    def run(dtype):
-        eng = Engine.from_random(cfg, 0, dtype, "cuda:0", max_tokens=4096, max_sequences=4)
-        slots = [eng.open_sequence() for _ in reqs]
-        outs = [eng.step([SequenceStep(s, r, want=[len(r) - 1]) for s, r in zip(slots, reqs)]).float().cpu().numpy()]
-        for i in range(6):
-            toks = [int(r[(i * 7) % len(r)]) for r in reqs]
-            outs.append(eng.step([SequenceStep(s, [t], want=[0]) for s, t in zip(slots, toks)]).float().cpu().numpy())
-        for s in slots:
-            eng.close_sequence(s)
-        eng.cache.check()
-        assert ops.device_status() == 0
-        del eng
-        torch.cuda.empty_cache()
-        return np.stack(outs)
-
-    half, full = run("bfloat16"), run("float32")
-    scale = np.abs(full).max()
-    assert np.abs(half - full).max() <= 4e-2 * scale

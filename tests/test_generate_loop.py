@@ -119,3 +119,51 @@ def test_stop_ids_and_banned_ids_sources(tmp_path, monkeypatch):
     monkeypatch.delenv("WPC_BAN_TOKENS")
     assert banned_from_env() == []
     assert uniform_for(1, 2, 3) == uniform_for(1, 2, 3) != uniform_for(1, 2, 4)
+
+
+def test_plan_batches_takes_what_the_cache_says_fits():
+    # a model without keys and values: only the slots limit a batch
+    assert plan_batches([10 ** 6, 10 ** 6, 5], 10 ** 6, None, 2) == [[0, 1], [2]]
+    # the cache's own answer (every group with its own pool)
+    seen = []
+
+    def fits(lens):
+        seen.append(list(lens))
+        return sum(lens) <= 100
+    assert plan_batches([30, 30, 30, 30], 10, fits, 8) == [[0, 1], [2, 3]]
+    assert [40] in seen and [40, 40, 40] in seen
+    with pytest.raises(ValueError, match="request 1 needs"):
+        plan_batches([5, 200], 10, fits, 8)
+
+
+def test_prompts_come_in_chunks_when_steps_are_bounded():
+    from wpc_engine_b200.engine.generate import prompt_steps
+    steps = prompt_steps([7, 8, 9], [[1, 2, 3, 4, 5], [6], [7, 8, 9]], 2)
+    assert [[(e.slot, list(e.tokens), list(e.want)) for e in s] for s in steps] == [
+        [(7, [1, 2], []), (8, [6], [0]), (9, [7, 8], [])],
+        [(7, [3, 4], []), (9, [9], [0])],
+        [(7, [5], [0])]]
+    assert len(prompt_steps([1], [[1, 2, 3]], None)) == 1
+
+
+class ChunkedFake(FakeEngine):
+    """Answers with real tensors, so that the loop can put the rows of several prompt steps together."""
+    max_step_tokens = 2
+
+    def step(self, entries):
+        import torch
+        super().step(entries)
+        return torch.tensor([[float(self.request_of[e.slot] * 100 + len(self.fed[e.slot]))] for e in entries if len(e.want)])
+
+    def sample(self, logits, slots, temperature, banned=()):
+        assert logits.shape[0] == len(slots)
+        return logits[:, 0].to(int)
+
+
+def test_loop_with_bounded_steps_feeds_chunks_then_one_token_each():
+    eng = ChunkedFake()
+    out = generate(eng, [[1, 2, 3, 4, 5], [6], [7, 8, 9]], GenerationOptions(max_tokens=3))
+    assert out == [[5, 6, 7], [101, 102, 103], [203, 204, 205]]
+    assert [[len(e[1]) for e in s] for s in eng.log[:3]] == [[2, 1, 2], [2, 1], [1]]
+    assert eng.log[3] == [(0, [5], [0]), (1, [101], [0]), (2, [203], [0])]
+    assert sorted(eng.free) == [0, 1, 2, 3]

@@ -327,17 +327,66 @@ def test_attention_decode_cluster_finds_one_far_key():
             assert (out - want[:, None, :]).abs().max().item() <= 2e-2 * want.abs().max().item() + 1e-3, (far, b)
 
 
-def test_attention_prefill_window_edges():
-    """A window's edge: the key just outside the window is made huge; it must not be seen, and
-    the key just inside must."""
-    nh, nkv, hd, W = 2, 1, 32, 40
-    lens, new = [200], [150]
-    qkv, kp, vp, table, seq, pos = paged_case(torch.bfloat16, nh, nkv, hd, lens, new, seed=3)
-    cu = torch.tensor([0, 150], dtype=torch.int32, device=DEV)
-    ctx = torch.tensor(lens, dtype=torch.int32, device=DEV)
-    got = ops.attention(qkv, nh, nkv, hd, kp, vp, table, cu, ctx, seq, pos, 0.2, W, 150, 200)
-    want = ref.attention_plain(qkv.cpu(), nh, nkv, hd, kp.cpu(), vp.cpu(), table.cpu(), seq.cpu(), pos.cpu(), 0.2, W)
-    close(got.cpu(), want, torch.bfloat16)
+def window_case(nh, nkv, hd, L, n_new, W, seed):
+    """One sequence of L positions, the last n_new of them this step's, window W, in which two
+    keys stand out for the step's last query (position L - 1, which sees L - W .. L - 1): the key
+    at L - W - 1, the last one outside the window, which would win by far if it were seen, and the
+    key at L - W, the first one inside, which wins among those that are.  Pages that lie wholly before the window
+    of the step's first query are marked as given back (-1), as the cache leaves them."""
+    qkv, kp, vp, table, seq, pos = paged_case(torch.bfloat16, nh, nkv, hd, [L], [n_new], seed=seed)
+    kp.mul_(0.05)
+    q2 = qkv.clone()
+    q2[-1, : nh * hd] = 0
+    q2[-1, 0: nh * hd: hd] = 8.0                              # every head of the last query asks for element 0
+    outside, inside = L - W - 1, L - W
+    for p_, height in ((outside, 60.0), (inside, 30.0)):
+        page = int(table[0, p_ // 64])
+        kp[page, :, p_ % 64, :] = 0
+        kp[page, :, p_ % 64, 0] = height
+    first_seen = max(0, (L - n_new) - W + 1)
+    for block in range(first_seen // 64):
+        table[0, block] = -1
+    page_in = int(table[0, inside // 64])
+    return q2, kp, vp, table, seq, pos, vp[page_in, :, inside % 64, :].float()
+
+
+def check_window_edge(got_row, want_v, nh, nkv, hd, what):
+    out = got_row.float().view(nkv, nh // nkv, hd)
+    assert (out - want_v[:, None, :]).abs().max().item() <= 3e-2 * want_v.abs().max().item() + 2e-3, what
+
+
+@pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 64), (14, 2, 128), (2, 1, 32)])
+@pytest.mark.parametrize("L,n_new,W", [(448, 150, 128), (449, 150, 128), (500, 2, 100), (700, 300, 193), (330, 200, 64)])
+def test_attention_prefill_window_edges(nh, nkv, hd, L, n_new, W):
+    """A window's edge in the many-token kernels (tcgen05 for head sizes 64 and 128, mma.sync
+    for 32): the key just outside the window of the last query is made huge and must not be
+    seen, the key just inside must win; the edge falls on a page boundary (L - W a multiple
+    of 64), beside one, and inside a page; chunks of two tokens straddle it; pages before the
+    window are gone from the table."""
+    q2, kp, vp, table, seq, pos, want_v = window_case(nh, nkv, hd, L, n_new, W, seed=L)
+    cu = torch.tensor([0, n_new], dtype=torch.int32, device=DEV)
+    ctx = torch.tensor([L], dtype=torch.int32, device=DEV)
+    for mma_only in (False, True):
+        got = ops.attention(q2, nh, nkv, hd, kp, vp, table, cu, ctx, seq, pos, 1.0, W, n_new, L, mma_only=mma_only)
+        check_window_edge(got[-1], want_v, nh, nkv, hd, (mma_only, L, n_new, W))
+    # and every row against the plain kernel, which reads no page that a query cannot see
+    want = ops.attention_plain(q2, nh, nkv, hd, kp, vp, table, seq, pos, 1.0, W)
+    close(got, want, torch.bfloat16)
+    assert ops.device_status() == 0
+
+
+@pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 64), (28, 4, 128), (3, 1, 48)])
+@pytest.mark.parametrize("L,W", [(448, 128), (449, 128), (1000, 100), (4000, 1025), (130, 64)])
+@pytest.mark.parametrize("how", ["grid", "splits", "cluster"])
+def test_attention_decode_window_edges(nh, nkv, hd, L, W, how):
+    """The same edge for a single-token step: the fixed grid, several CTAs to a pair, and a
+    cluster to a pair."""
+    q2, kp, vp, table, seq, pos, want_v = window_case(nh, nkv, hd, L, 1, W, seed=L + 1)
+    cu = torch.tensor([0, 1], dtype=torch.int32, device=DEV)
+    ctx = torch.tensor([L], dtype=torch.int32, device=DEV)
+    kw = {"grid": dict(cluster=0), "splits": dict(splits=3), "cluster": dict(cluster=2 if W < 128 else 3)}[how]
+    got = ops.attention(q2, nh, nkv, hd, kp, vp, table, cu, ctx, seq, pos, 1.0, W, 1, L, **kw)
+    check_window_edge(got[0], want_v, nh, nkv, hd, (how, L, W))
 
 
 @pytest.mark.parametrize("T,inner,K", [(1, 64, 96), (8, 256, 96), (50, 192, 72), (100, 320, 520), (100, 384, 520), (128, 1152, 256), (16, 4864, 896), (5, 1024, 1032), (64, 640, 2056), (200, 256, 96),
@@ -576,3 +625,66 @@ def test_linear_qk_rope_kv_store_fused_many_tokens(nh, nkv, hd, K, new, monkeypa
         page = int(table[b, p_ // 64])
         assert (k1[page, :, p_ % 64].cpu().float() - k3[page, :, p_ % 64]).abs().max().item() <= 1.2e-2 * mag
         assert (v1[page, :, p_ % 64].cpu().float() - v3[page, :, p_ % 64]).abs().max().item() <= 1.2e-2 * mag
+
+
+# ---- the variations of the parts: another activation, another pairing, a norm per head --------------
+@pytest.mark.parametrize("T,inner,K", [(1, 64, 96), (8, 256, 96), (100, 320, 520), (128, 1152, 256), (16, 4864, 896),
+                                       (200, 256, 96), (300, 384, 520), (2048, 1024, 256), (77, 77, 40)])
+@pytest.mark.parametrize("activation", ["silu", "gelu_tanh"])
+def test_gated_linear_activations(T, inner, K, activation):
+    """The activation is a parameter of the gated product: in the epilogue of every arrangement
+    (few tokens in clusters and alone, tiles on one SM, tiles on pairs) and in the kernel that
+    follows a plain product (sizes that the fused epilogue does not take)."""
+    group = 64 if inner % 64 == 0 else inner
+    x = rnd((T, K), torch.bfloat16, 151)
+    w = rnd((2 * inner, K), torch.bfloat16, 152, 0.1)
+    got = ops.gated_linear(x, w, inner, group, activation=activation)
+    want = ref.gated_linear(x.cpu(), w.cpu(), inner, group, activation=activation)
+    mag = want.float().abs().max().item()
+    assert (got.cpu().float() - want.float()).abs().max().item() <= 1.5e-2 * mag
+    if activation == "gelu_tanh":
+        other = ref.gated_linear(x.cpu(), w.cpu(), inner, group, activation="silu")
+        assert (got.cpu().float() - other.float()).abs().max().item() > 3e-2 * mag      # the code is looked at
+    for dtype in DTYPES:
+        gu = rnd((9, 2 * inner), dtype, 153)
+        close(ops.gate_mul(gu, inner, group, activation), ref.gate_mul(gu.cpu(), inner, group, activation).to(DEV), dtype)
+    assert ops.device_status() == 0
+
+
+def test_unknown_activation_is_refused():
+    with pytest.raises(ops.KernelError, match="unknown activation"):
+        ops.gated_linear(rnd((2, 64), torch.bfloat16), rnd((128, 64), torch.bfloat16), 64, 64, activation="relu")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,hd,pairs", [(3, 32, 16), (5, 48, 10), (2, 128, 64)])
+def test_rope_inplace_interleaved_pairs(dtype, heads, hd, pairs):
+    x = rnd((7, (heads + 1) * hd), dtype, 161)
+    pos = torch.tensor([0, 1, 5, 64, 65, 1000, 31999], dtype=torch.int32, device=DEV)
+    inv = torch.tensor(np.power(1e4, -2.0 * np.arange(pairs) / hd), dtype=torch.float64, device=DEV)
+    cos, sin = ops.rope_angles(pos, inv)
+    for inter in (False, True):
+        got = ops.rope_inplace(x.clone(), heads, hd, cos, sin, interleaved=inter)
+        want = ref.rope_inplace(x.cpu().clone(), heads, hd, cos.cpu(), sin.cpu(), interleaved=inter)
+        close(got.cpu(), want, dtype)
+        assert torch.equal(got[:, heads * hd:], x[:, heads * hd:])          # the head behind is left alone
+    a = ops.rope_inplace(x.clone(), heads, hd, cos, sin, interleaved=False)
+    b = ops.rope_inplace(x.clone(), heads, hd, cos, sin, interleaved=True)
+    assert not torch.equal(a, b)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,hd", [(3, 32), (5, 48), (28, 128), (1, 20)])
+def test_head_rmsnorm(dtype, heads, hd):
+    x = rnd((11, (heads + 2) * hd), dtype, 171)
+    gain = 1.0 + rnd((hd,), torch.float32, 172, 0.1)
+    got = ops.head_rmsnorm_(x.clone(), heads, hd, gain, 1e-5)
+    want = ref.head_rmsnorm_(x.cpu().clone(), heads, hd, gain.cpu(), 1e-5)
+    close(got.cpu(), want, dtype)
+    assert torch.equal(got[:, heads * hd:], x[:, heads * hd:])
+    # a view that starts behind other heads, as the k heads of a q/k/v row do
+    view = x.clone()
+    ops.head_rmsnorm_(view[:, hd:], heads, hd, gain, 1e-5)
+    want2 = x.cpu().clone()
+    ref.head_rmsnorm_(want2[:, hd:], heads, hd, gain.cpu(), 1e-5)
+    close(view.cpu(), want2, dtype)

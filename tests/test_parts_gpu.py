@@ -390,3 +390,141 @@ def test_toy_routed_model_with_another_position_encoding(tmp_path, dtype):
         assert np.abs(whole2[5:] - whole[5:]).max() > 1e-3 * scale
     finally:
         wpc.unregister_architecture("ToyRoutedLM")
+
+
+# ---- a third toy architecture: variations of the library's own parts --------------------------------
+# Attention with a norm on every head of q and k between projection and rotation (the option of
+# wpc-runtime/src/model.rs:14-21, 447-462), a rotation that pairs neighbouring elements, a gated
+# feed-forward with another activation, and a schedule whose second entry reads the first
+# entry's keys and values instead of keeping its own.  Checked against a restatement in NumPy.
+from wpc_engine_b200.parts import GatedMLP, HeadRMSNorm
+
+
+class InterleavedRotary(PositionEncoding):
+    """pos * theta^(-2i/head_dim) on the pairs (2i, 2i + 1)."""
+    pairing = "interleaved"
+
+    def __init__(self, head_dim, theta):
+        i = np.arange(head_dim // 2, dtype=np.float64)
+        self._inv = np.power(np.float64(theta), -(2.0 * i) / head_dim)
+        self._dev = None
+
+    def tables(self, ctx):
+        key = ("interleaved_rotary", id(self))
+        if key not in ctx.shared:
+            if self._dev is None:
+                self._dev = torch.from_numpy(self._inv.copy()).to(ctx.positions.device)
+            ctx.shared[key] = _ops.rope_angles(ctx.positions, self._dev)
+        return ctx.shared[key]
+
+
+@dataclasses.dataclass(frozen=True)
+class VariantConfig:
+    vocab_size: int
+    width: int
+    n_heads: int
+    n_kv_heads: int
+    head_dim: int
+    inner: int
+    theta: float
+    eps: float
+    longest: int
+
+    @classmethod
+    def from_dict(cls, raw):
+        return cls(**{f.name: raw[f.name] for f in dataclasses.fields(cls)})
+
+    def to_dict(self):
+        return dict(dataclasses.asdict(self), architectures=["ToyVariantLM"])
+
+
+VARIANT_SCHEDULE = [(0, None), (1, 0), (2, None)]        # (layer, the schedule entry whose cache it reads)
+
+
+def build_variant(c: VariantConfig):
+    pos = InterleavedRotary(c.head_dim, c.theta)
+    blocks = []
+    for _ in range(3):
+        attn = GQAAttention(c.width, c.n_heads, c.n_kv_heads, c.head_dim, pos, qkv_bias=False,
+                            q_norm=HeadRMSNorm(c.head_dim, c.eps), k_norm=HeadRMSNorm(c.head_dim, c.eps))
+        blocks.append(PreNormBlock(RMSNorm(c.width, c.eps), attn, RMSNorm(c.width, c.eps),
+                                   GatedMLP(c.width, c.inner, "gelu_tanh"), names=("ln1", "attn", "ln2", "ffn")))
+    emb = Embedding(c.vocab_size, c.width)
+    return DecoderModel(c, emb, blocks, RMSNorm(c.width, c.eps), OutputHead(c.vocab_size, c.width),
+                        schedule=[Run(layer, cache_of=src) for layer, src in VARIANT_SCHEDULE],
+                        names={"embedding": "wte", "blocks": "h.{}", "final_norm": "ln_f", "head": "head"},
+                        max_positions=c.longest)
+
+
+def variant_plain(c: VariantConfig, tensors, tokens):
+    """The toy model for a whole sequence in float64, from the formulas alone."""
+    w = {k: v.astype(np.float64) for k, v in tensors.items()}
+    T = len(tokens)
+    hd, half = c.head_dim, c.head_dim // 2
+    inv = np.power(np.float64(c.theta), -(2.0 * np.arange(half)) / hd)
+    ang = np.arange(T, dtype=np.float64)[:, None] * inv[None, :]
+    cs, sn = np.cos(ang).astype(np.float32).astype(np.float64), np.sin(ang).astype(np.float32).astype(np.float64)
+
+    def rotate(v):                                    # [T, heads, hd], pairs (2i, 2i + 1)
+        out = v.copy()
+        a, b = v[..., 0::2], v[..., 1::2]
+        out[..., 0::2] = a * cs[:, None, :] - b * sn[:, None, :]
+        out[..., 1::2] = b * cs[:, None, :] + a * sn[:, None, :]
+        return out
+
+    x = w["wte.weight"][np.asarray(tokens)]
+    kept = {}
+    for i, (layer, src) in enumerate(VARIANT_SCHEDULE):
+        p = f"h.{layer}"
+        n1 = P.rms_norm(x, w[f"{p}.ln1.weight"], c.eps)
+        q = (n1 @ w[f"{p}.attn.q_proj.weight"].T).reshape(T, c.n_heads, hd)
+        q = rotate(P.rms_norm(q, w[f"{p}.attn.q_norm.weight"], c.eps))
+        if src is None:
+            k = (n1 @ w[f"{p}.attn.k_proj.weight"].T).reshape(T, c.n_kv_heads, hd)
+            k = rotate(P.rms_norm(k, w[f"{p}.attn.k_norm.weight"], c.eps))
+            v = (n1 @ w[f"{p}.attn.v_proj.weight"].T).reshape(T, c.n_kv_heads, hd)
+            kept[i] = (k, v)
+        else:
+            k, v = kept[src]
+        x = x + P.attention(q, k, v).reshape(T, -1) @ w[f"{p}.attn.o_proj.weight"].T
+        n2 = P.rms_norm(x, w[f"{p}.ln2.weight"], c.eps)
+        g, u = n2 @ w[f"{p}.ffn.gate_proj.weight"].T, n2 @ w[f"{p}.ffn.up_proj.weight"].T
+        act = 0.5 * g * (1.0 + np.tanh(math.sqrt(2.0 / math.pi) * (g + 0.044715 * g ** 3)))
+        x = x + (act * u) @ w[f"{p}.ffn.down_proj.weight"].T
+    return P.rms_norm(x, w["ln_f.weight"], c.eps) @ w["head.weight"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("sizes", [dict(width=48, n_heads=3, n_kv_heads=1, head_dim=16, inner=56),
+                                   dict(width=256, n_heads=4, n_kv_heads=2, head_dim=64, inner=384)])
+def test_toy_model_of_varied_parts_against_numpy(tmp_path, dtype, sizes):
+    """Head norms, interleaved pairs, another activation, a layer that reads another layer's
+    cache: whole, tail one by one and in an unequal batch against the NumPy restatement."""
+    wpc.register_architecture("ToyVariantLM", VariantConfig, build_variant)
+    try:
+        cfg = VariantConfig(vocab_size=150, theta=10000.0, eps=1e-5, longest=256, **sizes)
+        folder = wpc.write_random_model(str(tmp_path / "variant"), cfg, 9, getattr(torch, dtype))
+        eng = wpc.Engine.from_folder(folder, dtype=dtype, max_tokens=2048, max_sequences=4)
+        assert eng.max_positions == 256 and eng.vocab_size == 150
+        # three schedule entries, two of them with a cache of their own
+        assert eng.model.cache_specs()[1] is None and eng.cache.groups[0].n_layers == 2
+        _, tensors = P.read_model_folder(folder)
+        toks = np.random.default_rng(2).integers(0, 150, size=90).tolist()
+        want = variant_plain(cfg, tensors, toks)
+        from helpers import run_batch, run_tail_one_by_one, run_whole
+        bound = 2e-4 * np.abs(want).max() if dtype == "float32" else 0.03 * want.std() + 0.02 * np.abs(want).max()
+        assert np.abs(run_whole(eng, toks) - want).max() <= bound
+        assert np.abs(run_tail_one_by_one(eng, toks, tail=30) - want).max() <= bound
+        batch = run_batch(eng, [toks, toks[:21]], [70, 5])
+        assert np.abs(batch[0] - want).max() <= bound and np.abs(batch[1] - want[:21]).max() <= bound
+        # the parts matter: without the head norms the logits are others
+        for b in eng.model.blocks:
+            b.mixer.q_norm = b.mixer.k_norm = None
+        assert np.abs(run_whole(eng, toks) - want).max() > 10 * bound
+        slot = eng.open_sequence()
+        with pytest.raises(ValueError, match="longest sequence"):
+            eng.step([SequenceStep(slot, [1] * 257, want=[])])
+        eng.close_sequence(slot)
+        eng.cache.check()
+    finally:
+        wpc.unregister_architecture("ToyVariantLM")

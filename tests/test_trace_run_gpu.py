@@ -37,12 +37,13 @@ def bound(want64, dtype, folder, tokens):
     return 0.03 * want64.std() + 0.02 * np.abs(want64).max()
 
 
-@pytest.mark.parametrize("name", ["B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_replay_three_ways(folders, tmp_path, name, dtype):
     folder = folders[(name, dtype)]
     with open(os.path.join(folder, "config.json")) as f:
         vocab = json.load(f)["vocab_size"]
+    # (Tiny-A takes at most 128 positions)
     reqs = {rid: random_tokens(vocab, n, 600 + i) for i, (rid, n) in enumerate([("a", 90), ("b", 40), ("c", 7)])}
     want = {rid: plain_logits(folder, t, np.float64) for rid, t in reqs.items()}
 
@@ -84,6 +85,14 @@ def test_replay_three_ways(folders, tmp_path, name, dtype):
 
     out_dir = str(tmp_path / "out")
     replay(folder, dtype, steps, out_dir, max_tokens=64 * 6)
+    with open(os.path.join(out_dir, "index.jsonl")) as f:
+        index = {rec["step"]: rec for rec in map(json.loads, f)}
+    assert sorted(index) == sorted(s["step"] for s in steps if any(e["want"] for e in s["entries"]))
+    for s in steps:
+        if s["step"] in index:
+            rec = index[s["step"]]
+            assert rec["file"] == f"{s['step']}.f32" and rec["vocab"] == vocab
+            assert rec["rows"] == [{"id": e["id"], "place": p} for e in s["entries"] for p in e["want"]]
     for item in expect:
         if len(item) == 4:
             step, rid, lo, hi = item

@@ -159,3 +159,66 @@ def test_random_weights_mode_is_reproducible_and_distributed_as_stated(tmp_path)
     assert raw["architectures"] == ["Qwen2ForCausalLM"] and Qwen2Config.from_dict(raw) == cfg
     assert os.path.getsize(os.path.join(write_random_model(str(tmp_path / "h"), cfg, 5, torch.bfloat16),
                                         "model.safetensors")) < os.path.getsize(os.path.join(a, "model.safetensors"))
+
+
+def test_a_32_bit_checkpoint_under_bfloat16_stays_32_bit_and_says_so(folders, capsys):
+    """Nothing is converted silently: matrices stored in 32 bits stay float32 (their products
+    then run on the CUDA cores), and one line on standard error names that path."""
+    model = fresh_model(TINY_A)
+    load_weights(model, folders[("A", "float32")], torch.bfloat16, "cpu")
+    err = capsys.readouterr().err
+    assert "stay float32" in err and "model.embed_tokens.weight" in err and err.count("\n") == 1
+    assert model.embedding.table.dtype == torch.float32
+    load_weights(fresh_model(TINY_A), folders[("A", "bfloat16")], torch.bfloat16, "cpu")
+    load_weights(fresh_model(TINY_A), folders[("A", "float32")], torch.float32, "cpu")
+    assert capsys.readouterr().err == ""
+
+
+def test_integer_tables_are_kept_as_int32_and_filled_by_the_random_mode(tmp_path):
+    """A part may want a table of integers (kind "index"): stored as I32 or I64, kept as int32,
+    and the random-weights mode draws it evenly from 0 .. high - 1."""
+    import dataclasses
+    from wpc_engine_b200.models.decoder import DecoderModel
+    from wpc_engine_b200.parts import Embedding, OutputHead, ParamSpec, Part, RMSNorm
+
+    class Lookup(Part):
+        def param_specs(self):
+            return {"map": ParamSpec((40,), kind="index", high=7), "zeros": ParamSpec((3, 2), kind="index")}
+
+        def bind(self, tensors):
+            self.map, self.zeros = tensors["map"], tensors["zeros"]
+
+    @dataclasses.dataclass(frozen=True)
+    class Cfg:
+        vocab_size: int = 40
+        width: int = 8
+
+        @classmethod
+        def from_dict(cls, raw):
+            return cls(raw["vocab_size"], raw["width"])
+
+        def to_dict(self):
+            return dict(dataclasses.asdict(self), architectures=["ToyLookupLM"])
+
+    class WithLookup(DecoderModel):
+        def roots(self):
+            return super().roots() + [("lookup", self.lookup)]
+
+    def build(c):
+        emb = Embedding(c.vocab_size, c.width)
+        m = WithLookup(c, emb, [], RMSNorm(c.width, 1e-5), OutputHead(c.vocab_size, c.width, tied_to=emb))
+        m.lookup = Lookup()
+        return m
+
+    wpc.register_architecture("ToyLookupLM", Cfg, build)
+    try:
+        folder = write_random_model(str(tmp_path / "lookup"), Cfg(), 4, torch.bfloat16)
+        stored = read_all(folder)
+        assert stored["lookup.map"].dtype == torch.int32 and 0 <= int(stored["lookup.map"].min()) \
+            and int(stored["lookup.map"].max()) == 6 and len(set(stored["lookup.map"].tolist())) == 7
+        assert not stored["lookup.zeros"].any()
+        model = build(Cfg())
+        load_weights(model, folder, torch.bfloat16, "cpu")
+        assert model.lookup.map.dtype == torch.int32 and torch.equal(model.lookup.map, stored["lookup.map"])
+    finally:
+        wpc.unregister_architecture("ToyLookupLM")

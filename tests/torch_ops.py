@@ -10,9 +10,9 @@ import math
 import torch
 
 PAGE = 64
-__all__ = ["require_device", "embed", "rmsnorm", "linear", "silu_mul", "gated_linear", "add_", "gather_rows", "convert",
-           "rope_angles", "rope_inplace", "qk_rope_kv_store", "linear_qk_rope_kv_store", "attention", "sample",
-           "fill_normal"]
+__all__ = ["require_device", "embed", "rmsnorm", "linear", "silu_mul", "gate_mul", "gated_linear", "add_", "gather_rows",
+           "convert", "rope_angles", "rope_inplace", "head_rmsnorm_", "qk_rope_kv_store", "linear_qk_rope_kv_store",
+           "attention", "sample", "fill_normal"]
 
 _M64 = (1 << 64) - 1
 
@@ -43,15 +43,27 @@ def linear(x, w, bias=None, out_dtype=None, residual=None, plain=False, static_w
 GATED_GROUP = 64
 
 
-def silu_mul(gu, inner, group=None):
+def activation(name, g):
+    if name == "silu":
+        return g / (1.0 + torch.exp(-g))
+    if name == "gelu_tanh":
+        return 0.5 * g * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (g + 0.044715 * g * g * g)))
+    raise ValueError(name)
+
+
+def gate_mul(gu, inner, group=None, activation_name="silu"):
     group = inner if group is None else group
     v = gu.float().reshape(gu.shape[0], inner // group, 2, group)
     g, u = v[:, :, 0].reshape(gu.shape[0], inner), v[:, :, 1].reshape(gu.shape[0], inner)
-    return (g / (1.0 + torch.exp(-g)) * u).to(gu.dtype)
+    return (activation(activation_name, g) * u).to(gu.dtype)
 
 
-def gated_linear(x, w, inner, group, plain=False, static_weight=False):
-    return silu_mul(linear(x, w), inner, group)
+def silu_mul(gu, inner, group=None):
+    return gate_mul(gu, inner, group, "silu")
+
+
+def gated_linear(x, w, inner, group, plain=False, static_weight=False, activation="silu"):
+    return gate_mul(linear(x, w), inner, group, activation)
 
 
 def add_(x, y):
@@ -72,21 +84,34 @@ def rope_angles(positions, inv_freq):
     return torch.cos(a).float(), torch.sin(a).float()
 
 
-def _rotate(v, cos, sin, head_dim):
+def _rotate(v, cos, sin, head_dim, interleaved=False):
     # v: [T, heads, head_dim] float32
     half, R = head_dim // 2, cos.shape[1]
     out = v.clone()
-    x1, x2 = v[..., :R], v[..., half:half + R]
     c, s = cos[:, None, :], sin[:, None, :]
+    if interleaved:
+        x1, x2 = v[..., 0:2 * R:2], v[..., 1:2 * R:2]
+        out[..., 0:2 * R:2] = x1 * c - x2 * s
+        out[..., 1:2 * R:2] = x2 * c + x1 * s
+        return out
+    x1, x2 = v[..., :R], v[..., half:half + R]
     out[..., :R] = x1 * c - x2 * s
     out[..., half:half + R] = x2 * c + x1 * s
     return out
 
 
-def rope_inplace(x, n_heads, head_dim, cos, sin):
+def rope_inplace(x, n_heads, head_dim, cos, sin, interleaved=False):
     T = x.shape[0]
     v = x[:, :n_heads * head_dim].float().reshape(T, n_heads, head_dim)
-    x[:, :n_heads * head_dim] = _rotate(v, cos, sin, head_dim).reshape(T, -1).to(x.dtype)
+    x[:, :n_heads * head_dim] = _rotate(v, cos, sin, head_dim, interleaved).reshape(T, -1).to(x.dtype)
+    return x
+
+
+def head_rmsnorm_(x, n_heads, head_dim, gain, eps):
+    T = x.shape[0]
+    v = x[:, :n_heads * head_dim].float().reshape(T, n_heads, head_dim)
+    ms = (v * v).sum(-1, keepdim=True) / head_dim
+    x[:, :n_heads * head_dim] = (v * (1.0 / torch.sqrt(ms + eps)) * gain).reshape(T, -1).to(x.dtype)
     return x
 
 

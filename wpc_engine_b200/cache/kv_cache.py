@@ -30,7 +30,7 @@ def pages_for(n_tokens: int) -> int:
 class KVView:
     """What a mixer sees of the cache in one step, for one cache layer."""
     k_pages: torch.Tensor        # [n_pages, n_kv_heads, PAGE, head_dim]
-    v_pages: torch.Tensor
+    v_pages: torch.Tensor        # [n_pages, n_kv_heads, PAGE, value_dim]
     page_table: torch.Tensor     # int32 [B, width]: page of block i of sequence b, -1 if none
     writes: bool = True
 
@@ -43,16 +43,33 @@ class StateView:
     writes: bool = True
 
 
+def window_pages(window: int, max_step_tokens: int) -> int:
+    """The most pages that one sequence holds in a group with `window` when no step brings it
+    more than max_step_tokens tokens: the blocks from the first position that the step's first
+    query sees to the step's last position."""
+    return pages_for(window + max_step_tokens - 1) + 1
+
+
 class KVGroup:
-    def __init__(self, spec: KVSpec, n_layers: int, n_pages: int, dtype: torch.dtype, device):
+    """The keys and values of the cache layers that share one `KVSpec`: tensors and a page pool of
+    the group's own.  `pages_per_sequence` (windowed groups of an engine whose steps are bounded)
+    is the most pages that one sequence ever holds here, None where its length alone bounds it."""
+
+    def __init__(self, spec: KVSpec, n_layers: int, n_pages: int, dtype: torch.dtype, device,
+                 pages_per_sequence: Optional[int] = None):
         self.spec = spec
         self.n_layers = n_layers
         self.n_pages = n_pages
-        shape = (n_layers, n_pages, spec.n_kv_heads, PAGE, spec.head_dim)
-        self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        self.pages_per_sequence = pages_per_sequence
+        self.k = torch.zeros((n_layers, n_pages, spec.n_kv_heads, PAGE, spec.head_dim), dtype=dtype, device=device)
+        self.v = torch.zeros((n_layers, n_pages, spec.n_kv_heads, PAGE, spec.value_dim), dtype=dtype, device=device)
         self.pool = FreeList(n_pages, "page")
         self.tables: Dict[int, List[int]] = {}        # slot -> page of each block (-1: given back)
+
+    def pages_needed(self, n_tokens: int) -> int:
+        """Pages that a sequence grown to n_tokens positions holds here at most."""
+        need = pages_for(n_tokens)
+        return need if self.pages_per_sequence is None else min(need, self.pages_per_sequence)
 
     def open(self, slot: int) -> None:
         self.tables[slot] = []
@@ -62,6 +79,15 @@ class KVGroup:
         need = pages_for(new_len) - len(table)
         if need > 0:
             table.extend(self.pool.take_many(need))
+
+    def release_beyond(self, slot: int, length: int) -> None:
+        """Gives back the pages behind the last position of a sequence of `length` positions
+        (what `reserve` took for a step that did not run)."""
+        table = self.tables[slot]
+        while len(table) > pages_for(length):
+            page = table.pop()
+            if page >= 0:
+                self.pool.give_back(page)
 
     def trim(self, slot: int, length: int) -> None:
         """Gives back the pages that no later query of a windowed group can see."""
@@ -94,17 +120,22 @@ class StateGroup:
 class SequenceCache:
     """Slots, groups and lengths.  `cache_specs[i]` is what cache layer i keeps (None: nothing).
 
-    max_tokens sizes every key/value group's pool: the most positions that live sequences
-    hold at any time, each sequence rounded up to whole pages.
+    max_tokens: the most positions that live sequences hold at any time, each sequence rounded
+    up to whole pages.  It sizes the pool of every key/value group that keeps all positions.
+    A group with a window needs less when no step brings a sequence more than `max_step_tokens`
+    tokens (None: unbounded): then each of the `max_sequences` slots holds at most
+    `window_pages(window, max_step_tokens)` pages there, and the pool is that small.  A model
+    without key/value groups has no pages at all.
     """
 
     def __init__(self, cache_specs: Sequence[object], max_tokens: int, dtype: torch.dtype, device,
-                 max_sequences: Optional[int] = None):
+                 max_sequences: Optional[int] = None, max_step_tokens: Optional[int] = None):
         self.device = device
         self.n_pages = pages_for(max_tokens)
         if self.n_pages < 1:
             raise CacheError(f"max_tokens {max_tokens} gives no page")
         self.n_slots = int(max_sequences) if max_sequences else self.n_pages
+        self.max_step_tokens = None if max_step_tokens is None else int(max_step_tokens)
         self.slots = FreeList(self.n_slots, "slot")
         self.lengths: Dict[int, int] = {}
         self.groups: List[object] = []
@@ -118,7 +149,11 @@ class SequenceCache:
         self.layer_index = [None] * len(cache_specs)
         for spec, layers in by_spec.items():
             if isinstance(spec, KVSpec):
-                group = KVGroup(spec, len(layers), self.n_pages, dtype, device)
+                per_seq, n_pages = None, self.n_pages
+                if spec.window is not None and self.max_step_tokens is not None:
+                    per_seq = window_pages(spec.window, self.max_step_tokens)
+                    n_pages = min(self.n_pages, self.n_slots * per_seq)
+                group = KVGroup(spec, len(layers), n_pages, dtype, device, per_seq)
             elif isinstance(spec, StateSpec):
                 group = StateGroup(spec, len(layers), self.n_slots, device)
             else:
@@ -159,6 +194,21 @@ class SequenceCache:
             if isinstance(g, KVGroup):
                 g.reserve(slot, start + n_new)
         return start
+
+    def release_unused(self, slot: int) -> None:
+        """Undoes `reserve` for a step that did not run: pages behind the sequence's length go back."""
+        for g in self.groups:
+            if isinstance(g, KVGroup):
+                g.release_beyond(slot, self.lengths[slot])
+
+    def fits(self, token_counts: Sequence[int]) -> bool:
+        """Whether sequences grown to these many positions can all live in the cache at once."""
+        if len(token_counts) > self.n_slots:
+            return False
+        for g in self.groups:
+            if isinstance(g, KVGroup) and sum(g.pages_needed(n) for n in token_counts) > g.n_pages:
+                return False
+        return True
 
     def commit(self, slot: int, n_new: int) -> None:
         self.lengths[slot] += n_new

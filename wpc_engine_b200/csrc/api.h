@@ -12,19 +12,29 @@ extern "C" {
 
 // Programmatic dependent launch for all kernels of the library: on (1, the default) or off (0).
 int wpc_set_pdl(int on);
+// How long a kernel waits on one of its mbarriers before it gives up, records
+// WPC_ERR_DEVICE_WAIT in the status word it was given and returns (default 2 s).  `starve` = 1
+// is for tests of that path: the kernels with TMA producers start no copies, so their waits
+// run out; nothing else about them changes.
+int wpc_set_wait_policy(unsigned long long limit_ns, int starve);
 
 int wpc_embed(const int* tokens, const void* table, int table_dtype, float* out, int T, int H, int V,
               cudaStream_t stream);
 int wpc_rmsnorm(const float* x, const float* gain, float eps, void* out, int out_dtype, int T, int H,
                 cudaStream_t stream);
-int wpc_silu_mul(const void* gu, void* out, int dtype, int T, int I, int group, cudaStream_t stream);
+// out[t, i] = act(gate) * up; act: WPC_ACT_SILU (1) or WPC_ACT_GELU_TANH (2) of common.cuh
+int wpc_gate_mul(const void* gu, void* out, int dtype, int T, int I, int group, int act, cudaStream_t stream);
 int wpc_add(float* x, const void* y, int y_dtype, size_t n, cudaStream_t stream);
 int wpc_gather_rows(const float* x, const int* idx, float* out, int n_rows, int H, int T, cudaStream_t stream);
 int wpc_convert(const void* in, int in_dtype, void* out, int out_dtype, size_t n, cudaStream_t stream);
 int wpc_rope_angles(const int* positions, const double* inv_freq, float* cosv, float* sinv, int T, int R,
                     cudaStream_t stream);
+// interleaved = 0: pairs (r, r + hd/2); 1: pairs (2r, 2r + 1)
 int wpc_rope_inplace(void* x, int dtype, int row_stride, int T, int n_heads, int hd, int R, const float* cosv,
-                     const float* sinv, cudaStream_t stream);
+                     const float* sinv, int interleaved, cudaStream_t stream);
+// RMS norm with gain [hd] of each of the first n_heads heads of every row, in place
+int wpc_head_rmsnorm(void* x, int dtype, int row_stride, int T, int n_heads, int hd, const float* gain, float eps,
+                     cudaStream_t stream);
 int wpc_qk_rope_kv_store(void* qkv, int dtype, int row_stride, int T, int nh, int nkv, int hd, int R,
                          const float* cosv, const float* sinv, void* k_pages, void* v_pages,
                          const int* page_table, int table_width, const int* seq_of_token, const int* positions,

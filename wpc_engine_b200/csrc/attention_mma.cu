@@ -764,12 +764,8 @@ static int launch_decode_stages(const void* q, int q_stride, void* out, int out_
   int smem = STAGES * 2 * Cfg<HD>::PAGE_ELEMS * 2;
   if (merge_bytes > smem) smem = merge_bytes;
   if (combine_bytes > smem) smem = combine_bytes;
-  static int configured = 0;
-  if (configured < smem) {
-    cudaError_t e = cudaFuncSetAttribute(decode_kernel<HD, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return (int)e;
-    configured = smem;
-  }
+  static int configured[MAX_DEVICES];
+  if (int rc = allow_smem(decode_kernel<HD, STAGES>, smem, configured)) return rc;
   wpc::launch(decode_kernel<HD, STAGES>, dim3(n_ctas), THREADS, smem, stream, 
       (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pages,
       (const __nv_bfloat16*)v_pages, page_table, table_width, ctx_lens, B, nh, nkv, scale * LOG2E, window,
@@ -800,13 +796,12 @@ static int launch_decode_cluster_stages(const void* q, int q_stride, void* out, 
   const int merge_bytes = (4 * 16 * HD + 2 * 4 * 16) * (int)sizeof(float);
   int smem = STAGES * 2 * Cfg<HD>::PAGE_ELEMS * 2;
   if (merge_bytes > smem) smem = merge_bytes;
-  static int configured = 0;
-  if (configured < smem) {
-    cudaError_t e = cudaFuncSetAttribute(decode_cluster_kernel<HD, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e == cudaSuccess)      // clusters of more than 8 CTAs
-      e = cudaFuncSetAttribute(decode_cluster_kernel<HD, STAGES>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+  static int configured[MAX_DEVICES];
+  if (configured[current_device()] < smem) {
+    // clusters of more than 8 CTAs need the kernel's consent
+    cudaError_t e = cudaFuncSetAttribute(decode_cluster_kernel<HD, STAGES>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
     if (e != cudaSuccess) return (int)e;
-    configured = smem;
+    if (int rc = allow_smem(decode_cluster_kernel<HD, STAGES>, smem, configured)) return rc;
   }
   wpc::launch_clusters(decode_cluster_kernel<HD, STAGES>, dim3((unsigned)(B * nkv * cluster)), THREADS, smem, stream,
                        (unsigned)cluster, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride,
@@ -839,7 +834,7 @@ static int decode_cluster_capacity(int cluster) {
     e = cudaFuncSetAttribute(decode_cluster_kernel<HD, STAGES>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
   if (e != cudaSuccess) { cudaGetLastError(); return -1; }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)(cluster * 148));
+  cfg.gridDim = dim3((unsigned)(cluster * sm_count()));
   cfg.blockDim = dim3(THREADS);
   cfg.dynamicSmemBytes = smem;
   cudaLaunchAttribute attr[1];
@@ -860,13 +855,8 @@ static int launch_prefill(const void* q, int q_stride, void* out, int out_stride
                           const void* v_pages, const int* page_table, int table_width, const int* cu_seqlens,
                           const int* ctx_lens, int B, int max_new, int nh, int nkv, float scale, int window,
                           cudaStream_t stream) {
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         Cfg<HD>::SMEM_BYTES);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
+  static int configured[MAX_DEVICES];
+  if (int rc = allow_smem(prefill_kernel<HD>, Cfg<HD>::SMEM_BYTES, configured)) return rc;
   const int n_rep = nh / nkv;
   dim3 grid((max_new * n_rep + 63) / 64, nkv, B);
   wpc::launch(prefill_kernel<HD>, grid, THREADS, Cfg<HD>::SMEM_BYTES, stream, 

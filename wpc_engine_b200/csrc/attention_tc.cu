@@ -31,7 +31,6 @@ constexpr int THREADS = 128;
 constexpr int ROWS = 128;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float RESCALE_STEP = 8.0f;
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -55,13 +54,13 @@ __device__ __forceinline__ unsigned long long global_ns() {
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
 }
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned long long limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = global_ns();
   for (;;) {
     for (int i = 0; i < 256; ++i)
       if (mbar_try_wait(bar, parity)) return true;
-    if (global_ns() - t0 > WAIT_LIMIT_NS) return false;
+    if (global_ns() - t0 > limit_ns) return false;
   }
 }
 __device__ __forceinline__ void tmem_alloc(uint32_t* holder, int cols) {
@@ -203,7 +202,7 @@ prefill_ws_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                   const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* __restrict__ out, int out_stride,
                   const int* __restrict__ page_table, int table_width, const int* __restrict__ cu_seqlens,
                   const int* __restrict__ ctx_lens, int nh, int nkv, float scale_log2, int window,
-                  int* __restrict__ status) {
+                  int* __restrict__ status, unsigned long long wait_ns, int starve) {
   using C = Cfg<HD>;
   using W = WsCfg<HD, NT>;
   constexpr int NS = W::NS;
@@ -278,8 +277,8 @@ prefill_ws_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
   auto tmem_O = [&](int t) { return tmem_base + NT * 128 + t * HD; };
 
   if (warp == COPY_WARP) {
-    // ---- copies ----
-    if (lane == 0) {
+    // ---- copies (none with `starve`, the tests' way to make the waits below run out) ----
+    if (lane == 0 && !starve) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
       int page_next = max(table[blk0], 0);
@@ -287,12 +286,12 @@ prefill_ws_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
         const int st = j % NS, n = j / NS;
         const int row = (page_next * nkv + g) * PAGE;
         if (j + 1 < n_pg) page_next = max(table[blk0 + j + 1], 0);
-        if (!mbar_wait(k_empty + st, (n & 1) ^ 1)) { atomicExch(failed, 1); break; }
+        if (!mbar_wait(k_empty + st, (n & 1) ^ 1, wait_ns)) { atomicExch(failed, 1); break; }
         mbar_expect_tx(k_full + st, C::PAGE_BYTES);
 #pragma unroll
         for (int hb = 0; hb < C::NB; ++hb)
           tma_load_2d(k_s + st * C::PAGE_BYTES + hb * (PAGE * 128), &map_k, hb * 64, row, k_full + st);
-        if (!mbar_wait(v_empty + st, (n & 1) ^ 1)) { atomicExch(failed, 1); break; }
+        if (!mbar_wait(v_empty + st, (n & 1) ^ 1, wait_ns)) { atomicExch(failed, 1); break; }
         mbar_expect_tx(v_full + st, C::PAGE_BYTES);
 #pragma unroll
         for (int hb = 0; hb < C::NB; ++hb)
@@ -321,20 +320,20 @@ prefill_ws_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
         for (int t = 0; t < NT; ++t) umma_commit(s_full + t * 2 + (j & 1));
         umma_commit(k_empty + j % NS);
       };
-      bool ok = mbar_wait(q_full, 0) && mbar_wait(k_full, 0);
+      bool ok = mbar_wait(q_full, 0, wait_ns) && mbar_wait(k_full, 0, wait_ns);
       if (ok) issue_qk(0);
       for (int j = 0; ok && j < n_pg; ++j) {
         if (j + 1 < n_pg) {
           const int j1 = j + 1;
-          ok = mbar_wait(k_full + j1 % NS, (j1 / NS) & 1);
+          ok = mbar_wait(k_full + j1 % NS, (j1 / NS) & 1, wait_ns);
 #pragma unroll
-          for (int t = 0; t < NT; ++t) ok = ok && mbar_wait(s_empty + t * 2 + (j1 & 1), ((j1 >> 1) & 1) ^ 1);
+          for (int t = 0; t < NT; ++t) ok = ok && mbar_wait(s_empty + t * 2 + (j1 & 1), ((j1 >> 1) & 1) ^ 1, wait_ns);
           if (!ok) break;
           issue_qk(j1);
         }
 #pragma unroll
-        for (int t = 0; t < NT; ++t) ok = ok && mbar_wait(p_full + t, j & 1);
-        ok = ok && mbar_wait(v_full + j % NS, (j / NS) & 1);
+        for (int t = 0; t < NT; ++t) ok = ok && mbar_wait(p_full + t, j & 1, wait_ns);
+        ok = ok && mbar_wait(v_full + j % NS, (j / NS) & 1, wait_ns);
         if (!ok) break;
         fence_after_sync();
         const uint32_t vb = v_s + (j % NS) * C::PAGE_BYTES;
@@ -377,7 +376,7 @@ prefill_ws_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
     bool ok = true;
     for (int j = 0; j < n_pg; ++j) {
       const int bb = j & 1;
-      ok = mbar_wait(s_full + t * 2 + bb, (j >> 1) & 1);
+      ok = mbar_wait(s_full + t * 2 + bb, (j >> 1) & 1, wait_ns);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       fence_after_sync();
@@ -428,7 +427,7 @@ prefill_ws_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
       l_sum += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       // the weighted values of the page before must be done before O and P are touched
       if (j > 0) {
-        ok = mbar_wait(p_empty + t, (j - 1) & 1);
+        ok = mbar_wait(p_empty + t, (j - 1) & 1, wait_ns);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         fence_after_sync();
@@ -455,7 +454,7 @@ prefill_ws_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
       mbar_arrive(p_full + t);
     }
     if (ok) {
-      ok = mbar_wait(p_empty + t, (n_pg - 1) & 1);
+      ok = mbar_wait(p_empty + t, (n_pg - 1) & 1, wait_ns);
       ok = __all_sync(0xffffffffu, ok);
       fence_after_sync();
     }
@@ -503,12 +502,8 @@ static int launch_ws(const void* q, int q_stride, void* out, int out_stride, con
                      int n_pages, const int* page_table, int table_width, const int* cu_seqlens, const int* ctx_lens,
                      int B, int max_new, int nh, int nkv, float scale, int window, int* status, cudaStream_t stream) {
   using W = WsCfg<HD, NT>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(prefill_ws_kernel<HD, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, W::SMEM);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
+  static int configured[MAX_DEVICES];
+  if (int rc = allow_smem(prefill_ws_kernel<HD, NT>, W::SMEM, configured)) return rc;
   // the cache as a matrix [n_pages * nkv * PAGE, HD]: a page of one KV head is 64 of its rows
   const long rows = (long)n_pages * nkv * PAGE;
   if (rows > 0x7fffffffL) return WPC_ERR_TOO_LARGE;
@@ -521,7 +516,7 @@ static int launch_ws(const void* q, int q_stride, void* out, int out_stride, con
   dim3 grid(nkv, (max_new * n_rep + NT * ROWS - 1) / (NT * ROWS), B);
   wpc::launch(prefill_ws_kernel<HD, NT>, grid, W::THREADS, W::SMEM, stream, mk, mv, (const __nv_bfloat16*)q, q_stride,
               (__nv_bfloat16*)out, out_stride, page_table, table_width, cu_seqlens, ctx_lens, nh, nkv, scale * LOG2E,
-              window, status);
+              window, status, wait_policy().limit_ns, wait_policy().starve);
   return launch_status();
 }
 

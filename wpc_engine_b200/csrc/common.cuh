@@ -62,6 +62,34 @@ __device__ __forceinline__ float block_max(float v, float* red) {
   return t;
 }
 
+// ---- the activation of a gated feed-forward: out = act(gate) * up ---------------------------------
+#define WPC_ACT_SILU 1          // g / (1 + exp(-g))  (wpc-runtime/src/model.rs:527-531)
+#define WPC_ACT_GELU_TANH 2     // g/2 (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3)))
+// FAST: the quotient of SiLU by __fdividef (2 units in the last place of float32), for
+// epilogues whose results become bfloat16 at once and where the exact division's slow path
+// would be a branch per element.
+template <bool FAST, int ACT>
+__device__ __forceinline__ float gate_act(float g) {
+  if (ACT == WPC_ACT_GELU_TANH) {
+    const float t = tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g));
+    return 0.5f * g * (1.0f + t);
+  }
+  return FAST ? __fdividef(g, 1.0f + expf(-g)) : g / (1.0f + expf(-g));
+}
+// Runs the statement given last once, with ACT a compile-time copy of `act`: a loop over many
+// elements then has no test inside it (a test per element would turn independent chains of exp
+// and division into branches that run one after the other).
+#define WPC_WITH_ACT(act, ACT, ...)                 \
+  do {                                              \
+    if ((act) == WPC_ACT_GELU_TANH) {               \
+      constexpr int ACT = WPC_ACT_GELU_TANH;        \
+      __VA_ARGS__;                                  \
+    } else {                                        \
+      constexpr int ACT = WPC_ACT_SILU;             \
+      __VA_ARGS__;                                  \
+    }                                               \
+  } while (0)
+
 __host__ __device__ __forceinline__ uint64_t mix64(uint64_t z) {
   z += 0x9E3779B97F4A7C15ull;
   z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
@@ -161,6 +189,52 @@ inline void launch_clusters(void (*kernel)(KArgs...), dim3 grid, dim3 block, siz
   pdl_skip_next() = 0;
   const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
   if (e != cudaSuccess) last_launch_error() = (int)e;
+}
+
+// ---- bounded waits ------------------------------------------------------------------------------
+// Every wait of a kernel on an mbarrier gives up after `limit_ns`; the kernel then records
+// WPC_ERR_DEVICE_WAIT in the device status word and returns.  `starve` is a switch for tests of
+// that path: the warp that starts a kernel's TMA copies starts none, so that the barriers that
+// wait for data are never signalled and the waits run out (nothing is in flight then, nothing
+// traps, and the kernel leaves as it would after a real loss).  Both are copied into a
+// kernel's arguments at launch.
+struct WaitPolicy {
+  unsigned long long limit_ns;
+  int starve;
+};
+inline WaitPolicy& wait_policy() {
+  static WaitPolicy p = {2000000000ull, 0};      // 2 s
+  return p;
+}
+
+// ---- the current device ---------------------------------------------------------------------------
+constexpr int MAX_DEVICES = 64;
+inline int current_device() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return 0;
+  return dev;
+}
+// SMs of the current device (asked once per device).
+inline int sm_count() {
+  static int n[MAX_DEVICES] = {0};
+  const int dev = current_device();
+  if (n[dev] <= 0) {
+    int v = 0;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+    n[dev] = v;
+  }
+  return n[dev];
+}
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per device and kernel: `done` is the
+// kernel's own table of the sizes set so far (zero-initialised static).  Returns 0 or a cudaError_t.
+template <typename K>
+inline int allow_smem(K kernel, int bytes, int (&done)[MAX_DEVICES]) {
+  const int dev = current_device();
+  if (done[dev] >= bytes && done[dev] > 0) return 0;
+  const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e != cudaSuccess) return (int)e;
+  done[dev] = bytes > 0 ? bytes : 1;
+  return 0;
 }
 
 inline int launch_status() {

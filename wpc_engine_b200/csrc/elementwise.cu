@@ -87,10 +87,11 @@ __global__ void rmsnorm_vec_kernel(const float* __restrict__ x, const float* __r
   }
 }
 
-// ---- SiLU(gate) * up (wpc-runtime/src/model.rs:527-531).  gu rows hold gate and up interleaved
-//      in blocks of G features: [G gate | G up | G gate | ...]; G = I is "all gates, then all ups".
+// ---- act(gate) * up, act = SiLU for the reference's model (wpc-runtime/src/model.rs:527-531).
+//      gu rows hold gate and up interleaved in blocks of G features: [G gate | G up | G gate | ...];
+//      G = I is "all gates, then all ups".
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, int G, size_t n) {
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, int G, size_t n, int act) {
   pdl_trigger();
   pdl_wait();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
@@ -99,13 +100,13 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
     const size_t base = t * 2 * I + (size_t)(c / G) * 2 * G + c % G;
     const float g = to_float(gu[base]);
     const float u = to_float(gu[base + G]);
-    out[i] = from_float<T>(g / (1.0f + expf(-g)) * u);
+    WPC_WITH_ACT(act, ACT, out[i] = from_float<T>(gate_act<false, ACT>(g) * u));
   }
 }
 
 // bfloat16, 8 features a thread (G a multiple of 8, rows 16-byte aligned)
 __global__ void silu_mul_vec_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int I,
-                                    int G, size_t n8) {
+                                    int G, size_t n8, int act) {
   pdl_trigger();
   pdl_wait();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x) {
@@ -118,11 +119,13 @@ __global__ void silu_mul_vec_kernel(const __nv_bfloat16* __restrict__ gu, __nv_b
     const __nv_bfloat162* u2 = (const __nv_bfloat162*)&uv;
     uint4 ov;
     __nv_bfloat162* o2 = (__nv_bfloat162*)&ov;
+    WPC_WITH_ACT(act, ACT, {
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const float2 g = __bfloat1622float2(g2[k]), u = __bfloat1622float2(u2[k]);
-      o2[k] = __floats2bfloat162_rn(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y);
-    }
+      for (int k = 0; k < 4; ++k) {
+        const float2 g = __bfloat1622float2(g2[k]), u = __bfloat1622float2(u2[k]);
+        o2[k] = __floats2bfloat162_rn(gate_act<false, ACT>(g.x) * u.x, gate_act<false, ACT>(g.y) * u.y);
+      }
+    });
     *(uint4*)(out + e) = ov;
   }
 }
@@ -177,20 +180,46 @@ __device__ __forceinline__ void rotate_pair(const T* v, int r, int half, float c
   o2 = x2 * c + x1 * s;
 }
 
+// Rotates pair r of every head in place.  interleaved = 0: the pair is (r, r + hd/2), the
+// reference's pairing (rope.rs:34-37); 1: the pair is (2r, 2r + 1).
 template <typename T>
 __global__ void rope_inplace_kernel(T* __restrict__ x, int row_stride, int n_heads, int hd, int R,
-                                    const float* __restrict__ cosv, const float* __restrict__ sinv) {
+                                    const float* __restrict__ cosv, const float* __restrict__ sinv, int interleaved) {
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x, half = hd / 2;
   T* row = x + (size_t)t * row_stride;
   for (int i = threadIdx.x; i < n_heads * R; i += blockDim.x) {
     const int h = i / R, r = i - h * R;
-    float o1, o2;
-    rotate_pair(row + h * hd, r, half, cosv[(size_t)t * R + r], sinv[(size_t)t * R + r], o1, o2);
-    row[h * hd + r] = from_float<T>(o1);
-    row[h * hd + r + half] = from_float<T>(o2);
+    const float c = cosv[(size_t)t * R + r], s = sinv[(size_t)t * R + r];
+    T* a = row + h * hd + (interleaved ? 2 * r : r);
+    T* b = interleaved ? a + 1 : a + half;
+    const float x1 = to_float(*a), x2 = to_float(*b);
+    *a = from_float<T>(x1 * c - x2 * s);
+    *b = from_float<T>(x2 * c + x1 * s);
   }
+}
+
+// ---- RMS norm of every head of a row, in place: a warp to a (token, head); the same arithmetic
+//      as rmsnorm_kernel over hd elements (wpc-runtime/src/model.rs:447-462 applies norm.rs:4-13
+//      to each head's slice)
+template <typename T>
+__global__ void head_rmsnorm_kernel(T* __restrict__ x, int row_stride, int n_heads, int hd,
+                                    const float* __restrict__ gain, float eps, int T_rows) {
+  pdl_trigger();
+  pdl_wait();
+  const int warp = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (warp >= T_rows * n_heads) return;
+  const int t = warp / n_heads, h = warp - t * n_heads;
+  T* v = x + (size_t)t * row_stride + (size_t)h * hd;
+  float ss = 0.f;
+  for (int i = lane; i < hd; i += 32) {
+    const float f = to_float(v[i]);
+    ss += f * f;
+  }
+  ss = warp_sum(ss);
+  const float scale = 1.0f / sqrtf(ss / (float)hd + eps);
+  for (int i = lane; i < hd; i += 32) v[i] = from_float<T>(to_float(v[i]) * scale * gain[i]);
 }
 
 // ---- q and k rotated (q in place), k and v appended to the pages of their sequence
@@ -284,6 +313,13 @@ int wpc_set_pdl(int on) {
   return was;
 }
 
+int wpc_set_wait_policy(unsigned long long limit_ns, int starve) {
+  if (limit_ns == 0) return WPC_ERR_BAD_ARGUMENT;
+  wait_policy().limit_ns = limit_ns;
+  wait_policy().starve = starve ? 1 : 0;
+  return 0;
+}
+
 int wpc_embed(const int* tokens, const void* table, int table_dtype, float* out, int T, int H, int V,
               cudaStream_t stream) {
   if (T <= 0) return 0;
@@ -309,17 +345,17 @@ int wpc_rmsnorm(const float* x, const float* gain, float eps, void* out, int out
   return launch_status();
 }
 
-int wpc_silu_mul(const void* gu, void* out, int dtype, int T, int I, int group, cudaStream_t stream) {
+int wpc_gate_mul(const void* gu, void* out, int dtype, int T, int I, int group, int act, cudaStream_t stream) {
   const size_t n = (size_t)T * I;
   if (n == 0) return 0;
-  if (group < 1 || I % group) return WPC_ERR_BAD_ARGUMENT;
+  if (group < 1 || I % group || (act != WPC_ACT_SILU && act != WPC_ACT_GELU_TANH)) return WPC_ERR_BAD_ARGUMENT;
   if (dtype == WPC_DTYPE_BF16 && group % 8 == 0 && (((uintptr_t)gu | (uintptr_t)out) & 15) == 0) {
     wpc::launch(silu_mul_vec_kernel, grid_for(n / 8, 256), 256, 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I,
-                                                                 group, n / 8);
+                                                                 group, n / 8, act);
     return launch_status();
   }
   WPC_DISPATCH_DTYPE(dtype, Tt, (wpc::launch(silu_mul_kernel<Tt>, grid_for(n, 256), 256, 0, stream, (const Tt*)gu, (Tt*)out,
-                                                                                          I, group, n)));
+                                                                                          I, group, n, act)));
   return launch_status();
 }
 
@@ -356,11 +392,21 @@ int wpc_rope_angles(const int* positions, const double* inv_freq, float* cosv, f
 }
 
 int wpc_rope_inplace(void* x, int dtype, int row_stride, int T, int n_heads, int hd, int R, const float* cosv,
-                     const float* sinv, cudaStream_t stream) {
+                     const float* sinv, int interleaved, cudaStream_t stream) {
   if (T <= 0 || R <= 0) return 0;
   if (hd % 2 || R > hd / 2) return WPC_ERR_BAD_ARGUMENT;
   WPC_DISPATCH_DTYPE(dtype, Tt, (wpc::launch(rope_inplace_kernel<Tt>, T, 256, 0, stream, (Tt*)x, row_stride, n_heads, hd,
-                                                                               R, cosv, sinv)));
+                                                                               R, cosv, sinv, interleaved ? 1 : 0)));
+  return launch_status();
+}
+
+int wpc_head_rmsnorm(void* x, int dtype, int row_stride, int T, int n_heads, int hd, const float* gain, float eps,
+                     cudaStream_t stream) {
+  if (T <= 0 || n_heads <= 0) return 0;
+  if (hd < 1 || !gain) return WPC_ERR_BAD_ARGUMENT;
+  const long warps = (long)T * n_heads;
+  WPC_DISPATCH_DTYPE(dtype, Tt, (wpc::launch(head_rmsnorm_kernel<Tt>, (unsigned)((warps + 7) / 8), 256, 0, stream, (Tt*)x,
+                                             row_stride, n_heads, hd, gain, eps, T)));
   return launch_status();
 }
 

@@ -55,7 +55,6 @@ constexpr int BM = 128;            // rows of A per tile = MMA M
 constexpr int BK = 64;             // K elements per stage: 128 bytes of bfloat16, one swizzle row
 constexpr int UMMA_K = 16;         // K of one tcgen05.mma for 16-bit inputs
 constexpr int THREADS = 192;
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // 2 s
 
 struct Params {
   int M, N, K;                 // rows of A, rows of B, shared dimension
@@ -66,7 +65,8 @@ struct Params {
   int ldc;                     // row stride of out, in elements
   int out_bf16;                // 1: bfloat16, 0: float32
   int accumulate;              // 1: out (float32) += result
-  int gated;                   // 1: features come as [64 gate | 64 up] blocks; out = silu(gate) * up, bfloat16
+  int gated;                   // 0, or the activation (WPC_ACT_*): features come as [64 gate | 64 up] blocks;
+                               //    out = act(gate) * up, bfloat16
   float* scratch;              // split-K partial sums: [tile][split][BN][BM] float32
   int* counters;               // one ticket counter per tile, zero between launches
   int* status;                 // device error word (may be null)
@@ -87,6 +87,8 @@ struct Params {
   const int* seq_of_token;
   const int* positions;
   int n_pages;
+  unsigned long long wait_ns;  // how long a wait on an mbarrier may last (wpc::wait_policy)
+  int starve;                  // test switch: the producer starts no copies, so that the waits run out
   int prefetch_weights;        // 1: the weight operand (A when swapped, else B) is never written while the
                                //    model runs, so its first stages may be fetched before the kernel
                                //    ahead in the stream has finished
@@ -121,14 +123,14 @@ __device__ __forceinline__ unsigned long long global_ns() {
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
 }
-// Bounded wait: false if the barrier did not flip within WAIT_LIMIT_NS.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+// Bounded wait: false if the barrier did not flip within limit_ns.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned long long limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = global_ns();
   for (;;) {
     for (int i = 0; i < 256; ++i)
       if (mbar_try_wait(bar, parity)) return true;
-    if (global_ns() - t0 > WAIT_LIMIT_NS) return false;
+    if (global_ns() - t0 > limit_ns) return false;
   }
 }
 
@@ -381,7 +383,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   if (CL && p.splits > 1) cluster_sync_all();
 
   if (warp == 0) {
-    if (lane == 0) {
+    if (lane == 0 && !p.starve) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");     // the descriptors themselves
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
       int it = 0;                                   // k-blocks loaded so far: position in the ring
@@ -413,7 +415,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         for (; i < n_kb; ++i, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
-          if (!mbar_wait(empty + s, ph ^ 1)) { atomicExch(flags, 1); ok = false; break; }
+          if (!mbar_wait(empty + s, ph ^ 1, p.wait_ns)) { atomicExch(flags, 1); ok = false; break; }
           mbar_expect_tx(full + s, S::STAGE_BYTES);
           uint8_t* a_dst = tiles + s * S::STAGE_BYTES;
           tma_load_2d(a_dst, &map_a, (kb0 + i) * BK, m0, full + s);
@@ -434,13 +436,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int n_kb = w.n_kb;
         const int b = MT == 1 ? (j & 1) : 0;           // two accumulators take turns, or both serve one tile
         const int use = MT == 1 ? (j >> 1) : j;        // how often this accumulator has been used before
-        if (!mbar_wait(accum_empty + b, (use & 1) ^ 1)) { atomicExch(flags, 1); break; }
+        if (!mbar_wait(accum_empty + b, (use & 1) ^ 1, p.wait_ns)) { atomicExch(flags, 1); break; }
         fence_after_sync();
         const uint32_t tmem_d = tmem_base + b * S::TMEM_COLS;
         for (int i = 0; i < n_kb; ++i, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
-          if (!mbar_wait(full + s, ph)) { atomicExch(flags, 1); ok = false; break; }
+          if (!mbar_wait(full + s, ph, p.wait_ns)) { atomicExch(flags, 1); ok = false; break; }
           fence_after_sync();
           const uint32_t a_addr = smem_u32(tiles + s * S::STAGE_BYTES);
           const uint64_t da = smem_desc_sw128(a_addr), db = smem_desc_sw128(a_addr + S::A_BYTES);
@@ -454,7 +456,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           }
           umma_commit(empty + s);       // the stage is free again once these MMAs have read it
         }
-        umma_commit(accum_full + b);    // arrives when everything issued above has finished
+        if (ok) umma_commit(accum_full + b);    // arrives when everything issued above has finished
       }
     }
     __syncwarp();
@@ -556,8 +558,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for (int u = 0; u < ROWS; ++u) xbuf[u * BM + r] = val[u];
             asm volatile("bar.sync 1, 128;" ::: "memory");
             if (r < 64) {
+              WPC_WITH_ACT(p.gated, ACT, {
 #pragma unroll
-              for (int u = 0; u < ROWS; ++u) val[u] = xbuf[u * BM + r + 64] * __fdividef(val[u], 1.0f + expf(-val[u]));
+                for (int u = 0; u < ROWS; ++u) val[u] = xbuf[u * BM + r + 64] * gate_act<true, ACT>(val[u]);
+              });
 #pragma unroll
               for (int u = 0; u < ROWS; ++u) {
                 const int k = k0 + u, j = ((k >> 2) * S + my) * 4 + (k & 3);
@@ -605,7 +609,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (hd) fetch(four, 0); else fetch(eight, 0);
         bool ok = true;
         if (!dry) {
-          ok = mbar_wait(accum_full, 0);
+          ok = mbar_wait(accum_full, 0, p.wait_ns);
           ok = __all_sync(0xffffffffu, ok);               // tcgen05.ld needs the whole warp on one path
           if (!ok) atomicExch(flags, 1);
           fence_after_sync();
@@ -648,7 +652,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const int n0 = w.n0, n_kb = w.n_kb, split = w.split, tile_id = w.tile_id;
       const int b = MT == 1 ? (j & 1) : 0;
       const int use = MT == 1 ? (j >> 1) : j;
-      bool ok = mbar_wait(accum_full + b, use & 1);
+      bool ok = mbar_wait(accum_full + b, use & 1, p.wait_ns);
       ok = __all_sync(0xffffffffu, ok);              // tcgen05.ld needs the whole warp on one path
       if (!ok) atomicExch(flags, 1);
       fence_after_sync();
@@ -735,11 +739,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 tmem_ld32(lane_addr + c + 64 + 32 * k, uu);
                 tmem_ld_wait();
               }
+              WPC_WITH_ACT(p.gated, ACT, {
 #pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                const float g = have_acc ? __uint_as_float(ug[j]) : 0.f, u = have_acc ? __uint_as_float(uu[j]) : 0.f;
-                v[j] = g / (1.0f + expf(-g)) * u;
-              }
+                for (int j = 0; j < 32; ++j) {
+                  const float g = have_acc ? __uint_as_float(ug[j]) : 0.f, u = have_acc ? __uint_as_float(uu[j]) : 0.f;
+                  v[j] = gate_act<false, ACT>(g) * u;
+                }
+              });
               if (row < p.M) store_row32(p, row, (n0 + c) / 2 + 32 * k, 32, v);
             }
           }
@@ -774,13 +780,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               float res[W];
 #pragma unroll
               for (int j = 0; j < W; ++j) res[j] = xch[(c + j) * 64 + r];
+              // (SiLU's quotient to 2 units in the last place of float32, far inside the bfloat16
+              // that it becomes: the exact division has a slow path, a branch again)
+              WPC_WITH_ACT(p.gated, ACT, {
 #pragma unroll
-              for (int j = 0; j < W; ++j) {
-                const float g = have_acc ? __uint_as_float(u32[j]) : 0.f;
-                // the quotient to 2 units in the last place of float32, far inside the bfloat16 that
-                // it becomes (the exact division has a slow path, a branch again)
-                res[j] *= __fdividef(g, 1.0f + expf(-g));
-              }
+                for (int j = 0; j < W; ++j) {
+                  const float g = have_acc ? __uint_as_float(u32[j]) : 0.f;
+                  res[j] *= gate_act<true, ACT>(g);
+                }
+              });
               if (wide) {
 #pragma unroll
                 for (int j = 0; j < W; ++j) xo[j * 64 + r] = __float2bfloat16_rn(res[j]);
@@ -978,7 +986,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   const uint32_t tmem_base = *tmem_holder;
 
   if (warp == 0) {
-    if (lane == 0) {
+    if (lane == 0 && !p.starve) {
       pdl_wait();
       int it = 0;
       bool ok = true;
@@ -988,7 +996,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         for (int i = 0; i < p.k_blocks; ++i, ++it) {
           const int s = it % PAIR_STAGES;
           const uint32_t ph = (it / PAIR_STAGES) & 1;
-          if (!mbar_wait(empty + s, ph ^ 1)) { atomicExch(flags, 1); ok = false; break; }
+          if (!mbar_wait(empty + s, ph ^ 1, p.wait_ns)) { atomicExch(flags, 1); ok = false; break; }
           if (rank == 0) mbar_expect_tx(full + s, 2 * (BM * BK * 2 + (PN >> 1) * BK * 2));
           const uint32_t leader_bar = peer_smem(smem_u32(full + s), 0);
           uint8_t* dst = tiles + s * PAIR_STAGE_BYTES;
@@ -1006,13 +1014,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       bool ok = true;
       for (int t = pair; ok && t < n_tiles; t += n_pairs, ++j) {
         const int b = j & 1, use = j >> 1;
-        if (!mbar_wait(accum_empty + b, (use & 1) ^ 1)) { atomicExch(flags, 1); break; }
+        if (!mbar_wait(accum_empty + b, (use & 1) ^ 1, p.wait_ns)) { atomicExch(flags, 1); break; }
         fence_after_sync();
         const uint32_t tmem_d = tmem_base + b * PAIR_N;
         for (int i = 0; i < p.k_blocks; ++i, ++it) {
           const int s = it % PAIR_STAGES;
           const uint32_t ph = (it / PAIR_STAGES) & 1;
-          if (!mbar_wait(full + s, ph)) { atomicExch(flags, 1); ok = false; break; }
+          if (!mbar_wait(full + s, ph, p.wait_ns)) { atomicExch(flags, 1); ok = false; break; }
           fence_after_sync();
           const uint32_t a_addr = smem_u32(tiles + s * PAIR_STAGE_BYTES);
           const uint64_t da = smem_desc_sw128(a_addr), db = smem_desc_sw128(a_addr + BM * BK * 2);
@@ -1021,7 +1029,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             umma_bf16_pair(tmem_d, da + 2 * k, db + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
           umma_commit_pair(empty + s);
         }
-        umma_commit_pair(accum_full + b);
+        if (ok) umma_commit_pair(accum_full + b);
       }
     }
   } else {
@@ -1033,7 +1041,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       const int tile_n = t / tiles_m, tile_m = t - tile_n * tiles_m;
       const int m0 = tile_m * 2 * BM + (int)rank * BM, n0 = tile_n * PN;
       const int b = j & 1, use = j >> 1;
-      bool ok = mbar_wait(accum_full + b, use & 1);
+      bool ok = mbar_wait(accum_full + b, use & 1, p.wait_ns);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) atomicExch(flags, 1);
       fence_after_sync();
@@ -1053,11 +1061,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
               tmem_ld32(lane_addr + c + 64 + 32 * k, uu);
               tmem_ld_wait();
             }
+            WPC_WITH_ACT(p.gated, ACT, {
 #pragma unroll
-            for (int jj = 0; jj < 32; ++jj) {
-              const float g = have_acc ? __uint_as_float(ug[jj]) : 0.f, u = have_acc ? __uint_as_float(uu[jj]) : 0.f;
-              v[jj] = g / (1.0f + expf(-g)) * u;
-            }
+              for (int jj = 0; jj < 32; ++jj) {
+                const float g = have_acc ? __uint_as_float(ug[jj]) : 0.f, u = have_acc ? __uint_as_float(uu[jj]) : 0.f;
+                v[jj] = gate_act<false, ACT>(g) * u;
+              }
+            });
             if (row < p.M && c < n_valid) store_row32(p, row, (n0 + c) / 2 + 32 * k, 32, v);
           }
         }
@@ -1239,13 +1249,11 @@ static int g_stage_limit = MAX_STAGES;
 template <int BN, bool SWAP, int MT = 1, bool CL = false>
 static int launch(const CUtensorMap& ma, const CUtensorMap& mb, Params& p, cudaStream_t stream) {
   using S = Smem<BN, MT>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, SWAP, MT, CL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         S::total(S::max_stages(1)));
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
+  static int configured[MAX_DEVICES];
+  if (int rc = allow_smem(gemm_tc_kernel<BN, SWAP, MT, CL>, S::total(S::max_stages(1)), configured)) return rc;
+  p.wait_ns = wait_policy().limit_ns;
+  p.starve = wait_policy().starve;
+  const int sms = sm_count();
   const long units = (long)((p.M + MT * BM - 1) / (MT * BM)) * ((p.N + BN - 1) / BN) * p.splits;
   if (units > 0x7fffffffL) return WPC_ERR_TOO_LARGE;
   if (CL) {
@@ -1267,14 +1275,14 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, Params& p, cudaS
   // Many tiles in the normal arrangement: one persistent CTA per SM walks the tiles, its
   // epilogue overlapping the next tile's MMAs.  Otherwise one CTA per unit; if those are few,
   // each is alone on its SM and takes a deep ring, if many, two share an SM.
-  const bool persistent = !SWAP && p.splits == 1 && units > 148;
-  const int per_sm = persistent ? 1 : ((units > 148 && S::max_stages(2) >= 4) ? 2 : 1);
+  const bool persistent = !SWAP && p.splits == 1 && units > sms;
+  const int per_sm = persistent ? 1 : ((units > sms && S::max_stages(2) >= 4) ? 2 : 1);
   int stages = S::max_stages(per_sm);
   const int kb_per = (p.k_blocks + p.splits - 1) / p.splits;
   if (!persistent && stages > kb_per) stages = kb_per < 2 ? 2 : kb_per;
   if (stages > g_stage_limit) stages = g_stage_limit < 2 ? 2 : g_stage_limit;
   p.stages = stages;
-  dim3 grid(persistent ? 148 : (unsigned)units);
+  dim3 grid(persistent ? (unsigned)sms : (unsigned)units);
   // cut tiles of the normal arrangement that add into the output turn their blocks around in
   // shared memory first (see the epilogue): room for [4][32][33] floats behind the ring
   constexpr int RED_STAGE_BYTES = 4 * 32 * 33 * 4;
@@ -1293,15 +1301,14 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, Params& p, cudaS
 
 template <bool ROPE>
 static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, Params& p, cudaStream_t stream) {
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<ROPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
+  static int configured[MAX_DEVICES];
+  if (int rc = allow_smem(gemm_pair_kernel<ROPE>, PAIR_SMEM, configured)) return rc;
+  p.wait_ns = wait_policy().limit_ns;
+  p.starve = wait_policy().starve;
+  const long max_pairs = sm_count() / 2;
   const long n_tiles = (long)((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + p.pair_n - 1) / p.pair_n);
   if (n_tiles > 0x3fffffffL) return WPC_ERR_TOO_LARGE;
-  const unsigned pairs = (unsigned)(n_tiles < 74 ? n_tiles : 74);
+  const unsigned pairs = (unsigned)(n_tiles < max_pairs ? n_tiles : max_pairs);
   p.stages = PAIR_STAGES;
   if (p.M >= 1024) wpc::pdl_skip_next() = 1;          // as in launch(): long kernels do not start early
   wpc::launch_clusters(gemm_pair_kernel<ROPE>, dim3(2 * pairs), THREADS, PAIR_SMEM, stream, 2u, ma, mb, p);
@@ -1334,9 +1341,9 @@ int wpc_gemm_tc_workspace(int rows_a, int rows_b, int bn, int splits, size_t* sc
 // a: [rows_a, K] bfloat16, row stride lda; b: [rows_b, K] bfloat16, row stride ldb.
 // swap = 0: out[rows_a, rows_b] (bias over rows_b);  swap = 1: out[rows_b, rows_a] (bias over
 // rows_a).  bn: the tile's extent along rows_b (16, 32, 64, 128; 256 without swap).
-// gated = 1: the weights hold gate and up rows interleaved in blocks of 64 features (64 gate
-// rows, then the 64 up rows of the same features); out is [tokens, features / 2] bfloat16 =
-// silu(gate) * up.  Needs no bias, no split except in clusters, and bn >= 128 in the normal arrangement.
+// gated = WPC_ACT_SILU (1) or WPC_ACT_GELU_TANH (2): the weights hold gate and up rows interleaved
+// in blocks of 64 features (64 gate rows, then the 64 up rows of the same features); out is
+// [tokens, features / 2] bfloat16 = act(gate) * up.  Needs no bias, no split except in clusters, and bn >= 128 in the normal arrangement.
 // tall = 1 (no split; normal arrangement with bn 256, or swapped with bn 128): tiles of 256 rows
 // of a on one SM, see the kernel;
 // tall = 2: 256 x bn tiles on pairs of SMs (gemm_pair_kernel), bn 128..256 in steps of 16.
@@ -1354,6 +1361,7 @@ int wpc_gemm_tc(const void* a, int lda, int rows_a, const void* b, int ldb, int 
   if (tall == 2 && (bn < 128 || bn > 256 || bn % 16 || (gated && bn % 128))) return WPC_ERR_UNSUPPORTED;
   if (K <= 0 || (lda % 8) || (ldb % 8) || (((uintptr_t)a) & 15) || (((uintptr_t)b) & 15)) return WPC_ERR_UNSUPPORTED;
   if (accumulate && out_dtype != WPC_DTYPE_F32) return WPC_ERR_BAD_ARGUMENT;
+  if (gated != 0 && gated != WPC_ACT_SILU && gated != WPC_ACT_GELU_TANH) return WPC_ERR_BAD_ARGUMENT;
   Params p = {};
   p.stages = 2;
   p.M = rows_a; p.N = rows_b; p.K = K;
@@ -1478,7 +1486,7 @@ int wpc_gemm_tc_rope_store(const void* w, int ldw, const void* x, int ldx, int t
 int wpc_gemm_tc_cluster_capacity(int bn, int splits) {
   if (splits < 2 || splits > 8) return 0;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)(splits * 148));
+  cfg.gridDim = dim3((unsigned)(splits * sm_count()));
   cfg.blockDim = dim3(THREADS);
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -1521,8 +1529,6 @@ static __device__ __align__(256) unsigned char wpc_static_scratch[WPC_STATIC_SCR
 namespace wpc {
 namespace tc {
 
-constexpr int MAX_DEVICES = 64;
-
 // The device address of the scratch array on the current device, looked up once per device.
 static int static_scratch_address(unsigned char** out) {
   static unsigned char* addr[MAX_DEVICES] = {nullptr};
@@ -1563,7 +1569,7 @@ static int tensor_map_uncached(const void* ptr, int rows, int cols, int ld, int 
 extern "C" int wpc_linear_few_tokens_static(const void* x, int ldx, int tokens, const void* w, int ldw, int features,
                                             int K, const float* bias, void* out, int out_dtype, int ldc, int splits,
                                             cudaStream_t stream) {
-  if (tokens < 1 || tokens > 128 || features < 1 || K < 1) return WPC_ERR_BAD_ARGUMENT;
+  if (tokens < 1 || tokens > 128 || features < 1 || K < 1 || splits < 0) return WPC_ERR_BAD_ARGUMENT;
   if ((ldx % 8) || (ldw % 8) || (((uintptr_t)x) & 15) || (((uintptr_t)w) & 15)) return WPC_ERR_UNSUPPORTED;
   if (out_dtype != WPC_DTYPE_BF16 && out_dtype != WPC_DTYPE_F32) return WPC_ERR_BAD_ARGUMENT;
   const int bn = tokens <= 16 ? 16 : tokens <= 32 ? 32 : tokens <= 64 ? 64 : 128;
@@ -1572,7 +1578,7 @@ extern "C" int wpc_linear_few_tokens_static(const void* x, int ldx, int tokens, 
   if (tiles > WPC_STATIC_MAX_TILES) return WPC_ERR_TOO_LARGE;
   const size_t per_split = (size_t)tiles * bn * BM;
   if (splits == 0) {
-    splits = 148 / tiles;
+    splits = sm_count() / tiles;
     if (splits > k_blocks / 4) splits = k_blocks / 4;
     if (splits > 16) splits = 16;
     while (splits > 1 && per_split * splits > WPC_STATIC_SCRATCH_FLOATS) --splits;
@@ -1587,8 +1593,9 @@ extern "C" int wpc_linear_few_tokens_static(const void* x, int ldx, int tokens, 
   float* scratch = (float*)base;
   int* counters = (int*)(base + (size_t)WPC_STATIC_SCRATCH_FLOATS * 4);
   int* status = counters + WPC_STATIC_MAX_TILES;
-  // the tickets must start at zero whatever an earlier call left behind
-  cudaError_t e = cudaMemsetAsync(counters, 0, 8192, stream);
+  // the tickets must start at zero whatever an earlier call left behind; the status word behind
+  // them is left alone, so that wpc_linear_few_tokens_static_status sees what any call recorded
+  cudaError_t e = cudaMemsetAsync(counters, 0, WPC_STATIC_MAX_TILES * sizeof(int), stream);
   if (e != cudaSuccess) return (int)e;
 
   Params p = {};
@@ -1612,4 +1619,16 @@ extern "C" int wpc_linear_few_tokens_static(const void* x, int ldx, int tokens, 
     case 64: return launch<64, true>(ma, mb, p, stream);
     default: return launch<128, true>(ma, mb, p, stream);
   }
+}
+
+extern "C" int wpc_linear_few_tokens_static_status(int* status_out, cudaStream_t stream) {
+  if (!status_out) return WPC_ERR_BAD_ARGUMENT;
+  unsigned char* base = nullptr;
+  int rc = static_scratch_address(&base);
+  if (rc) return rc;
+  int* status = (int*)(base + (size_t)WPC_STATIC_SCRATCH_FLOATS * 4) + WPC_STATIC_MAX_TILES;
+  cudaError_t e = cudaMemcpyAsync(status_out, status, sizeof(int), cudaMemcpyDeviceToHost, stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+  if (e == cudaSuccess && *status_out != 0) e = cudaMemsetAsync(status, 0, sizeof(int), stream);
+  return (int)e;
 }

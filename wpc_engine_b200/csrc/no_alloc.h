@@ -36,7 +36,15 @@
 // streams, or different host threads on different streams) race on the array; run them one
 // after another on one stream.
 //
-// Returns 0, a cudaError_t value, or a WPC_ERR_* code of common.cuh.
+// Returns 0, a cudaError_t value, or a WPC_ERR_* code of common.cuh.  `splits` below zero is a
+// bad argument.
+//
+// Errors that only the GPU can see: every wait inside the kernel is bounded, and a kernel whose
+// wait ran out leaves its output unwritten and records WPC_ERR_DEVICE_WAIT (1004) in a status
+// word that lies in the same array.  wpc_linear_few_tokens_static_status waits for `stream`,
+// copies that word of the current device to `*status_out` (0: every call since the last look
+// went through) and clears it; it allocates nothing either.  A caller that cannot afford the
+// wait after every call asks once per batch of calls: the word keeps the last error.
 #pragma once
 #include <cuda_runtime.h>
 #include <stddef.h>
@@ -52,6 +60,7 @@ extern "C" {
 int wpc_linear_few_tokens_static(const void* x, int ldx, int tokens, const void* w, int ldw, int features, int K,
                                  const float* bias, void* out, int out_dtype, int ldc, int splits,
                                  cudaStream_t stream);
+int wpc_linear_few_tokens_static_status(int* status_out, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

@@ -29,13 +29,16 @@ class DecoderModel:
     wanted rows -> output head (wpc-runtime/src/model.rs:419-547, for many tokens at once).
 
     `names` gives the stored-name prefix of each root part; `ignored` lists stored names that
-    may be present without being used.
+    may be present without being used.  `max_positions`: the longest sequence that the model
+    may see (None: no limit); the builder takes it from whatever key its configuration has.
     """
 
     def __init__(self, config, embedding: Embedding, blocks: Sequence[Block], final_norm: Norm,
                  head: OutputHead, schedule: Optional[Sequence[Run]] = None,
-                 names: Optional[Dict[str, str]] = None, ignored: Sequence[str] = ()):
+                 names: Optional[Dict[str, str]] = None, ignored: Sequence[str] = (),
+                 max_positions: Optional[int] = None):
         self.config = config
+        self.max_positions = None if max_positions is None else int(max_positions)
         self.embedding = embedding
         self.blocks = list(blocks)
         self.final_norm = final_norm
@@ -52,6 +55,11 @@ class DecoderModel:
                 if not 0 <= run.cache_of < i or self.schedule[run.cache_of].cache_of is not None:
                     raise ValueError(f"schedule entry {i} reads the cache of entry {run.cache_of}, "
                                      "which is not an earlier entry with a cache of its own")
+
+    @property
+    def vocab_size(self) -> int:
+        """Token ids that a step may bring: 0 .. vocab_size - 1."""
+        return self.embedding.vocab_size
 
     # -- tensors -----------------------------------------------------------------------------
     def roots(self) -> List[Tuple[str, Part]]:

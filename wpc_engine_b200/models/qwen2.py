@@ -27,4 +27,5 @@ def build_qwen2(config: Qwen2Config) -> DecoderModel:
     embedding = Embedding(c.vocab_size, c.hidden_size)
     head = OutputHead(c.vocab_size, c.hidden_size, tied_to=embedding if c.tie_word_embeddings else None)
     ignored = ("lm_head.weight",) if c.tie_word_embeddings else ()
-    return DecoderModel(c, embedding, blocks, RMSNorm(c.hidden_size, c.rms_norm_eps), head, ignored=ignored)
+    return DecoderModel(c, embedding, blocks, RMSNorm(c.hidden_size, c.rms_norm_eps), head, ignored=ignored,
+                        max_positions=c.max_position_embeddings)

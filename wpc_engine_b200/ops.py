@@ -20,6 +20,9 @@ from .constants import PAGE
 _F32, _BF16 = 0, 1
 _ERRORS = {1001: "bad argument", 1002: "unsupported size", 1003: "size beyond the stated maximum",
            1004: "a device-side wait ran out"}
+# what a non-zero device status word means (written by kernels, read by the host after them)
+_DEVICE_ERRORS = {1001: "a token's position has no page in the cache (its key and value were not written)",
+                  1004: "a wait inside a kernel ran out; the kernel returned without finishing its output"}
 
 
 class KernelError(RuntimeError):
@@ -43,6 +46,13 @@ def library():
                 except (BuildError, OSError) as e:
                     raise KernelError(f"the CUDA kernel library is not available: {e}") from None
     return _lib
+
+
+def set_wait_policy(limit_ns: int = 2_000_000_000, starve: bool = False) -> None:
+    """How long a kernel waits on one of its barriers before it gives up and records an error
+    in the device status word (2 s by default).  `starve` is for tests of that path: kernels
+    with TMA producers then start no copies, so that their waits run out."""
+    _check("set_wait_policy", library().wpc_set_wait_policy(ctypes.c_ulonglong(int(limit_ns)), int(bool(starve))))
 
 
 def set_pdl(on: bool) -> bool:
@@ -160,7 +170,20 @@ def linear_plain(x, w, bias=None, out_dtype=None, residual=None) -> torch.Tensor
     return linear(x, w, bias, out_dtype, residual, plain=True)
 
 
-_SMS = 148
+_SMS = 148                # SMs of a B200, which the launch plans were measured on
+_sms_of = {}
+
+
+def sms() -> int:
+    """SMs of the current device (148 where there is none, for the plans' arithmetic alone)."""
+    if not torch.cuda.is_available():
+        return _SMS
+    dev = torch.cuda.current_device()
+    if dev not in _sms_of:
+        _sms_of[dev] = int(torch.cuda.get_device_properties(dev).multi_processor_count)
+    return _sms_of[dev]
+
+
 # Switches between kernels for the same product.  The defaults are the measured best on B200;
 # the tests flip them to reach the kernels that the defaults leave for other sizes.
 PAIR_TILES = True         # many tokens: 256 x 256 tiles on pairs of SMs (tcgen05 cta_group::2)
@@ -196,10 +219,35 @@ def workspace(device):
     return ws
 
 
+def status_word(device="cuda") -> torch.Tensor:
+    """The device error word itself (int32 [1]), for callers that copy it beside their results."""
+    return workspace(device)[2]
+
+
 def device_status(device="cuda") -> int:
-    """The device error word (0: none): set when a bounded wait inside a kernel ran out."""
+    """The device error word (0: none), read now: it waits for the device.  Kernels set it when
+    a bounded wait ran out (1004) or a position had no page (1001); it keeps the last error
+    until `raise_device_status` or `clear_device_status`."""
     ws = _workspaces.get(torch.device(device).index or 0)
     return 0 if ws is None else int(ws[2].item())
+
+
+def clear_device_status(device="cuda") -> None:
+    ws = _workspaces.get(torch.device(device).index or 0)
+    if ws is not None:
+        ws[2].zero_()
+
+
+def raise_device_status(code: int, device="cuda", what: str = "a kernel") -> None:
+    """Turns a non-zero status word (already read) into a KernelError and clears the word."""
+    if code:
+        clear_device_status(device)
+        raise KernelError(f"{what} reported error {code}: {_DEVICE_ERRORS.get(code, 'unknown code')}")
+
+
+def check_device_status(device="cuda", what: str = "a kernel") -> None:
+    """Reads the status word (waits for the device) and raises KernelError if it is set."""
+    raise_device_status(device_status(device), device, what)
 
 
 _cluster_capacity = {}
@@ -229,7 +277,7 @@ def plan_tensor_core_linear(M: int, N: int, K: int):
         bn = 256 if N >= 256 else 128 if N > 64 else 64
         tiles = m_tiles * ((N + bn - 1) // bn)
     splits = 1
-    if tiles * 2 <= _SMS:
+    if tiles * 2 <= sms():
         if swap and CLUSTER_SPLITS:
             for s in range(min(8, k_blocks // 4), 1, -1):
                 if tiles <= cluster_capacity(bn, s):
@@ -243,7 +291,7 @@ def plan_tensor_core_linear(M: int, N: int, K: int):
 def _ticket_splits(tiles: int, k_blocks: int, bn: int) -> int:
     """Slices of K for products that combine through scratch memory or red.add: about one CTA
     to an SM (two to an SM measured slower in a whole step, also with many tokens)."""
-    splits = max(1, min(_SMS // tiles, k_blocks // 4, 16))
+    splits = max(1, min(sms() // tiles, k_blocks // 4, 16))
     while splits > 1 and tiles * splits * bn * 128 > _WORKSPACE_FLOATS:
         splits -= 1
     if tiles > _WORKSPACE_COUNTERS:
@@ -264,7 +312,7 @@ def tall_tiles(M: int, N: int, swap: bool, bn: int, splits: int, K: int = 0, acc
     if swap or bn != 256 or splits != 1 or M < 256 or (accumulate and K < 8192):
         return 0
     tiles = ((M + 255) // 256) * ((N + 255) // 256)
-    return 256 if _SMS // 2 <= tiles <= _SMS else 0
+    return 256 if sms() // 2 <= tiles <= sms() else 0
 
 
 def pair_tiles(M: int, N: int, swap: bool, bn: int) -> bool:
@@ -284,7 +332,7 @@ def pair_tile_width(M: int, N: int) -> int:
     tiles_m = (M + 255) // 256
     best, best_cost = 256, None
     for pn in PAIR_WIDTHS:
-        waves = -(-(tiles_m * -(-N // pn)) // (_SMS // 2))
+        waves = -(-(tiles_m * -(-N // pn)) // (sms() // 2))
         cost = waves * (pn + 32)
         if best_cost is None or cost < best_cost:
             best, best_cost = pn, cost
@@ -303,7 +351,7 @@ def _tensor_core_linear(x, w, bias, out, accumulate, static_weight=False) -> boo
     if cluster and accumulate and M <= RED_MAX_TOKENS and (K + 63) // 64 <= RED_MAX_K_BLOCKS:
         # few tokens, few tiles, added into float32: the slices add their shares with red.add
         tiles = (N + 127) // 128
-        if tiles * splits * 2 <= _SMS:
+        if tiles * splits * 2 <= sms():
             cluster, splits = False, _ticket_splits(tiles, (K + 63) // 64, bn)
     tall = tall_tiles(M, N, swap, bn, splits, K, bool(accumulate))
     if tall:
@@ -323,26 +371,44 @@ def _tensor_core_linear(x, w, bias, out, accumulate, static_weight=False) -> boo
     return True
 
 
-def silu_mul(gu: torch.Tensor, inner: int, group: Optional[int] = None) -> torch.Tensor:
-    """silu(gate) * up, where a row of gu holds gate and up interleaved in blocks of `group`
-    features ([group gates | group ups | ...]); group None or inner: all gates, then all ups."""
+ACTIVATIONS = {"silu": 1, "gelu_tanh": 2}     # the codes WPC_ACT_* of csrc/common.cuh
+
+
+def _act(name: str) -> int:
+    try:
+        return ACTIVATIONS[name]
+    except KeyError:
+        raise KernelError(f"unknown activation {name!r}; the kernels know {sorted(ACTIVATIONS)}") from None
+
+
+def gate_mul(gu: torch.Tensor, inner: int, group: Optional[int] = None, activation: str = "silu") -> torch.Tensor:
+    """act(gate) * up, where a row of gu holds gate and up interleaved in blocks of `group`
+    features ([group gates | group ups | ...]); group None or inner: all gates, then all ups.
+    activation: "silu" (g / (1 + exp(-g))) or "gelu_tanh"."""
     group = inner if group is None else group
     _need(gu.is_contiguous() and gu.dim() == 2 and gu.shape[1] == 2 * inner, "gu must be contiguous [T, 2*inner]")
     _need(group >= 1 and inner % group == 0, "group must divide inner")
     out = torch.empty((gu.shape[0], inner), dtype=gu.dtype, device=gu.device)
-    _check("silu_mul", library().wpc_silu_mul(_p(gu), _p(out), _code(gu.dtype), gu.shape[0], inner, group, _stream()))
+    _check("gate_mul", library().wpc_gate_mul(_p(gu), _p(out), _code(gu.dtype), gu.shape[0], inner, group,
+                                              _act(activation), _stream()))
     return out
+
+
+def silu_mul(gu: torch.Tensor, inner: int, group: Optional[int] = None) -> torch.Tensor:
+    """silu(gate) * up: `gate_mul` with the reference's activation (model.rs:527-531)."""
+    return gate_mul(gu, inner, group, "silu")
 
 
 GATED_GROUP = 64      # gate/up interleave that lets the tensor-core product apply silu(gate) * up itself
 
 
 def gated_linear(x: torch.Tensor, w: torch.Tensor, inner: int, group: int, plain: bool = False,
-                 static_weight: bool = False) -> torch.Tensor:
-    """silu(x Wg^T) * (x Wu^T) as [T, inner], where w [2*inner, K] holds the rows of Wg and Wu
+                 static_weight: bool = False, activation: str = "silu") -> torch.Tensor:
+    """act(x Wg^T) * (x Wu^T) as [T, inner], where w [2*inner, K] holds the rows of Wg and Wu
     interleaved in blocks of `group`.  With bfloat16 and group 64 the tensor-core product
     applies the activation in its epilogue and the [T, 2*inner] intermediate never reaches
-    memory; otherwise a product and `silu_mul` follow one another."""
+    memory; otherwise a product and `gate_mul` follow one another."""
+    act = _act(activation)
     _rows(x, "x")
     _rows(w, "w")
     M, K = x.shape
@@ -363,9 +429,9 @@ def gated_linear(x: torch.Tensor, w: torch.Tensor, inner: int, group: int, plain
         # few tokens and fewer tiles than SMs (a small model): K is split over clusters, as in linear()
         splits = 1
         tiles, k_blocks = (2 * inner + 127) // 128, (K + 63) // 64
-        if swap and CLUSTER_SPLITS and not tall and tiles < _SMS:
+        if swap and CLUSTER_SPLITS and not tall and tiles < sms():
             for s in range(min(8, k_blocks // 4), 1, -1):
-                if tiles <= cluster_capacity(bn, s) and tiles * s <= 2 * _SMS:
+                if tiles <= cluster_capacity(bn, s) and tiles * s <= 2 * sms():
                     splits = s
                     break
         out = torch.empty((M, inner), dtype=torch.bfloat16, device=x.device)
@@ -373,10 +439,10 @@ def gated_linear(x: torch.Tensor, w: torch.Tensor, inner: int, group: int, plain
         a, b = (w, x) if swap else (x, w)
         _check("gemm_tc", library().wpc_gemm_tc(
             _p(a), a.stride(0), a.shape[0], _p(b), b.stride(0), b.shape[0], K, _p(None), _p(out), _BF16,
-            out.stride(0), 0, 1, int(swap), bn, splits, _p(scratch), ctypes.c_size_t(scratch.numel()), _p(counters),
+            out.stride(0), 0, act, int(swap), bn, splits, _p(scratch), ctypes.c_size_t(scratch.numel()), _p(counters),
             counters.numel(), _p(status), int(static_weight), int(tall), int(splits > 1), _stream()))
         return out
-    return silu_mul(linear(x, w, plain=plain, static_weight=static_weight), inner, group)
+    return gate_mul(linear(x, w, plain=plain, static_weight=static_weight), inner, group, activation)
 
 
 def add_(x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
@@ -415,13 +481,28 @@ def rope_angles(positions: torch.Tensor, inv_freq: torch.Tensor) -> Tuple[torch.
     return cos, sin
 
 
-def rope_inplace(x: torch.Tensor, n_heads: int, head_dim: int, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
-    """Rotates the first n_heads heads of every row of x in place."""
+def rope_inplace(x: torch.Tensor, n_heads: int, head_dim: int, cos: torch.Tensor, sin: torch.Tensor,
+                 interleaved: bool = False) -> torch.Tensor:
+    """Rotates the first n_heads heads of every row of x in place: pair r of a head is the
+    elements (r, r + head_dim/2) (rope.rs:34-37), or (2r, 2r + 1) with `interleaved`."""
     _rows(x, "x")
     _need(x.shape[1] >= n_heads * head_dim and cos.shape == sin.shape and cos.shape[0] == x.shape[0],
           "x too narrow or tables of the wrong length")
+    _need(cos.dtype == torch.float32 and cos.is_contiguous() and sin.is_contiguous(), "tables: contiguous float32")
     _check("rope_inplace", library().wpc_rope_inplace(_p(x), _code(x.dtype), x.stride(0), x.shape[0], n_heads,
-                                                      head_dim, cos.shape[1], _p(cos), _p(sin), _stream()))
+                                                      head_dim, cos.shape[1], _p(cos), _p(sin), int(bool(interleaved)),
+                                                      _stream()))
+    return x
+
+
+def head_rmsnorm_(x: torch.Tensor, n_heads: int, head_dim: int, gain: torch.Tensor, eps: float) -> torch.Tensor:
+    """RMS norm with gain [head_dim] of each of the first n_heads heads of every row of x, in
+    place (the per-head q/k norm of wpc-runtime/src/model.rs:447-462)."""
+    _rows(x, "x")
+    _need(x.shape[1] >= n_heads * head_dim, "x is too narrow")
+    _need(gain.dtype == torch.float32 and gain.numel() == head_dim and gain.is_contiguous(), "gain: float32 [head_dim]")
+    _check("head_rmsnorm", library().wpc_head_rmsnorm(_p(x), _code(x.dtype), x.stride(0), x.shape[0], n_heads, head_dim,
+                                                      _p(gain), ctypes.c_float(eps), _stream()))
     return x
 
 
@@ -438,10 +519,11 @@ def qk_rope_kv_store(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim:
           "pages must be contiguous [n_pages, n_kv_heads, PAGE, head_dim] of qkv's type")
     _need(page_table.dtype == torch.int32 and page_table.is_contiguous(), "page_table must be contiguous int32")
     R = 0 if cos is None else cos.shape[1]
+    _, _, status = workspace(qkv.device)
     _check("qk_rope_kv_store", library().wpc_qk_rope_kv_store(
         _p(qkv), _code(qkv.dtype), qkv.stride(0), qkv.shape[0], n_heads, n_kv_heads, head_dim, R, _p(cos), _p(sin),
         _p(k_pages), _p(v_pages), _p(page_table), page_table.shape[1], _p(seq_of_token), _p(positions),
-        k_pages.shape[0], _p(None), _stream()))
+        k_pages.shape[0], _p(status), _stream()))
 
 
 PREFILL_ATTENTION_TILES = 1     # row tiles of 128 rows to a CTA of the tcgen05 prefill attention (1 or 2)
@@ -561,7 +643,7 @@ def _plan_decode(n_seqs: int, n_kv_heads: int, max_ctx_len: int, window: Optiona
     pairs = max(n_seqs * n_kv_heads, 1)
     if per_pair:
         return max(1, min(pairs * per_pair, 1024)), 0.0
-    if 3 * _SMS // 2 <= pairs <= 2 * _SMS:
+    if 3 * sms() // 2 <= pairs <= 2 * sms():
         # nearly two pairs to an SM: a CTA to a pair, so that equally long sequences need no
         # combining at all (64 sequences x 4 KV heads of 4,000 positions: 91 against 99 us);
         # with fewer pairs than that, fewer CTAs would stream too little (192 CTAs: 90 against 77 us)
@@ -575,17 +657,17 @@ def _plan_decode(n_seqs: int, n_kv_heads: int, max_ctx_len: int, window: Optiona
     # fills its ring, merges and takes a ticket twice (about 8 us).  One sequence of 4,000
     # positions: 84 CTAs of 3 pages, 14 us, against 60 CTAs of 4 or 5 pages, 18 us.
     def estimate(n, per, aligned):
-        page, start = (1.05, 0.0) if n <= _SMS else (1.5, 2.0)
+        page, start = (1.05, 0.0) if n <= sms() else (1.5, 2.0)
         parts = -(-blocks // per)
         return start + per * page + (7.0 + 0.12 * parts if parts > 1 else 0.0) + (0.0 if aligned else 8.0) + 0.002 * n
 
     units = pairs * blocks
-    target = max(1, min(2 * _SMS, pairs * max(blocks // 4, 1)))
+    target = max(1, min(2 * sms(), pairs * max(blocks // 4, 1)))
     best_n, best_t = target, estimate(target, -(-units // target), False)
     for per in range(1, blocks + 1):
         if blocks % per == 0:
             n = pairs * (blocks // per)
-            if n <= 2 * _SMS:
+            if n <= 2 * sms():
                 t = estimate(n, per, True)
                 if t < best_t:
                     best_n, best_t = n, t
@@ -620,7 +702,7 @@ def plan_decode_cluster(n_seqs: int, n_kv_heads: int, n_heads: int, head_dim: in
     SMs, and one that finds no room in any GPC waits for the others to end (32 clusters of 8
     where 33 fit: 28 to 32 us in most launches, 18 us in the others)."""
     pairs = max(n_seqs * n_kv_heads, 1)
-    if not CLUSTER_DECODE or (n_heads // n_kv_heads) * head_dim > CLUSTER_DECODE_MAX_OUT or pairs > _SMS:
+    if not CLUSTER_DECODE or (n_heads // n_kv_heads) * head_dim > CLUSTER_DECODE_MAX_OUT or pairs > sms():
         return 0
     blocks = (max_ctx_len + PAGE - 1) // PAGE
     if window:
@@ -628,9 +710,9 @@ def plan_decode_cluster(n_seqs: int, n_kv_heads: int, n_heads: int, head_dim: in
     best_c, best_t = 0, _plan_decode(n_seqs, n_kv_heads, max_ctx_len, window)[1]
     for c in range(2, 17):
         n = pairs * c
-        if n > 2 * _SMS or c > blocks:
+        if n > 2 * sms() or c > blocks:
             break
-        alone = n <= _SMS
+        alone = n <= sms()
         if pairs * 1.1 > decode_cluster_capacity(head_dim, c, alone):
             continue
         page, start = (1.05, 0.0) if alone else (1.5, 2.0)

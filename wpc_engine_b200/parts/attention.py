@@ -7,7 +7,7 @@ from typing import Dict, Optional
 import torch
 
 from .. import ops
-from .base import KVSpec, Mixer, PositionEncoding
+from .base import HeadNorm, KVSpec, Mixer, PositionEncoding
 from .linear import Linear, fuse_rows
 
 
@@ -19,13 +19,21 @@ class GQAAttention(Mixer):
 
     Query head qh reads KV head qh // (n_heads // n_kv_heads) (model.rs:484).  `window`
     None: a query sees every earlier position and itself; else only the last `window`.
-    `scale` None: 1/sqrt(head_dim) (model.rs:477).  All sizes are parameters.
+    `scale` None: 1/sqrt(head_dim) (model.rs:477).  `q_norm`, `k_norm`: norms of each head
+    of q and of k between projection and position encoding (model.rs:447-462; the Qwen2
+    layers have none).  All sizes are parameters.
+
+    With a position encoding that rotates half-split pairs and no head norms, one kernel does
+    the projection, the rotation and the cache write; otherwise these run one after another
+    (projection, head norms, `position.rotate`, cache write), with the same result.
     """
 
     def __init__(self, width: int, n_heads: int, n_kv_heads: int, head_dim: int,
                  position: Optional[PositionEncoding], qkv_bias: bool = True,
                  window: Optional[int] = None, scale: Optional[float] = None,
-                 names=("q_proj", "k_proj", "v_proj", "o_proj")):
+                 names=("q_proj", "k_proj", "v_proj", "o_proj"),
+                 q_norm: Optional[HeadNorm] = None, k_norm: Optional[HeadNorm] = None,
+                 norm_names=("q_norm", "k_norm")):
         if n_heads % n_kv_heads:
             raise ValueError(f"n_heads {n_heads} is not a multiple of n_kv_heads {n_kv_heads}")
         self.width = int(width)
@@ -40,10 +48,16 @@ class GQAAttention(Mixer):
         self.v_proj = Linear(width, n_kv_heads * head_dim, bias=qkv_bias)
         self.o_proj = Linear(n_heads * head_dim, width, bias=False)
         self.names = tuple(names)
+        self.q_norm, self.k_norm = q_norm, k_norm
+        self.norm_names = tuple(norm_names)
         self.qkv = None
 
     def subparts(self) -> Dict[str, object]:
-        return dict(zip(self.names, (self.q_proj, self.k_proj, self.v_proj, self.o_proj)))
+        subs = dict(zip(self.names, (self.q_proj, self.k_proj, self.v_proj, self.o_proj)))
+        for name, norm in zip(self.norm_names, (self.q_norm, self.k_norm)):
+            if norm is not None:
+                subs[name] = norm
+        return subs
 
     def cache_spec(self):
         return KVSpec(self.n_kv_heads, self.head_dim, self.window)
@@ -57,20 +71,34 @@ class GQAAttention(Mixer):
             lin.weight = w[lo:hi]
             lin.bias = None if b is None else b[lo:hi]
 
+    def _fused(self) -> bool:
+        """Whether one kernel may project, rotate and write the cache: its tail knows half-split
+        rotation by (cos, sin) tables and nothing between projection and rotation."""
+        plain_rotation = self.position is None or (self.position.pairing == "half_split"
+                                                   and type(self.position).rotate is PositionEncoding.rotate)
+        return plain_rotation and self.q_norm is None and self.k_norm is None
+
     def forward(self, ctx, h: torch.Tensor, cache, residual: torch.Tensor):
         nh, nkv, hd = self.n_heads, self.n_kv_heads, self.head_dim
-        cos = sin = None
-        if self.position is not None:
-            cos, sin = self.position.tables(ctx)
-        if cache.writes:
+        if cache.writes and self._fused():
+            cos = sin = None
+            if self.position is not None:
+                cos, sin = self.position.tables(ctx)
             qkv = ops.linear_qk_rope_kv_store(h, self.qkv.weight, self.qkv.bias, nh, nkv, hd, cos, sin,
                                               cache.k_pages, cache.v_pages, cache.page_table,
                                               ctx.seq_of_token, ctx.positions)
         else:
-            # a layer that reads another layer's cache computes queries only
-            qkv = self.q_proj.forward(h)
-            if cos is not None:
-                ops.rope_inplace(qkv, nh, hd, cos, sin)
+            # step by step; a layer that reads another layer's cache computes queries only
+            qkv = self.qkv.forward(h) if cache.writes else self.q_proj.forward(h)
+            if self.q_norm is not None:
+                self.q_norm.forward_heads(ctx, qkv, nh, hd)
+            if self.k_norm is not None and cache.writes:
+                self.k_norm.forward_heads(ctx, qkv[:, nh * hd:], nkv, hd)
+            if self.position is not None:       # the k heads lie right behind the q heads
+                self.position.rotate(ctx, qkv, nh + nkv if cache.writes else nh, hd)
+            if cache.writes:
+                ops.qk_rope_kv_store(qkv, nh, nkv, hd, None, None, cache.k_pages, cache.v_pages, cache.page_table,
+                                     ctx.seq_of_token, ctx.positions)
         attn = ops.attention(qkv, nh, nkv, hd, cache.k_pages, cache.v_pages, cache.page_table,
                              ctx.cu_seqlens, ctx.ctx_lens, ctx.seq_of_token, ctx.positions,
                              self.scale, self.window, ctx.max_new_tokens, ctx.max_ctx_len)

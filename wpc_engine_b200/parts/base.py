@@ -11,9 +11,14 @@ What each kind of part must offer:
   `bind(tensors)` (receives them on the device; may re-lay them out, bit-exactly).
 * `Norm`:               `forward(ctx, x)`: x is the float32 residual stream [T, width];
                          returns the normed rows in the activation dtype.
-* `PositionEncoding`:    `tables(ctx)`: whatever its mixer needs for this step's positions,
-                         computed once a step and shared by all layers that hold the same
-                         encoding object.
+* `HeadNorm`:           `forward_heads(ctx, x, n_heads, head_dim)`: norms each of the first
+                         n_heads heads of every row of x (activation dtype) in place.
+* `PositionEncoding`:    `pairing` names which two elements of a head are rotated together:
+                         "half_split" (i, i + head_dim/2) or "interleaved" (2i, 2i + 1);
+                         `tables(ctx)`: (cos, sin), float32 [T, pairs], for this step's
+                         positions, computed once a step and shared by all layers that hold
+                         the same encoding object; `rotate(ctx, x, n_heads, head_dim)` applies
+                         them in place (an encoding that is no rotation overrides it).
 * `Mixer`:               `cache_spec()`: what it keeps per sequence (`KVSpec`, `StateSpec` or
                          None); `forward(ctx, h, cache, residual)`: h is [T, width] in the
                          activation dtype; it either adds its output to `residual` in place
@@ -40,18 +45,28 @@ class ParamSpec:
           "vector" (gains and biases: widened to float32, which is exact),
           "table"  (rows looked up by an integer id: kept like a matrix),
           "index"  (a table of integers: kept as int32).
+    init: how the random-weights mode fills it: "normal" (N(0, 0.02)), "gain" (1 + N(0, 0.02));
+          an "index" tensor is filled with integers drawn evenly from 0 .. high - 1 (zeros
+          without `high`).
     """
     shape: Tuple[int, ...]
     kind: str = "matrix"
-    init: str = "normal"       # how the random-weights mode fills it: "normal" or "gain"
+    init: str = "normal"
+    high: Optional[int] = None
 
 
 @dataclass(frozen=True)
 class KVSpec:
-    """Keys and values per position: `window` None keeps all of them, else the last `window`."""
+    """Keys and values per position: `window` None keeps all of them, else the last `window`.
+    `v_head_dim` None: values are as wide as keys (`head_dim`)."""
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    v_head_dim: Optional[int] = None
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_head_dim is None else self.v_head_dim
 
 
 @dataclass(frozen=True)
@@ -84,9 +99,25 @@ class Norm(Part):
         raise NotImplementedError
 
 
+class HeadNorm(Part):
+    def forward_heads(self, ctx, x: torch.Tensor, n_heads: int, head_dim: int) -> None:
+        raise NotImplementedError
+
+
 class PositionEncoding(Part):
+    pairing = "half_split"
+
     def tables(self, ctx):
         raise NotImplementedError
+
+    def rotate(self, ctx, x: torch.Tensor, n_heads: int, head_dim: int) -> None:
+        """Applies the encoding to the first n_heads heads of every row of x, in place."""
+        from .. import ops
+        if self.pairing not in ("half_split", "interleaved"):
+            raise ValueError(f"{type(self).__name__}: pairing must be 'half_split' or 'interleaved', "
+                             f"got {self.pairing!r}")
+        cos, sin = self.tables(ctx)
+        ops.rope_inplace(x, n_heads, head_dim, cos, sin, interleaved=self.pairing == "interleaved")
 
 
 class Mixer(Part):

@@ -1,4 +1,4 @@
-"""Gated feed-forward with SiLU (wpc-runtime/src/model.rs:518-536)."""
+"""Gated feed-forward (wpc-runtime/src/model.rs:518-536: with SiLU)."""
 from __future__ import annotations
 
 from typing import Dict
@@ -10,8 +10,9 @@ from .base import FeedForward
 from .linear import Linear
 
 
-class SwiGLU(FeedForward):
-    """down( silu(gate(h)) * up(h) ), no biases (model.rs:107-109).
+class GatedMLP(FeedForward):
+    """down( act(gate(h)) * up(h) ), no biases (model.rs:107-109).  `activation` is one of
+    `ops.ACTIVATIONS` ("silu": the reference's, model.rs:527-531; "gelu_tanh").
 
     After loading, the gate and up matrices become one [2*inner, width] matrix so that one
     product reads h once.  Their rows are interleaved in blocks of `group` features (`group`
@@ -21,7 +22,10 @@ class SwiGLU(FeedForward):
     output is still the same dot product of the same row: a pure re-layout.
     """
 
-    def __init__(self, width: int, inner: int):
+    def __init__(self, width: int, inner: int, activation: str = "silu"):
+        if activation not in ops.ACTIVATIONS:
+            raise ValueError(f"unknown activation {activation!r}; known: {sorted(ops.ACTIVATIONS)}")
+        self.activation = activation
         self.width = int(width)
         self.inner = int(inner)
         self.gate_proj = Linear(width, inner)
@@ -45,6 +49,14 @@ class SwiGLU(FeedForward):
         self.gate_proj.weight, self.up_proj.weight = view[:, 0], view[:, 1]     # [blocks, group, width] views
 
     def forward(self, ctx, h: torch.Tensor, residual: torch.Tensor):
-        act = ops.gated_linear(h, self.gate_up.weight, self.inner, self.group, static_weight=True)
+        act = ops.gated_linear(h, self.gate_up.weight, self.inner, self.group, static_weight=True,
+                               activation=self.activation)
         self.down_proj.forward(act, residual=residual)
         return None
+
+
+class SwiGLU(GatedMLP):
+    """The gated feed-forward with SiLU, the reference's (model.rs:518-536)."""
+
+    def __init__(self, width: int, inner: int):
+        super().__init__(width, inner, "silu")

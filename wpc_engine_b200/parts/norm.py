@@ -6,7 +6,7 @@ from typing import Dict
 import torch
 
 from .. import ops
-from .base import Norm, ParamSpec
+from .base import HeadNorm, Norm, ParamSpec
 
 
 class RMSNorm(Norm):
@@ -28,3 +28,25 @@ class RMSNorm(Norm):
 
     def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:
         return ops.rmsnorm(x, self.gain, self.eps, ctx.act_dtype)
+
+
+class HeadRMSNorm(HeadNorm):
+    """The same norm over each head of a row (width head_dim, one gain vector for all heads):
+    the per-head norm of q and k between projection and rotation that the reference's layer
+    has as an option (wpc-runtime/src/model.rs:14-21, 447-462)."""
+
+    def __init__(self, head_dim: int, eps: float):
+        self.head_dim = int(head_dim)
+        self.eps = float(eps)
+        self.gain = None
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        return {"weight": ParamSpec((self.head_dim,), kind="vector", init="gain")}
+
+    def bind(self, tensors):
+        self.gain = tensors["weight"]
+
+    def forward_heads(self, ctx, x: torch.Tensor, n_heads: int, head_dim: int) -> None:
+        if head_dim != self.head_dim:
+            raise ValueError(f"this norm is {self.head_dim} wide, the heads are {head_dim}")
+        ops.head_rmsnorm_(x, n_heads, head_dim, self.gain, self.eps)

@@ -13,6 +13,7 @@ behaviour, weights.rs:153-173).
 """
 from __future__ import annotations
 
+import sys
 from typing import Dict, List
 
 import torch
@@ -96,9 +97,18 @@ def load_weights(model, folder: str, dtype: torch.dtype, device) -> None:
         wanted = model.wanted_tensors()
         check_names(wanted, files, ignored=model.ignored)
         tensors = {}
+        wide = []
         for name, (_, _, spec) in wanted.items():
             host = files.read(name)
-            tensors[name] = host.to(device=device, dtype=device_dtype(host.dtype, spec.kind, dtype)).contiguous()
+            kept = device_dtype(host.dtype, spec.kind, dtype)
+            if dtype == torch.bfloat16 and kept == torch.float32 and spec.kind in ("matrix", "table"):
+                wide.append(name)
+            tensors[name] = host.to(device=device, dtype=kept).contiguous()
     finally:
         files.close()
+    if wide:
+        # nothing is converted behind the user's back; the slow path is named once instead
+        print(f"[wpc_engine_b200] {len(wide)} matrices of {folder} are stored in 32 or 16-bit IEEE floats "
+              f"(first: {wide[0]}) and stay float32: their products run on the CUDA cores, not on the tensor "
+              "cores.  Store the checkpoint in bfloat16 for the fast path.", file=sys.stderr, flush=True)
     bind_model(model, tensors)

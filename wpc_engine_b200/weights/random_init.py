@@ -29,6 +29,15 @@ def _name_seed(seed: int, name: str) -> int:
     return (h ^ (seed * 0x9E3779B97F4A7C15)) & ((1 << 63) - 1)
 
 
+def _random_index(spec, seed: int, name: str) -> torch.Tensor:
+    """An integer table: int32 drawn evenly from 0 .. spec.high - 1 on the host (zeros without `high`)."""
+    if not spec.high:
+        return torch.zeros(spec.shape, dtype=torch.int32)
+    gen = torch.Generator(device="cpu")
+    gen.manual_seed(_name_seed(seed, name))
+    return torch.randint(0, int(spec.high), spec.shape, generator=gen, dtype=torch.int32)
+
+
 def write_random_model(folder: str, config, seed: int, dtype: torch.dtype = torch.bfloat16) -> str:
     """Writes config.json and model.safetensors for `config` (a registered architecture's
     configuration object); returns the folder."""
@@ -38,6 +47,9 @@ def write_random_model(folder: str, config, seed: int, dtype: torch.dtype = torc
     os.makedirs(folder, exist_ok=True)
     tensors = []
     for name, (_, _, spec) in model.wanted_tensors().items():
+        if spec.kind == "index":
+            tensors.append((name, _random_index(spec, seed, name)))
+            continue
         gen = torch.Generator(device="cpu")
         gen.manual_seed(_name_seed(seed, name))
         t = torch.randn(spec.shape, generator=gen, dtype=torch.float32) * STD
@@ -54,6 +66,9 @@ def random_weights_on_device(model, seed: int, dtype: torch.dtype, device) -> No
     """Fills the model's tensors on the device with the fill kernel (no file, no host copy)."""
     tensors: Dict[str, torch.Tensor] = {}
     for name, (_, _, spec) in model.wanted_tensors().items():
+        if spec.kind == "index":          # small tables of integers: drawn on the host
+            tensors[name] = _random_index(spec, seed, name).to(device)
+            continue
         t = torch.empty(spec.shape, dtype=device_dtype(dtype, spec.kind, dtype), device=device)
         ops.fill_normal(t, _name_seed(seed, name), 1.0 if spec.init == "gain" else 0.0, STD)
         tensors[name] = t
