@@ -641,10 +641,11 @@ def test_gated_linear_activations(T, inner, K, activation):
     got = ops.gated_linear(x, w, inner, group, activation=activation)
     want = ref.gated_linear(x.cpu(), w.cpu(), inner, group, activation=activation)
     mag = want.float().abs().max().item()
-    assert (got.cpu().float() - want.float()).abs().max().item() <= 1.5e-2 * mag
-    if activation == "gelu_tanh":
+    err = (got.cpu().float() - want.float()).abs().max().item()
+    assert err <= 1.5e-2 * mag
+    if activation == "gelu_tanh":          # the code is looked at: the other activation is much further away
         other = ref.gated_linear(x.cpu(), w.cpu(), inner, group, activation="silu")
-        assert (got.cpu().float() - other.float()).abs().max().item() > 3e-2 * mag      # the code is looked at
+        assert (got.cpu().float() - other.float()).abs().max().item() > 4 * max(err, 2e-3 * mag)
     for dtype in DTYPES:
         gu = rnd((9, 2 * inner), dtype, 153)
         close(ops.gate_mul(gu, inner, group, activation), ref.gate_mul(gu.cpu(), inner, group, activation).to(DEV), dtype)

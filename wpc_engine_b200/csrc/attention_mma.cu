@@ -278,17 +278,34 @@ decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* 
     const int* gtable = page_table + (size_t)b * table_width + blk0;
     const int n_seg = blk1 - blk0;
     for (int i = tid; i < min(n_seg, MAX_SEGMENT_PAGES); i += THREADS) s_pages[i] = gtable[i];
-    // Up to here only the step's lengths and page numbers were read, which the host wrote before
-    // the step's first kernel started.  Queries, keys and values come from the kernel ahead:
-    // nothing of them is read before it has finished (copying pages of earlier positions ahead
-    // of this wait gave wrong results under CUDA graphs, cause not found).
-    if (u == u0) pdl_wait();
-    __syncthreads();
+    __syncthreads();                                     // the page numbers are in shared memory for every thread
     auto page_of = [&](int blk) { const int i = blk - blk0; return i < MAX_SEGMENT_PAGES ? s_pages[i] : gtable[i]; };
 
-    // a ring of DECODE_STAGES pages: two are in flight while one is computed
+    // A ring of DECODE_STAGES pages: two are in flight while one is computed.  Up to here only
+    // the step's lengths and page numbers were read, which the host wrote before the step's
+    // first kernel started.  The queries come from the kernel ahead, and so do the key and the
+    // value of this step's token, which lie in the sequence's last page: those are read after
+    // the dependency wait.  Every earlier page holds positions of earlier steps only, finished
+    // long before this step began: a CTA's first segment fetches such pages while the kernel
+    // ahead is still running (one commit a stage, in order, so that the counting of the loop
+    // below holds whichever side of the wait a page was started on).
+    const int last_blk = pos / PAGE;
+    const bool early = u == u0;
+    int filled = 0;
+    if (early) {
 #pragma unroll
-    for (int i = 0; i < DECODE_STAGES - 1; ++i) {
+      for (; filled < DECODE_STAGES - 1; ++filled) {
+        if (blk0 + filled < blk1) {
+          if (blk0 + filled == last_blk) break;
+          const size_t src = (size_t)max(page_of(blk0 + filled), 0) * page_elems + (size_t)g * PAGE * HD;
+          load_page<HD>(ks + filled * Cfg<HD>::PAGE_ELEMS, k_pages + src, tid);
+          load_page<HD>(vs + filled * Cfg<HD>::PAGE_ELEMS, v_pages + src, tid);
+        }
+        cp_async_commit();
+      }
+      pdl_wait();
+    }
+    for (int i = filled; i < DECODE_STAGES - 1; ++i) {
       if (blk0 + i < blk1) {
         const size_t src = (size_t)max(page_of(blk0 + i), 0) * page_elems + (size_t)g * PAGE * HD;
         load_page<HD>(ks + i * Cfg<HD>::PAGE_ELEMS, k_pages + src, tid);
@@ -506,14 +523,25 @@ decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bf
   const int* gtable = page_table + (size_t)b * table_width + blk0;
   const int n_seg = blk1 - blk0;
   for (int i = tid; i < min(n_seg, CLUSTER_SEGMENT_PAGES); i += THREADS) s_pages[i] = gtable[i];
-  // Up to here only the step's lengths and page numbers were read, which the host wrote before
-  // the step's first kernel started.  Queries, keys and values come from the kernel ahead.
-  pdl_wait();
-  __syncthreads();
+  __syncthreads();                                       // the page numbers are in shared memory for every thread
   auto page_of = [&](int blk) { const int i = blk - blk0; return i < CLUSTER_SEGMENT_PAGES ? s_pages[i] : gtable[i]; };
 
+  // The first pages of the ring are started ahead of the dependency wait, except the sequence's
+  // last page, which holds the key and value that the kernel ahead writes (see decode_kernel).
+  const int last_blk = pos / PAGE;
+  int filled = 0;
 #pragma unroll
-  for (int i = 0; i < DECODE_STAGES - 1; ++i) {
+  for (; filled < DECODE_STAGES - 1; ++filled) {
+    if (blk0 + filled < blk1) {
+      if (blk0 + filled == last_blk) break;
+      const size_t src = (size_t)max(page_of(blk0 + filled), 0) * page_elems + (size_t)g * PAGE * HD;
+      load_page<HD>(ks + filled * Cfg<HD>::PAGE_ELEMS, k_pages + src, tid);
+      load_page<HD>(vs + filled * Cfg<HD>::PAGE_ELEMS, v_pages + src, tid);
+    }
+    cp_async_commit();
+  }
+  pdl_wait();
+  for (int i = filled; i < DECODE_STAGES - 1; ++i) {
     if (blk0 + i < blk1) {
       const size_t src = (size_t)max(page_of(blk0 + i), 0) * page_elems + (size_t)g * PAGE * HD;
       load_page<HD>(ks + i * Cfg<HD>::PAGE_ELEMS, k_pages + src, tid);
