@@ -63,6 +63,7 @@ int wpc_attention_plain(const void* q, int q_stride, void* out, int out_stride, 
                         cudaStream_t stream);
 
 int wpc_attention_mma_supports(int nh, int nkv, int hd);
+int wpc_attention_decode_early_pages(int on);
 int wpc_attention_decode(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                          const void* v_pages, const int* page_table, int table_width, const int* ctx_lens, int B,
                          int nh, int nkv, int hd, float scale, int window, int n_ctas, float* part_o, float* part_ml,

@@ -190,6 +190,11 @@ __device__ __forceinline__ void load_q(uint32_t (&qf)[HD / 16][4], const __nv_bf
 // part_o: [(CTAs + pairs), 16, HD] float32; part_ml: [(CTAs + pairs), 16, 2]; the partial of CTA
 // c for pair k lives at slot c + k (consecutive pairs share at most one CTA, so slots are unique).
 constexpr int MAX_DECODE_SEQS = 1024;
+// Whether the decode kernels start the copies of earlier pages ahead of their dependency wait.
+inline int& early_pages() {
+  static int on = 1;
+  return on;
+}
 // Pages in the ring of a decode CTA: 3 with two CTAs to an SM; 6 when there are so few CTAs that
 // each has an SM to itself (few sequences), so that all of a CTA's pages are on their way at once.
 constexpr int DECODE_STAGES_SHARED = 3;
@@ -202,7 +207,7 @@ decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* 
               const __nv_bfloat16* __restrict__ k_pages, const __nv_bfloat16* __restrict__ v_pages,
               const int* __restrict__ page_table, int table_width, const int* __restrict__ ctx_lens, int B,
               int nh, int nkv, float scale_log2, int window, float* __restrict__ part_o,
-              float* __restrict__ part_ml, int* __restrict__ counters, int smem_bytes) {
+              float* __restrict__ part_ml, int* __restrict__ counters, int smem_bytes, int early_pages) {
   pdl_trigger();
   extern __shared__ __align__(16) uint8_t smem_raw[];
   __nv_bfloat16* ks = (__nv_bfloat16*)smem_raw;                       // [DECODE_STAGES][PAGE][STRIDE]
@@ -290,11 +295,11 @@ decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* 
     // ahead is still running (one commit a stage, in order, so that the counting of the loop
     // below holds whichever side of the wait a page was started on).
     const int last_blk = pos / PAGE;
-    const bool early = u == u0;
+    const bool early = u == u0;          // (later segments of a CTA begin after the wait anyway)
     int filled = 0;
     if (early) {
 #pragma unroll
-      for (; filled < DECODE_STAGES - 1; ++filled) {
+      for (; early_pages && filled < DECODE_STAGES - 1; ++filled) {
         if (blk0 + filled < blk1) {
           if (blk0 + filled == last_blk) break;
           const size_t src = (size_t)max(page_of(blk0 + filled), 0) * page_elems + (size_t)g * PAGE * HD;
@@ -499,7 +504,7 @@ __global__ void __launch_bounds__(THREADS)
 decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* __restrict__ out, int out_stride,
                       const __nv_bfloat16* __restrict__ k_pages, const __nv_bfloat16* __restrict__ v_pages,
                       const int* __restrict__ page_table, int table_width, const int* __restrict__ ctx_lens, int B,
-                      int nh, int nkv, float scale_log2, int window, int C) {
+                      int nh, int nkv, float scale_log2, int window, int C, int early_pages) {
   pdl_trigger();
   extern __shared__ __align__(16) uint8_t smem_raw[];
   __nv_bfloat16* ks = (__nv_bfloat16*)smem_raw;                       // [DECODE_STAGES][PAGE][STRIDE]
@@ -531,7 +536,7 @@ decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bf
   const int last_blk = pos / PAGE;
   int filled = 0;
 #pragma unroll
-  for (; filled < DECODE_STAGES - 1; ++filled) {
+  for (; early_pages && filled < DECODE_STAGES - 1; ++filled) {
     if (blk0 + filled < blk1) {
       if (blk0 + filled == last_blk) break;
       const size_t src = (size_t)max(page_of(blk0 + filled), 0) * page_elems + (size_t)g * PAGE * HD;
@@ -797,7 +802,7 @@ static int launch_decode_stages(const void* q, int q_stride, void* out, int out_
   wpc::launch(decode_kernel<HD, STAGES>, dim3(n_ctas), THREADS, smem, stream, 
       (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pages,
       (const __nv_bfloat16*)v_pages, page_table, table_width, ctx_lens, B, nh, nkv, scale * LOG2E, window,
-      part_o, part_ml, counters, smem);
+      part_o, part_ml, counters, smem, early_pages());
   return launch_status();
 }
 
@@ -834,7 +839,7 @@ static int launch_decode_cluster_stages(const void* q, int q_stride, void* out, 
   wpc::launch_clusters(decode_cluster_kernel<HD, STAGES>, dim3((unsigned)(B * nkv * cluster)), THREADS, smem, stream,
                        (unsigned)cluster, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride,
                        (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, page_table, table_width, ctx_lens,
-                       B, nh, nkv, scale * LOG2E, window, cluster);
+                       B, nh, nkv, scale * LOG2E, window, cluster, early_pages());
   return launch_status();
 }
 
@@ -912,6 +917,14 @@ using namespace wpc;
   }
 
 extern "C" {
+
+// Decode attention copies pages of earlier positions before the kernel ahead has finished
+// (1, the default) or starts every copy after it (0); returns the old setting.
+int wpc_attention_decode_early_pages(int on) {
+  const int was = fa::early_pages();
+  fa::early_pages() = on ? 1 : 0;
+  return was;
+}
 
 // 1 if these sizes can take the tensor-core kernels, else 0 (the plain kernel takes them).
 int wpc_attention_mma_supports(int nh, int nkv, int hd) {

@@ -60,6 +60,12 @@ def set_pdl(on: bool) -> bool:
     return bool(library().wpc_set_pdl(int(bool(on))))
 
 
+def set_decode_early_pages(on: bool) -> bool:
+    """Whether decode attention starts copying the pages of earlier positions while the kernel
+    ahead of it still runs (on by default); returns the old setting."""
+    return bool(library().wpc_attention_decode_early_pages(int(bool(on))))
+
+
 def require_device(device="cuda") -> None:
     """Raises unless `device` is a CUDA device and the kernel library loads."""
     dev = torch.device(device)
@@ -328,7 +334,12 @@ PAIR_WIDTHS = (256,)      # tile widths that pair_tile_width may choose from (th
 
 
 def pair_tile_width(M: int, N: int) -> int:
-    """Columns of a pair's tile: the width whose tiles fill whole waves of the 74 pairs best."""
+    """Columns of a pair's tile: the width whose tiles fill whole waves of the pairs of SMs best.
+    Only 256 is offered: narrower tiles keep more pairs busy in a part-empty last wave, but a
+    pair takes in its operands at about 83 GB/s per SM whatever the width, so a wave of 160-wide
+    tiles costs 86 % of a wave of 256-wide ones for 62 % of the work (measured at 2,048 x 3,584:
+    one width of 256: 227 us for K = 18,944; 9 tile columns of 256 and then 8 of 160 as two
+    launches, both single full waves: 248 us)."""
     tiles_m = (M + 255) // 256
     best, best_cost = 256, None
     for pn in PAIR_WIDTHS:
