@@ -218,8 +218,8 @@ def prefill_run(engine, gen, lens, repeats=3, warm=2):
 
 def kernel_rates(engine, cfg, layers, batch, ctx, prefill_tokens, hbm_peak, tf_peak):
     """Each product and the attention of a decode step and of a prefill, alone: one launch on
-    every layer's weights in turn (together far larger than L2) between two CUDA events, three
-    passes, the median per launch.  Decode figures are GB/s of what the kernel must read,
+    every layer's weights in turn (together far larger than L2), replayed from a CUDA graph
+    between two CUDA events, three passes, the median per launch.  Decode figures are GB/s of what the kernel must read,
     prefill figures TFLOP/s; `frac` is the share of the measured peak."""
     import torch
     from wpc_engine_b200 import ops
@@ -233,16 +233,23 @@ def kernel_rates(engine, cfg, layers, batch, ctx, prefill_tokens, hbm_peak, tf_p
         return torch.randn(shape, generator=g).to(torch.bfloat16).to(dev)
 
     def timed(launch, n):
-        """Median microseconds per launch of `launch(layer)` over three passes of n layers."""
+        """Median microseconds per launch of `launch(layer)`: the n launches are captured into a
+        CUDA graph (so that the host's part of a call, tens of microseconds, is not in the
+        figure) and the graph is replayed three times between events."""
         for layer in range(n):
             launch(layer)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for layer in range(n):
+                launch(layer)
+        graph.replay()
         us = []
         for _ in range(3):
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             torch.cuda.synchronize()
             e0.record()
-            for layer in range(n):
-                launch(layer)
+            graph.replay()
             e1.record()
             torch.cuda.synchronize()
             us.append(e0.elapsed_time(e1) * 1e3 / n)

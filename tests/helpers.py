@@ -76,12 +76,19 @@ def run_batch(engine, requests, prompt_lens):
                 engine.close_sequence(s)
 
 
+def bfloat16_bound(want64):
+    """The largest error allowed to bfloat16 logits against the plain implementation in
+    float64, fixed here once for all tests: three times the largest error that the engine showed
+    on the tiny configurations (whole, tail one by one, batches, mixed steps: 0.21 of
+    0.03 std + 0.02 max when this was set), in units of the logits' spread and size."""
+    return 0.02 * want64.std() + 0.012 * np.abs(want64).max()
+
+
 def assert_close_to_plain(got, folder, tokens, dtype_name, what=""):
     """Compares engine logits [T, V] with the plain implementation in float64.
 
     float32: the error may be a few times the plain implementation's own float32 rounding
-    noise against float64.  bfloat16: a bound in units of the logits' spread, fixed here
-    once for all tests."""
+    noise against float64.  bfloat16: `bfloat16_bound`."""
     want64 = plain_logits(folder, tokens, np.float64)
     err = np.abs(got.astype(np.float64) - want64).max()
     if dtype_name == "float32":
@@ -89,6 +96,6 @@ def assert_close_to_plain(got, folder, tokens, dtype_name, what=""):
         noise = np.abs(want32.astype(np.float64) - want64).max()
         bound = 4 * noise + 1e-6
     else:
-        bound = 0.03 * want64.std() + 0.02 * np.abs(want64).max()
+        bound = bfloat16_bound(want64)
     assert err <= bound, f"{what}: max error {err:.3e} exceeds {bound:.3e}"
     return err

@@ -65,6 +65,33 @@ def test_linear(dtype, shape, mode):
         close(ops.linear(x, w, bias), ref.linear(x, w, bias), dtype)
 
 
+@pytest.mark.parametrize("M", [1, 2, 3, 5, 8, 9, 16, 17])
+@pytest.mark.parametrize("N,K", [(40, 24), (33, 1030), (130, 2056), (1000, 520), (7, 4100)])
+@pytest.mark.parametrize("dtypes", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
+                                    (torch.float32, torch.bfloat16), (torch.bfloat16, torch.float32)])
+def test_plain_linear_of_few_rows(M, N, K, dtypes):
+    """The float32 product for up to 16 rows streams the weights once (every count of rows on both
+    sides of 16, widths that are no multiples of 4 or of the chunk, rows that start unaligned),
+    with bias, into float32 or bfloat16 or added to a residual: against float64."""
+    xd, wd = dtypes
+    x, w = rnd((M, K + 3), xd, 14)[:, 3:], rnd((N, K), wd, 15, 0.1)          # x: a view whose rows are unaligned
+    bias = rnd((N,), seed=16)
+    want = (x.double().cpu() @ w.double().cpu().t() + bias.double().cpu())
+    mag = want.abs().max().item()
+    got = ops.linear_plain(x, w, bias, out_dtype=torch.float32)
+    assert (got.double().cpu() - want).abs().max().item() <= 3e-6 * mag * max(1.0, (K / 1000) ** 0.5)
+    xc = torch.empty((M, K), dtype=xd, device=DEV).copy_(x)          # the same rows, aligned
+    got16 = ops.linear_plain(xc, w, bias, out_dtype=torch.bfloat16)
+    assert (got16.double().cpu() - want).abs().max().item() <= 1e-2 * mag
+    r0 = rnd((M, N), seed=17)
+    acc = ops.linear_plain(xc, w, None, residual=r0.clone())
+    assert (acc.double().cpu() - (want - bias.double().cpu() + r0.double().cpu())).abs().max().item() <= 1e-5 * max(mag, 1.0)
+    # a row's result does not depend on the rows beside it (the same kernel and the same alignment)
+    alone = ops.linear_plain(xc[:1].clone(), w, bias, out_dtype=torch.float32)
+    if M <= 16:
+        assert torch.equal(alone[0], ops.linear_plain(xc, w, bias, out_dtype=torch.float32)[0])
+
+
 def test_linear_keeps_32_bit_weights_with_16_bit_rows():
     x, w = rnd((9, 48), torch.bfloat16, 8), rnd((20, 48), torch.float32, 9)
     close(ops.linear(x, w), ref.linear(x, w), torch.bfloat16)
@@ -148,6 +175,24 @@ def test_attention(dtype, nh, nkv, hd, window):
     close(got.cpu(), want, dtype)
     plain = ops.attention_plain(qkv, nh, nkv, hd, kp, vp, table, seq, pos, scale, window)
     close(plain.cpu(), want, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("splits", [2, 5, 40])
+@pytest.mark.parametrize("window", [None, 300])
+def test_attention_plain_with_shared_keys(dtype, splits, window):
+    """The plain kernel with the keys of a query divided among several blocks (more blocks than
+    keys for the short sequence): the same results as with one block to a query."""
+    nh, nkv, hd = 6, 2, 48
+    lens, new = [1300, 3, 700], [1, 1, 2]
+    qkv, kp, vp, table, seq, pos = paged_case(dtype, nh, nkv, hd, lens, new, seed=29)
+    one = ops.attention_plain(qkv, nh, nkv, hd, kp, vp, table, seq, pos, 0.15, window, splits=1)
+    many = ops.attention_plain(qkv, nh, nkv, hd, kp, vp, table, seq, pos, 0.15, window, splits=splits)
+    close(many, one, dtype)
+    auto = ops.attention_plain(qkv, nh, nkv, hd, kp, vp, table, seq, pos, 0.15, window, max_ctx_len=1300)
+    close(auto, one, dtype)
+    want = ref.attention_plain(qkv.cpu(), nh, nkv, hd, kp.cpu(), vp.cpu(), table.cpu(), seq.cpu(), pos.cpu(), 0.15, window)
+    close(many.cpu(), want, dtype)
 
 
 def test_attention_finds_one_far_key():

@@ -7,7 +7,7 @@ import pytest
 import torch
 
 from conftest import make_folder
-from helpers import assert_close_to_plain, random_tokens, run_batch, run_tail_one_by_one, run_whole
+from helpers import assert_close_to_plain, bfloat16_bound, random_tokens, run_batch, run_tail_one_by_one, run_whole
 from plain import qwen2_plain as P
 from wpc_engine_b200 import Engine, SequenceStep
 
@@ -121,7 +121,7 @@ def test_real_layer_shape_against_plain(real_shape, dtype):
 
     def check(got, i, what):
         err = np.abs(got.astype(np.float64) - want64[i]).max()
-        bound = 4 * noise[i] + 1e-6 if dtype == "float32" else 0.03 * want64[i].std() + 0.02 * np.abs(want64[i]).max()
+        bound = 4 * noise[i] + 1e-6 if dtype == "float32" else bfloat16_bound(want64[i])
         assert err <= bound, f"{what}: max error {err:.3e} exceeds {bound:.3e}"
 
     def wanted(i, lo, hi):       # places of request i inside tokens lo .. hi - 1, relative to lo
@@ -205,7 +205,7 @@ def test_more_sequences_than_ctas(tmp_path_factory, dtype, n_seqs):
                 noise = np.abs(P.forward(cfg, tensors, reqs[i], np.float32, rows=[lens[i] + k]).astype(np.float64) - want[k]).max()
                 bound = 4 * noise + 1e-6
             else:
-                bound = 0.03 * want.std() + 0.02 * np.abs(want).max()
+                bound = bfloat16_bound(want)
             assert err <= bound, (i, k, lens[i], err, bound)
 
 

@@ -10,7 +10,7 @@ import numpy as np
 import pytest
 
 from conftest import ROOT
-from helpers import plain_logits, random_tokens
+from helpers import bfloat16_bound, plain_logits, random_tokens
 
 pytestmark = pytest.mark.gpu
 TRACE_RUN = os.path.join(ROOT, "bin", "trace_run")
@@ -34,7 +34,7 @@ def bound(want64, dtype, folder, tokens):
     if dtype == "float32":
         want32 = plain_logits(folder, tokens, np.float32)
         return 4 * np.abs(want32 - want64).max() + 1e-6
-    return 0.03 * want64.std() + 0.02 * np.abs(want64).max()
+    return bfloat16_bound(want64)
 
 
 @pytest.mark.parametrize("name", ["A", "B", "C"])

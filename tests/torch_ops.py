@@ -147,7 +147,7 @@ def attention(q, n_heads, n_kv_heads, head_dim, k_pages, v_pages, page_table, cu
 
 
 def attention_plain(q, n_heads, n_kv_heads, head_dim, k_pages, v_pages, page_table, seq_of_token, positions,
-                    scale, window):
+                    scale, window, max_ctx_len=None, splits=None):
     T = q.shape[0]
     out = torch.zeros((T, n_heads * head_dim), dtype=torch.float32, device=q.device)
     n_rep = n_heads // n_kv_heads

@@ -60,7 +60,7 @@ int wpc_gemm_tc_rope_store(const void* w, int ldw, const void* x, int ldx, int t
 int wpc_attention_plain(const void* q, int q_stride, void* out, int out_stride, int dtype, const void* k_pages,
                         const void* v_pages, const int* page_table, int table_width, const int* seq_of_token,
                         const int* positions, int T, int nh, int nkv, int hd, float scale, int window,
-                        cudaStream_t stream);
+                        int n_splits, float* part, cudaStream_t stream);
 
 int wpc_attention_mma_supports(int nh, int nkv, int hd);
 int wpc_attention_decode_early_pages(int on);

@@ -1,7 +1,9 @@
 // Attention over the paged cache, the plain way: one block per (query token, query head),
 // any head size, any context length, float32 arithmetic with an online softmax over chunks
 // of keys.  It is the attention of the true 32-bit path and the plain twin of the fast
-// kernels (wpc-runtime/src/model.rs:476-510).
+// kernels (wpc-runtime/src/model.rs:476-510).  When the queries are few and their contexts
+// long (a decode step of the 32-bit path), the keys of a query are divided evenly among
+// several blocks, whose partial results a second kernel adds up in order.
 #include "api.h"
 #include "common.cuh"
 
@@ -16,7 +18,7 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
                        const T* __restrict__ k_pages, const T* __restrict__ v_pages,
                        const int* __restrict__ page_table, int table_width,
                        const int* __restrict__ seq_of_token, const int* __restrict__ positions,
-                       int nh, int nkv, int hd, float scale, int window) {
+                       int nh, int nkv, int hd, float scale, int window, float* __restrict__ part) {
   pdl_trigger();
   pdl_wait();
   extern __shared__ float smem[];
@@ -28,8 +30,11 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
   const int pos = positions[t];
   const int b = seq_of_token[t];
   const int* table = page_table + (size_t)b * table_width;
-  const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-  const int n_keys = pos - lo + 1;
+  // this block's share of the keys that the query sees (all of them with one block to a query)
+  const int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const int n_splits = gridDim.z, per = (pos - first + 1 + n_splits - 1) / n_splits;
+  const int lo = first + (int)blockIdx.z * per;
+  const int n_keys = max(min(pos + 1, lo + per) - lo, 0);
 
   const T* qrow = q + (size_t)t * q_stride + (size_t)h * hd;
   for (int d = threadIdx.x; d < hd; d += AP_THREADS) qs[d] = to_float(qrow[d]);
@@ -78,12 +83,48 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
     }
     __syncthreads();
   }
+  if (n_splits > 1) {
+    // unnormalised outputs, then the running maximum and sum: [token][head][split][hd + 2]
+    float* prow = part + (((size_t)t * nh + h) * n_splits + blockIdx.z) * (hd + 2);
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int d = threadIdx.x + u * AP_THREADS;
+      if (d < hd) prow[d] = acc[u];
+    }
+    if (threadIdx.x == 0) {
+      prow[hd] = m_run;
+      prow[hd + 1] = l_run;
+    }
+    return;
+  }
   T* orow = out + (size_t)t * out_stride + (size_t)h * hd;
   const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
 #pragma unroll
   for (int u = 0; u < 2; ++u) {
     const int d = threadIdx.x + u * AP_THREADS;
     if (d < hd) orow[d] = from_float<T>(acc[u] * inv);
+  }
+}
+
+// Adds up the partial results of a query's blocks, in block order.
+template <typename T>
+__global__ void attention_plain_combine_kernel(const float* __restrict__ part, T* __restrict__ out, int out_stride, int nh,
+                                               int hd, int n_splits) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x, h = blockIdx.y;
+  const float* prow = part + ((size_t)t * nh + h) * n_splits * (hd + 2);
+  float m = -INFINITY;
+  for (int z = 0; z < n_splits; ++z) m = fmaxf(m, prow[(size_t)z * (hd + 2) + hd]);
+  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+    float num = 0.f, den = 0.f;
+    for (int z = 0; z < n_splits; ++z) {
+      const float* pz = prow + (size_t)z * (hd + 2);
+      const float f = pz[hd] == -INFINITY ? 0.f : expf(pz[hd] - m);
+      num = fmaf(f, pz[d], num);
+      den = fmaf(f, pz[hd + 1], den);
+    }
+    out[(size_t)t * out_stride + (size_t)h * hd + d] = from_float<T>(den > 0.f ? num / den : 0.f);
   }
 }
 
@@ -94,14 +135,23 @@ using namespace wpc;
 extern "C" int wpc_attention_plain(const void* q, int q_stride, void* out, int out_stride, int dtype,
                                    const void* k_pages, const void* v_pages, const int* page_table,
                                    int table_width, const int* seq_of_token, const int* positions, int T, int nh,
-                                   int nkv, int hd, float scale, int window, cudaStream_t stream) {
+                                   int nkv, int hd, float scale, int window, int n_splits, float* part,
+                                   cudaStream_t stream) {
+  // n_splits > 1: that many blocks share the keys of each query; part: float32 scratch of
+  // T * nh * n_splits * (hd + 2) elements for their partial results
   if (T <= 0) return 0;
   if (hd < 1 || hd > 2 * AP_THREADS || nkv < 1 || nh % nkv) return WPC_ERR_UNSUPPORTED;
+  if (n_splits < 1 || n_splits > 65535 || (n_splits > 1 && !part)) return WPC_ERR_BAD_ARGUMENT;
   const size_t smem = (size_t)(hd + AP_CHUNK) * sizeof(float);
-  dim3 grid(T, nh);
+  dim3 grid(T, nh, n_splits);
   WPC_DISPATCH_DTYPE(dtype, Tt,
                      wpc::launch(attention_plain_kernel<Tt>, grid, AP_THREADS, smem, stream, 
                          (const Tt*)q, q_stride, (Tt*)out, out_stride, (const Tt*)k_pages, (const Tt*)v_pages,
-                         page_table, table_width, seq_of_token, positions, nh, nkv, hd, scale, window));
+                         page_table, table_width, seq_of_token, positions, nh, nkv, hd, scale, window, part));
+  int rc = launch_status();
+  if (rc || n_splits == 1) return rc;
+  WPC_DISPATCH_DTYPE(dtype, Tt,
+                     wpc::launch(attention_plain_combine_kernel<Tt>, dim3(T, nh), 128, 0, stream, (const float*)part,
+                                 (Tt*)out, out_stride, nh, hd, n_splits));
   return launch_status();
 }

@@ -595,7 +595,7 @@ def attention(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, k_p
     the others (or with `mma_only`).  Everything else runs the plain kernel."""
     if q.dtype != torch.bfloat16 or not library().wpc_attention_mma_supports(n_heads, n_kv_heads, head_dim):
         return attention_plain(q, n_heads, n_kv_heads, head_dim, k_pages, v_pages, page_table, seq_of_token,
-                               positions, scale, window)
+                               positions, scale, window, max_ctx_len)
     _rows(q, "q")
     _need(q.shape[1] >= n_heads * head_dim, "q is too narrow")
     _need(k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.dtype == q.dtype, "pages: wrong type")
@@ -734,16 +734,26 @@ def plan_decode_cluster(n_seqs: int, n_kv_heads: int, n_heads: int, head_dim: in
 
 
 def attention_plain(q, n_heads, n_kv_heads, head_dim, k_pages, v_pages, page_table, seq_of_token, positions,
-                    scale, window) -> torch.Tensor:
+                    scale, window, max_ctx_len: Optional[int] = None, splits: Optional[int] = None) -> torch.Tensor:
+    """The attention of the 32-bit path and the plain twin of the fast kernels: a block to each
+    (token, head).  With few tokens and long contexts (`max_ctx_len`, the longest sequence of
+    the step) several blocks share a query's keys, about 256 each and no more blocks than fill
+    the device twice (`splits` forces their number); their parts are added in order."""
     _rows(q, "q")
     _need(q.shape[1] >= n_heads * head_dim, "q is too narrow")
     _need(k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.dtype == q.dtype, "pages: wrong type")
     T = q.shape[0]
     out = torch.empty((T, n_heads * head_dim), dtype=q.dtype, device=q.device)
+    if splits is None:
+        keys = min(max_ctx_len or 0, window or (max_ctx_len or 0))
+        splits = max(1, min(keys // 256, 2 * sms() // max(T * n_heads, 1)))
+    part = None
+    if splits > 1:
+        part = torch.empty((T * n_heads * splits * (head_dim + 2),), dtype=torch.float32, device=q.device)
     _check("attention_plain", library().wpc_attention_plain(
         _p(q), q.stride(0), _p(out), out.stride(0), _code(q.dtype), _p(k_pages), _p(v_pages), _p(page_table),
         page_table.shape[1], _p(seq_of_token), _p(positions), T, n_heads, n_kv_heads, head_dim,
-        ctypes.c_float(scale), int(window or 0), _stream()))
+        ctypes.c_float(scale), int(window or 0), int(splits), _p(part), _stream()))
     return out
 
 
