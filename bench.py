@@ -416,6 +416,14 @@ def profile_case(args):
 
         python bench.py --case decode --layers 4 --batch 8 --context 4000 --steps 3
         python bench.py --case prefill --layers 4 --tokens 2048 --steps 2 [--shape 0.5b]
+
+    With --timeline (decode only) the steps are replayed from CUDA graphs as in generation, and
+    the kernels' start and end times come from torch.profiler: for every kernel name the
+    launches a step, the mean duration, and the mean time from the end of the kernel before it
+    to its own end, which is what it adds to the step (durations overlap: with programmatic
+    dependent launch a kernel is resident while the one before it still runs).
+
+        python bench.py --case decode --timeline --layers 28 --batch 8 --context 4000
     """
     import torch
     import wpc_engine_b200 as wpc
@@ -428,9 +436,11 @@ def profile_case(args):
     per_seq = (args.context + args.steps if decode else args.tokens) + 64
     batch = args.batch if decode else 1
     eng = wpc.Engine.from_random(cfg, 0, "bfloat16", "cuda:0", max_tokens=batch * (per_seq + 64),
-                                 max_sequences=batch + 1, use_graphs=False)
+                                 max_sequences=batch + 1, use_graphs=bool(args.timeline))
     fill_cache(eng)
     gen = torch.Generator().manual_seed(0)
+    if decode and args.timeline:
+        return timeline(eng, cfg, batch, args.context, gen)
     if decode:
         slots = [eng.open_sequence() for _ in range(batch)]
         for s in slots:
@@ -453,6 +463,46 @@ def profile_case(args):
     return 0
 
 
+def timeline(eng, cfg, batch, context, gen, steps=4):
+    import collections
+    import torch
+    import wpc_engine_b200 as wpc
+    from torch.profiler import ProfilerActivity, profile
+    slots = [eng.open_sequence() for _ in range(batch)]
+    for s in slots:
+        eng.cache.reserve(s, context)
+        eng.cache.commit(s, context)
+    eng.set_sampler_state(slots, 0, list(range(batch)))
+
+    def one():
+        toks = torch.randint(0, cfg.vocab_size, (batch,), generator=gen).tolist()
+        logits = eng.step([wpc.SequenceStep(s, [t], want=[0]) for s, t in zip(slots, toks)], borrow=True, check=False)
+        eng.sample(logits, slots, 0.0)
+    for _ in range(6):
+        one()
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(steps):
+            one()
+        torch.cuda.synchronize()
+    events = [e for e in prof.events() if e.device_type.name == "CUDA" and "emcpy" not in e.name and "emset" not in e.name]
+    events.sort(key=lambda e: e.time_range.start)
+    stat, last_end = collections.OrderedDict(), None
+    for e in events:
+        start, end = e.time_range.start, e.time_range.end
+        d = stat.setdefault(e.name.split("(")[0][-64:], [0, 0.0, 0.0])
+        d[0] += 1
+        d[1] += end - start
+        d[2] += max(end - last_end, 0) if last_end is not None else end - start
+        last_end = end if last_end is None else max(end, last_end)
+    total = sum(d[2] for d in stat.values())
+    print(f"batch {batch}, context {context}, {len(eng.model.blocks)} layers: {total / steps:.1f} us a step")
+    print("launches a step | mean duration us | adds us each | adds us a step | kernel")
+    for name, (n, dur, add) in stat.items():
+        print(f"{n / steps:8.1f} | {dur / n:8.2f} | {add / n:8.2f} | {add / steps:9.1f} | {name}")
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -467,6 +517,7 @@ def main():
     ap.add_argument("--batch", type=int, default=8, help="--case decode: sequences")
     ap.add_argument("--context", type=int, default=4000, help="--case decode: cached positions per sequence")
     ap.add_argument("--tokens", type=int, default=2048, help="--case prefill: prompt length")
+    ap.add_argument("--timeline", action="store_true", help="--case decode: kernel timeline of graph-replayed steps")
     args = ap.parse_args()
 
     if args.impl == "reference":

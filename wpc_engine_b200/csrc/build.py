@@ -106,7 +106,8 @@ def library_path(verbose: bool = True) -> str:
 
     done = 0
     with concurrent.futures.ThreadPoolExecutor(max_workers=min(8, max(1, len(stale)))) as pool:
-        for src in pool.map(compile_one, stale):
+        for fut in concurrent.futures.as_completed([pool.submit(compile_one, src) for src in stale]):
+            src = fut.result()                 # in the order in which the files finish: a line now and then
             done += 1
             if verbose:
                 _say(f"  {src} done ({done}/{len(stale)}, {time.time() - t0:.0f} s)")
