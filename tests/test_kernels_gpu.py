@@ -34,11 +34,15 @@ def test_embed(dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("width", [4, 72, 1000, 3584])
+@pytest.mark.parametrize("width", [4, 72, 1000, 3584, 18001])
 def test_rmsnorm(dtype, width):
     x = rnd((5, width), seed=2, scale=3.0)
     gain = 1 + rnd((width,), seed=3, scale=0.1)
     close(ops.rmsnorm(x, gain, 1e-5, dtype), ref.rmsnorm(x, gain, 1e-5, dtype), dtype)
+    # the rows whose logits are wanted, gathered and normed in one kernel
+    rows = torch.tensor([4, 0, 4, 2], dtype=torch.int32, device=DEV)
+    got = ops.rmsnorm(x, gain, 1e-5, dtype, rows=rows)
+    assert got.shape == (4, width) and torch.equal(got, ops.rmsnorm(x, gain, 1e-5, dtype)[rows.long()])
 
 
 def test_rmsnorm_anchor():

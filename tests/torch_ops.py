@@ -25,7 +25,9 @@ def embed(tokens, table):
     return table[tokens.long()].float()
 
 
-def rmsnorm(x, gain, eps, out_dtype):
+def rmsnorm(x, gain, eps, out_dtype, rows=None):
+    if rows is not None:
+        x = x[rows.long()]
     ms = (x * x).sum(-1, keepdim=True) / x.shape[-1]
     return (x * (1.0 / torch.sqrt(ms + eps)) * gain).to(out_dtype)
 

@@ -20,8 +20,9 @@ int wpc_set_wait_policy(unsigned long long limit_ns, int starve);
 
 int wpc_embed(const int* tokens, const void* table, int table_dtype, float* out, int T, int H, int V,
               cudaStream_t stream);
+// rows == null: out [T, H]; else out [n_rows, H], row i the norm of x[rows[i]]
 int wpc_rmsnorm(const float* x, const float* gain, float eps, void* out, int out_dtype, int T, int H,
-                cudaStream_t stream);
+                const int* rows, int n_rows, cudaStream_t stream);
 // out[t, i] = act(gate) * up; act: WPC_ACT_SILU (1) or WPC_ACT_GELU_TANH (2) of common.cuh
 int wpc_gate_mul(const void* gu, void* out, int dtype, int T, int I, int group, int act, cudaStream_t stream);
 int wpc_add(float* x, const void* y, int y_dtype, size_t n, cudaStream_t stream);

@@ -23,11 +23,13 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const Tw* __restric
 // ---- RMS norm: out = x * rsqrt(mean(x^2) + eps) * gain (wpc-runtime/src/norm.rs:4-13)
 template <typename To>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ gain,
-                               float eps, To* __restrict__ out, int H) {
+                               float eps, To* __restrict__ out, int H, const int* __restrict__ rows, int T) {
   pdl_trigger();
   pdl_wait();
   __shared__ float red[32];
-  const float* row = x + (size_t)blockIdx.x * H;
+  int src = rows ? rows[blockIdx.x] : (int)blockIdx.x;
+  if (src < 0 || src >= T) src = 0;
+  const float* row = x + (size_t)src * H;
   To* o = out + (size_t)blockIdx.x * H;
   float ss = 0.f;
   for (int i = threadIdx.x; i < H; i += blockDim.x) {
@@ -50,12 +52,16 @@ __device__ __forceinline__ void store4(__nv_bfloat16* o, float4 v) {
 
 // The same for widths that are multiples of 4 and at most 4 * VPT * blockDim: the row is read
 // once, 16 bytes at a time, and stays in registers between the sum and the scaling.
+// `rows` (or null): output row i is the norm of input row rows[i] (the rows whose logits are wanted),
+// which the host wrote before the step began; T: rows of x, to keep a bad index inside it.
 template <typename To, int VPT>
 __global__ void rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ gain,
-                                   float eps, To* __restrict__ out, int H) {
+                                   float eps, To* __restrict__ out, int H, const int* __restrict__ rows, int T) {
   pdl_trigger();
   __shared__ float red[32];
-  const float4* row = (const float4*)(x + (size_t)blockIdx.x * H);
+  int src = rows ? rows[blockIdx.x] : (int)blockIdx.x;
+  if (src < 0 || src >= T) src = 0;
+  const float4* row = (const float4*)(x + (size_t)src * H);
   const float4* g4 = (const float4*)gain;
   To* o = out + (size_t)blockIdx.x * H;
   const int n4 = H / 4;
@@ -328,19 +334,21 @@ int wpc_embed(const int* tokens, const void* table, int table_dtype, float* out,
   return launch_status();
 }
 
+// rows == null: out [T, H] = norm of x [T, H].  Else out [n_rows, H]: row i is the norm of x[rows[i]].
 int wpc_rmsnorm(const float* x, const float* gain, float eps, void* out, int out_dtype, int T, int H,
-                cudaStream_t stream) {
-  if (T <= 0) return 0;
+                const int* rows, int n_rows, cudaStream_t stream) {
+  const int n = rows ? n_rows : T;
+  if (n <= 0 || T <= 0) return 0;
   const bool aligned = H % 4 == 0 && (((uintptr_t)x | (uintptr_t)gain | (uintptr_t)out) & 15) == 0;
   if (aligned && H <= 1024) {
-    WPC_DISPATCH_DTYPE(out_dtype, To, (wpc::launch(rmsnorm_vec_kernel<To, 2>, T, 128, 0, stream, x, gain, eps, (To*)out, H)));
+    WPC_DISPATCH_DTYPE(out_dtype, To, (wpc::launch(rmsnorm_vec_kernel<To, 2>, n, 128, 0, stream, x, gain, eps, (To*)out, H, rows, T)));
   } else if (aligned && H <= 4096) {
-    WPC_DISPATCH_DTYPE(out_dtype, To, (wpc::launch(rmsnorm_vec_kernel<To, 4>, T, 256, 0, stream, x, gain, eps, (To*)out, H)));
+    WPC_DISPATCH_DTYPE(out_dtype, To, (wpc::launch(rmsnorm_vec_kernel<To, 4>, n, 256, 0, stream, x, gain, eps, (To*)out, H, rows, T)));
   } else if (aligned && H <= 16384) {
-    WPC_DISPATCH_DTYPE(out_dtype, To, (wpc::launch(rmsnorm_vec_kernel<To, 8>, T, 512, 0, stream, x, gain, eps, (To*)out, H)));
+    WPC_DISPATCH_DTYPE(out_dtype, To, (wpc::launch(rmsnorm_vec_kernel<To, 8>, n, 512, 0, stream, x, gain, eps, (To*)out, H, rows, T)));
   } else {
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
-    WPC_DISPATCH_DTYPE(out_dtype, To, (wpc::launch(rmsnorm_kernel<To>, T, threads, 0, stream, x, gain, eps, (To*)out, H)));
+    WPC_DISPATCH_DTYPE(out_dtype, To, (wpc::launch(rmsnorm_kernel<To>, n, threads, 0, stream, x, gain, eps, (To*)out, H, rows, T)));
   }
   return launch_status();
 }

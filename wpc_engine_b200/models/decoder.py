@@ -10,7 +10,6 @@ from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 
-from .. import ops
 from ..cache import KVGroup, KVView, SequenceCache, StateGroup, StateView
 from ..parts.base import Block, Norm, Part, all_graph_safe, collect_params
 from ..parts.embedding import Embedding, OutputHead
@@ -115,6 +114,5 @@ class DecoderModel:
             self.blocks[run.layer].forward(ctx, x, view)
         if ctx.want_rows.numel() == 0:
             return None
-        rows = ops.gather_rows(x, ctx.want_rows)
-        h = self.final_norm.forward(ctx, rows)
+        h = self.final_norm.forward_rows(ctx, x, ctx.want_rows)
         return self.head.forward(ctx, h)

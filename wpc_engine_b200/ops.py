@@ -126,13 +126,19 @@ def embed(tokens: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def rmsnorm(x: torch.Tensor, gain: torch.Tensor, eps: float, out_dtype: torch.dtype) -> torch.Tensor:
-    """x * rsqrt(mean(x^2) + eps) * gain per row; x and gain float32."""
+def rmsnorm(x: torch.Tensor, gain: torch.Tensor, eps: float, out_dtype: torch.dtype,
+            rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x * rsqrt(mean(x^2) + eps) * gain per row; x and gain float32.  With `rows` (int32 [n]) only
+    the rows x[rows[i]] are normed, into [n, width]: the gather and the norm in one kernel."""
     _need(x.dtype == torch.float32 and x.is_contiguous() and x.dim() == 2, "x must be contiguous float32 [T, width]")
     _need(gain.dtype == torch.float32 and gain.numel() == x.shape[1], "gain must be float32 [width]")
-    out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    n = x.shape[0]
+    if rows is not None:
+        _need(rows.dtype == torch.int32 and rows.is_contiguous(), "rows must be contiguous int32")
+        n = rows.numel()
+    out = torch.empty((n, x.shape[1]), dtype=out_dtype, device=x.device)
     _check("rmsnorm", library().wpc_rmsnorm(_p(x), _p(gain), ctypes.c_float(eps), _p(out), _code(out_dtype),
-                                            x.shape[0], x.shape[1], _stream()))
+                                            x.shape[0], x.shape[1], _p(rows), n, _stream()))
     return out
 
 

@@ -10,7 +10,8 @@ What each kind of part must offer:
 * every part: `param_specs()` (the tensors it wants, by local name, with shapes) and
   `bind(tensors)` (receives them on the device; may re-lay them out, bit-exactly).
 * `Norm`:               `forward(ctx, x)`: x is the float32 residual stream [T, width];
-                         returns the normed rows in the activation dtype.
+                         returns the normed rows in the activation dtype.  Optional:
+                         `forward_rows(ctx, x, rows)`, the same for the rows x[rows] only.
 * `HeadNorm`:           `forward_heads(ctx, x, n_heads, head_dim)`: norms each of the first
                          n_heads heads of every row of x (activation dtype) in place.
 * `PositionEncoding`:    `pairing` names which two elements of a head are rotated together:
@@ -97,6 +98,12 @@ class Part:
 class Norm(Part):
     def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
+
+    def forward_rows(self, ctx, x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
+        """The norm of the rows x[rows] only (the places whose logits are wanted); a norm may
+        override this to gather and norm in one kernel."""
+        from .. import ops
+        return self.forward(ctx, ops.gather_rows(x, rows))
 
 
 class HeadNorm(Part):

@@ -29,6 +29,9 @@ class RMSNorm(Norm):
     def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:
         return ops.rmsnorm(x, self.gain, self.eps, ctx.act_dtype)
 
+    def forward_rows(self, ctx, x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
+        return ops.rmsnorm(x, self.gain, self.eps, ctx.act_dtype, rows=rows)
+
 
 class HeadRMSNorm(HeadNorm):
     """The same norm over each head of a row (width head_dim, one gain vector for all heads):
