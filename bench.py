@@ -435,7 +435,7 @@ def profile_case(args):
     decode = args.case == "decode"
     per_seq = (args.context + args.steps if decode else args.tokens) + 64
     batch = args.batch if decode else 1
-    eng = wpc.Engine.from_random(cfg, 0, "bfloat16", "cuda:0", max_tokens=batch * (per_seq + 64),
+    eng = wpc.Engine.from_random(cfg, 0, args.dtype, "cuda:0", max_tokens=batch * (per_seq + 64),
                                  max_sequences=batch + 1, use_graphs=bool(args.timeline))
     fill_cache(eng)
     gen = torch.Generator().manual_seed(0)
@@ -517,6 +517,7 @@ def main():
     ap.add_argument("--batch", type=int, default=8, help="--case decode: sequences")
     ap.add_argument("--context", type=int, default=4000, help="--case decode: cached positions per sequence")
     ap.add_argument("--tokens", type=int, default=2048, help="--case prefill: prompt length")
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"], help="--case: the path to run")
     ap.add_argument("--timeline", action="store_true", help="--case decode: kernel timeline of graph-replayed steps")
     args = ap.parse_args()
 

@@ -10,6 +10,14 @@
 namespace wpc {
 
 constexpr int AP_THREADS = 128;
+
+// four consecutive elements of a key row as floats (the row starts 16-byte aligned when hd is a multiple of 4)
+__device__ __forceinline__ float4 load4(const float* p) { return *(const float4*)p; }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
+  const uint2 t = *(const uint2*)p;
+  const float2 a = __bfloat1622float2(*(const __nv_bfloat162*)&t.x), b = __bfloat1622float2(*(const __nv_bfloat162*)&t.y);
+  return make_float4(a.x, a.y, b.x, b.y);
+}
 constexpr int AP_CHUNK = 512;        // keys per chunk; their scores live in shared memory
 
 template <typename T>
@@ -51,7 +59,17 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
       const int page = table[p / WPC_PAGE];
       const T* kr = k_pages + (((size_t)page * nkv + kvh) * WPC_PAGE + p % WPC_PAGE) * hd;
       float dot = 0.f;
-      for (int d = 0; d < hd; ++d) dot = fmaf(qs[d], to_float(kr[d]), dot);
+      if ((hd & 3) == 0) {                              // the same order of additions, four elements a load
+        for (int d = 0; d < hd; d += 4) {
+          const float4 kv = load4(kr + d);
+          dot = fmaf(qs[d], kv.x, dot);
+          dot = fmaf(qs[d + 1], kv.y, dot);
+          dot = fmaf(qs[d + 2], kv.z, dot);
+          dot = fmaf(qs[d + 3], kv.w, dot);
+        }
+      } else {
+        for (int d = 0; d < hd; ++d) dot = fmaf(qs[d], to_float(kr[d]), dot);
+      }
       dot *= scale;
       ps[j] = dot;
       m_loc = fmaxf(m_loc, dot);
@@ -73,10 +91,12 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
       const int d = threadIdx.x + u * AP_THREADS;
       if (d < hd) {
         float a = acc[u] * corr;
-        for (int j = 0; j < cn; ++j) {
+        for (int j = 0; j < cn;) {                       // page by page: one look-up for up to 64 keys
           const int p = lo + c0 + j;
-          const int page = table[p / WPC_PAGE];
-          a = fmaf(ps[j], to_float(v_pages[(((size_t)page * nkv + kvh) * WPC_PAGE + p % WPC_PAGE) * hd + d]), a);
+          const int in_page = p % WPC_PAGE, n = min(cn - j, WPC_PAGE - in_page);
+          const T* vr = v_pages + (((size_t)table[p / WPC_PAGE] * nkv + kvh) * WPC_PAGE + in_page) * hd + d;
+          for (int i = 0; i < n; ++i) a = fmaf(ps[j + i], to_float(vr[(size_t)i * hd]), a);
+          j += n;
         }
         acc[u] = a;
       }

@@ -76,13 +76,13 @@ gemm_simt_kernel(const Ta* __restrict__ A, int lda, const Tw* __restrict__ W, in
 
 // ---- few rows (tokens): a product that streams the weights once ----------------------------------
 // With up to 16 rows of A the tile kernel above would spend a 64 x 64 tile on them and read the
-// weights through shared memory at a fraction of the memory bandwidth.  Here a block of eight
-// warps takes 32 features; a warp takes four of them and walks their weight rows with 16-byte
-// loads, each lane its own elements of k, all rows of A against them; the rows of A pass through
+// weights through shared memory at a fraction of the memory bandwidth.  Here a warp takes FPW
+// features (four, or one when the features are so few that blocks of 32 features would leave
+// SMs idle) and walks their weight rows with 16-byte loads, each lane its own elements of k, all rows of A against them; the rows of A pass through
 // shared memory in chunks of k that the eight warps share.  A lane adds its elements in ascending
 // k, then the 32 lanes are added in a fixed tree: float32 multiply-add only, the same order for a
 // row whatever the other rows are.
-constexpr int GV_WARPS = 8, GV_FPW = 4;
+constexpr int GV_WARPS = 8;
 // k elements of every row of A in shared memory at a time (32 KiB at most)
 __host__ __device__ constexpr int gv_chunk(int mt) { return mt <= 8 ? 1024 : 512; }
 
@@ -103,7 +103,7 @@ template <> struct Vec4<__nv_bfloat16> {
 
 // MT: rows of A handled at once (1, 2, 4, 8 or 16; M <= MT).  VEC: K and both row strides are
 // multiples of 4 elements and both bases 16-byte aligned, so that four elements load at once.
-template <typename Ta, typename Tw, typename To, int MODE, int MT, bool VEC>
+template <typename Ta, typename Tw, typename To, int MODE, int MT, bool VEC, int GV_FPW>
 __global__ void __launch_bounds__(GV_WARPS * 32)
 gemv_simt_kernel(const Ta* __restrict__ A, int lda, const Tw* __restrict__ W, int ldw, const float* __restrict__ bias,
                  To* __restrict__ C, int ldc, int M, int N, int K) {
@@ -130,6 +130,7 @@ gemv_simt_kernel(const Ta* __restrict__ A, int lda, const Tw* __restrict__ W, in
     }
     __syncthreads();
     if (VEC) {
+#pragma unroll(GV_FPW == 1 ? 4 : 2)
       for (int k = lane * 4; k < kc; k += 128) {
         float w[GV_FPW][4];
 #pragma unroll
@@ -183,10 +184,19 @@ template <typename Ta, typename Tw, typename To, int MODE>
 static void launch_gemv_rows(const void* A, int lda, const void* W, int ldw, const float* bias, void* C, int ldc, int M,
                              int N, int K, cudaStream_t stream) {
   const bool vec = K % 4 == 0 && lda % 4 == 0 && ldw % 4 == 0 && (((uintptr_t)A | (uintptr_t)W) & 15) == 0;
-  const unsigned grid = (unsigned)((N + GV_WARPS * GV_FPW - 1) / (GV_WARPS * GV_FPW));
+  // four features to a warp unless that leaves fewer than two blocks to an SM
+  const bool wide = (N + GV_WARPS * 4 - 1) / (GV_WARPS * 4) >= 2 * sm_count();
+  const int fpw = wide ? 4 : 1;
+  const unsigned grid = (unsigned)((N + GV_WARPS * fpw - 1) / (GV_WARPS * fpw));
 #define WPC_GEMV(MT_, VEC_)                                                                                        \
-  wpc::launch(gemv_simt_kernel<Ta, Tw, To, MODE, MT_, VEC_>, grid, GV_WARPS * 32, 0, stream, (const Ta*)A, lda,     \
-              (const Tw*)W, ldw, bias, (To*)C, ldc, M, N, K)
+  do {                                                                                                             \
+    if (wide)                                                                                                      \
+      wpc::launch(gemv_simt_kernel<Ta, Tw, To, MODE, MT_, VEC_, 4>, grid, GV_WARPS * 32, 0, stream, (const Ta*)A,  \
+                  lda, (const Tw*)W, ldw, bias, (To*)C, ldc, M, N, K);                                             \
+    else                                                                                                           \
+      wpc::launch(gemv_simt_kernel<Ta, Tw, To, MODE, MT_, VEC_, 1>, grid, GV_WARPS * 32, 0, stream, (const Ta*)A,  \
+                  lda, (const Tw*)W, ldw, bias, (To*)C, ldc, M, N, K);                                             \
+  } while (0)
   if (vec) {
     if (M <= 1) WPC_GEMV(1, true); else if (M <= 2) WPC_GEMV(2, true); else if (M <= 4) WPC_GEMV(4, true);
     else if (M <= 8) WPC_GEMV(8, true); else WPC_GEMV(16, true);
