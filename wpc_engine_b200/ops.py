@@ -364,6 +364,13 @@ def _tensor_core_linear(x, w, bias, out, accumulate, static_weight=False) -> boo
     if K % 8 or x.stride(0) % 8 or w.stride(0) % 8 or x.data_ptr() % 16 or w.data_ptr() % 16:
         return False
     swap, bn, splits = plan_tensor_core_linear(M, N, K)
+    if not swap and not accumulate:
+        # Many tokens and an output that is written, not added to: K stays whole.  The slices of a
+        # split product of this arrangement meet through scratch memory and tickets, which costs
+        # far more than the idle SMs of few tiles (q/k/v of the 7B shape at 130 to 512 tokens:
+        # 57 to 93 us split in 2 to 4, 25 to 27 us whole); slices that add into a float32 output
+        # with red.add are the cheaper ones there (o_proj 26 against 36 us, down 50 against 110 us).
+        splits = 1
     cluster = bool(swap and CLUSTER_SPLITS and 2 <= splits <= 8)
     if cluster and accumulate and M <= RED_MAX_TOKENS and (K + 63) // 64 <= RED_MAX_K_BLOCKS:
         # few tokens, few tiles, added into float32: the slices add their shares with red.add
@@ -563,7 +570,7 @@ def linear_qk_rope_kv_store(x: torch.Tensor, w: torch.Tensor, bias: Optional[tor
             and w.data_ptr() % 16 == 0 and x.stride(1) == 1 and w.stride(1) == 1):
         swap, bn, splits = plan_tensor_core_linear(M, N, K)
         few = swap and CLUSTER_SPLITS and 2 <= splits <= 8                  # the cluster variant's tail
-        many = (not swap) and splits == 1 and head_dim >= 64 and pair_tiles(M, N, swap, bn)   # the pair kernel's epilogue
+        many = (not swap) and head_dim >= 64 and pair_tiles(M, N, swap, bn)   # the pair kernel's epilogue (K whole: see _tensor_core_linear)
         if few or many:
             if many:
                 bn = 256
