@@ -567,6 +567,26 @@ def test_pair_tiles(M, N, K, width, monkeypatch):
     assert ops.device_status() == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(256, 3584, 3584), (512, 3584, 18944), (400, 1000, 2056), (2048, 896, 4864), (256, 300, 520)])
+def test_pair_tiles_with_slices_of_k(M, N, K, monkeypatch):
+    """Few tiles whose result is added into float32: slices of K on pairs of SMs add their shares
+    with vector reductions; with and without bias, sizes that leave partial tiles and a last
+    slice that is shorter."""
+    assert ops.pair_tiles(M, N, False, 256)
+    splits = ops.pair_splits(M, N, K)
+    x, w = rnd((M, K), torch.bfloat16, 101), rnd((N, K), torch.bfloat16, 102, 0.05)
+    bias = rnd((N,), seed=103)
+    r0 = rnd((M, N), seed=104)
+    want = ops.linear_plain(x, w, bias, residual=r0.clone())
+    mag = max(want.abs().max().item(), 1.0)
+    got = ops.linear(x, w, bias, residual=r0.clone())
+    assert (got - want).abs().max().item() <= 2e-3 * mag, splits
+    monkeypatch.setattr(ops, "PAIR_SPLIT_K", False)
+    other = ops.linear(x, w, bias, residual=r0.clone())
+    assert (other - want).abs().max().item() <= 2e-3 * mag
+    assert ops.device_status() == 0
+
+
 def test_pair_tiles_find_one_element(monkeypatch):
     """A single one in x picks one column of w exactly, for rows in either CTA of a pair and
     features in either half of the tile (each CTA holds half of the weight rows)."""

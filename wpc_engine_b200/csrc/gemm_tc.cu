@@ -909,6 +909,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 //   * tensor memory is allocated and freed by one warp of each CTA with cta_group::2.
 // Cluster barriers (hardware, reached by every thread on every path) stand after the set-up
 // and before the exit; every mbarrier wait is bounded as in the kernel above.
+// With few tiles and a float32 output that is added to (p.splits > 1), a pair's unit of work is a
+// slice of a tile's K; every slice adds its share with red.global.add.v4 (the last bits of the sum
+// then depend on the order of arrival).
 constexpr int PAIR_STAGES = 6;
 constexpr int PAIR_STAGE_BYTES = 2 * BM * BK * 2;       // this CTA's halves of A and B: 16 KiB each
 constexpr int PAIR_SMEM = 1024 + 1024 + PAIR_STAGES * PAIR_STAGE_BYTES;
@@ -938,6 +941,9 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
+__device__ __forceinline__ void red_add_f32x4(float* dst, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t* holder, int cols) {
   asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(holder)), "r"(cols)
                : "memory");
@@ -965,6 +971,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   const int PN = p.pair_n;                                // columns of the tile; each CTA holds PN / 2 rows of B
   const int tiles_m = (p.M + 2 * BM - 1) / (2 * BM);
   const int n_tiles = tiles_m * ((p.N + PN - 1) / PN);
+  // units of work: (tile, slice of K), the slices of a tile side by side
+  const int S = p.splits, kb_per = (p.k_blocks + S - 1) / S;
+  const int n_units = n_tiles * S;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < PAIR_STAGES; ++s) {
@@ -990,18 +999,20 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       pdl_wait();
       int it = 0;
       bool ok = true;
-      for (int t = pair; ok && t < n_tiles; t += n_pairs) {
+      for (int u = pair; ok && u < n_units; u += n_pairs) {
+        const int t = u / S, slice = u - t * S;
         const int tile_n = t / tiles_m, tile_m = t - tile_n * tiles_m;
         const int m0 = tile_m * 2 * BM + (int)rank * BM, n0 = tile_n * PN + (int)rank * (PN >> 1);
-        for (int i = 0; i < p.k_blocks; ++i, ++it) {
+        const int kb0 = slice * kb_per, n_kb = max(min(p.k_blocks, kb0 + kb_per) - kb0, 0);
+        for (int i = 0; i < n_kb; ++i, ++it) {
           const int s = it % PAIR_STAGES;
           const uint32_t ph = (it / PAIR_STAGES) & 1;
           if (!mbar_wait(empty + s, ph ^ 1, p.wait_ns)) { atomicExch(flags, 1); ok = false; break; }
           if (rank == 0) mbar_expect_tx(full + s, 2 * (BM * BK * 2 + (PN >> 1) * BK * 2));
           const uint32_t leader_bar = peer_smem(smem_u32(full + s), 0);
           uint8_t* dst = tiles + s * PAIR_STAGE_BYTES;
-          tma_load_2d_pair(dst, &map_a, i * BK, m0, leader_bar);
-          tma_load_2d_pair(dst + BM * BK * 2, &map_b, i * BK, n0, leader_bar);
+          tma_load_2d_pair(dst, &map_a, (kb0 + i) * BK, m0, leader_bar);
+          tma_load_2d_pair(dst + BM * BK * 2, &map_b, (kb0 + i) * BK, n0, leader_bar);
         }
       }
     }
@@ -1012,12 +1023,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                              ((uint32_t)((2 * BM) >> 4) << 24);
       int it = 0, j = 0;
       bool ok = true;
-      for (int t = pair; ok && t < n_tiles; t += n_pairs, ++j) {
+      for (int u = pair; ok && u < n_units; u += n_pairs, ++j) {
+        const int slice = u % S;
+        const int kb0 = slice * kb_per, n_kb = max(min(p.k_blocks, kb0 + kb_per) - kb0, 0);
         const int b = j & 1, use = j >> 1;
         if (!mbar_wait(accum_empty + b, (use & 1) ^ 1, p.wait_ns)) { atomicExch(flags, 1); break; }
         fence_after_sync();
         const uint32_t tmem_d = tmem_base + b * PAIR_N;
-        for (int i = 0; i < p.k_blocks; ++i, ++it) {
+        for (int i = 0; i < n_kb; ++i, ++it) {
           const int s = it % PAIR_STAGES;
           const uint32_t ph = (it / PAIR_STAGES) & 1;
           if (!mbar_wait(full + s, ph, p.wait_ns)) { atomicExch(flags, 1); ok = false; break; }
@@ -1037,16 +1050,18 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const int q = warp & 3;
     const int r = q * 32 + lane;
     int j = 0;
-    for (int t = pair; t < n_tiles; t += n_pairs, ++j) {
+    for (int u = pair; u < n_units; u += n_pairs, ++j) {
+      const int t = u / S, slice = u - t * S;
       const int tile_n = t / tiles_m, tile_m = t - tile_n * tiles_m;
       const int m0 = tile_m * 2 * BM + (int)rank * BM, n0 = tile_n * PN;
+      const int n_kb = max(min(p.k_blocks, (slice + 1) * kb_per) - slice * kb_per, 0);
       const int b = j & 1, use = j >> 1;
       bool ok = mbar_wait(accum_full + b, use & 1, p.wait_ns);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) atomicExch(flags, 1);
       fence_after_sync();
       const int n_valid = min(PN, p.N - n0);
-      const bool have_acc = p.k_blocks > 0 && ok;
+      const bool have_acc = n_kb > 0 && ok;
       const uint32_t lane_addr = tmem_base + b * PAIR_N + ((uint32_t)(q * 32) << 16);
       const int row = m0 + r;
       if (ok && p.gated) {
@@ -1137,6 +1152,31 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 *(uint4*)(dst + half + pb + jj) = ob;
               }
             }
+          }
+        }
+      } else if (ok && S > 1) {
+        // a slice of K: its share is added to the float32 output, 16 bytes a reduction (the bias
+        // comes with the first slice)
+        for (int c = 0; c < n_valid && have_acc; c += 32) {
+          const int nc = min(32, n_valid - c);
+          uint32_t uu[32];
+          tmem_ld32(lane_addr + c, uu);
+          tmem_ld_wait();
+          if (row >= p.M) continue;
+          float* dst = (float*)p.out + (size_t)row * p.ldc + n0 + c;
+          const bool with_bias = p.bias && slice == 0;
+          if (nc == 32 && (((uintptr_t)dst) & 15) == 0) {
+#pragma unroll
+            for (int jj = 0; jj < 32; jj += 4) {
+              float a4[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) a4[e] = __uint_as_float(uu[jj + e]) + (with_bias ? p.bias[n0 + c + jj + e] : 0.f);
+              red_add_f32x4(dst + jj, a4[0], a4[1], a4[2], a4[3]);
+            }
+          } else {
+#pragma unroll
+            for (int jj = 0; jj < 32; ++jj)
+              if (jj < nc) atomicAdd(dst + jj, __uint_as_float(uu[jj]) + (with_bias ? p.bias[n0 + c + jj] : 0.f));
           }
         }
       } else if (ok) {
@@ -1306,7 +1346,8 @@ static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, Params& p, 
   p.wait_ns = wait_policy().limit_ns;
   p.starve = wait_policy().starve;
   const long max_pairs = sm_count() / 2;
-  const long n_tiles = (long)((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + p.pair_n - 1) / p.pair_n);
+  if (p.splits < 1) p.splits = 1;
+  const long n_tiles = (long)((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + p.pair_n - 1) / p.pair_n) * p.splits;
   if (n_tiles > 0x3fffffffL) return WPC_ERR_TOO_LARGE;
   const unsigned pairs = (unsigned)(n_tiles < max_pairs ? n_tiles : max_pairs);
   p.stages = PAIR_STAGES;
@@ -1346,7 +1387,8 @@ int wpc_gemm_tc_workspace(int rows_a, int rows_b, int bn, int splits, size_t* sc
 // [tokens, features / 2] bfloat16 = act(gate) * up.  Needs no bias, no split except in clusters, and bn >= 128 in the normal arrangement.
 // tall = 1 (no split; normal arrangement with bn 256, or swapped with bn 128): tiles of 256 rows
 // of a on one SM, see the kernel;
-// tall = 2: 256 x bn tiles on pairs of SMs (gemm_pair_kernel), bn 128..256 in steps of 16.
+// tall = 2: 256 x bn tiles on pairs of SMs (gemm_pair_kernel), bn 128..256 in steps of 16; with
+// accumulate (and no gate) splits > 1 cuts K into that many slices, which add with red.add.
 // prefetch_weights = 1 promises that the weights are not written by earlier work still in
 // flight on the stream (model parameters): their first tiles are then fetched before the
 // preceding kernel has finished.
@@ -1357,7 +1399,10 @@ int wpc_gemm_tc(const void* a, int lda, int rows_a, const void* b, int ldb, int 
   if (rows_a <= 0 || rows_b <= 0) return 0;
   if (cluster && (!swap || splits < 2 || splits > 8)) return WPC_ERR_UNSUPPORTED;
   if (tall && swap && (tall != 1 || splits > 1 || cluster || bn != 128)) return WPC_ERR_UNSUPPORTED;
-  if (tall && !swap && (splits > 1 || tall > 2 || (tall == 1 && bn != 256))) return WPC_ERR_UNSUPPORTED;
+  // (pair tiles may split K when the result is added to a float32 output and nothing else is done to it)
+  if (tall && !swap && (tall > 2 || (tall == 1 && (bn != 256 || splits > 1)) ||
+                        (tall == 2 && splits > 1 && (!accumulate || gated))))
+    return WPC_ERR_UNSUPPORTED;
   if (tall == 2 && (bn < 128 || bn > 256 || bn % 16 || (gated && bn % 128))) return WPC_ERR_UNSUPPORTED;
   if (K <= 0 || (lda % 8) || (ldb % 8) || (((uintptr_t)a) & 15) || (((uintptr_t)b) & 15)) return WPC_ERR_UNSUPPORTED;
   if (accumulate && out_dtype != WPC_DTYPE_F32) return WPC_ERR_BAD_ARGUMENT;
