@@ -327,13 +327,17 @@ def tall_tiles(M: int, N: int, swap: bool, bn: int, splits: int, K: int = 0, acc
     return 256 if sms() // 2 <= tiles <= sms() else 0
 
 
-def pair_tiles(M: int, N: int, swap: bool, bn: int) -> bool:
+def pair_tiles(M: int, N: int, swap: bool, bn: int, padded: bool = True) -> bool:
     """Whether the product runs in 256-row tiles on pairs of SMs (tcgen05 cta_group::2, each SM
-    fetches a third less per flop than with 128 x 256 tiles of its own): many tokens, wide
-    output, and a token count that 256-row tiles do not pad much further than 128-row tiles
-    (measured at the 7B shape: 2,048 tokens 26.9 against 28.2 ms, 8,192 tokens 119.5 against
-    130 ms, 300 tokens 9.4 against 8.6 ms)."""
-    return bool(PAIR_TILES and not swap and bn == 256 and M >= 256 and (M % 256 == 0 or M % 256 > 128))
+    fetches a third less per flop than with 128 x 256 tiles of its own): more than 128 tokens
+    and a wide output.  `padded` False (the gated product, by far the largest of a layer):
+    only token counts that 256-row tiles do not pad much further than 128-row tiles.  Measured
+    at the 7B shape, pair tiles against 128-row tiles: 300 tokens o_proj 18.7 against 28.4 us,
+    down 54 against 66, q/k/v 33.0 against 35.6, but gate/up 132 against 99 us; 1,030 tokens
+    q/k/v 52 against 63 us, down 126 against 136, gate/up 242 against 240."""
+    if not (PAIR_TILES and not swap and bn == 256 and M > 128):
+        return False
+    return bool(padded or (M >= 256 and (M % 256 == 0 or M % 256 > 128)))
 
 
 PAIR_WIDTHS = (256,)      # tile widths that pair_tile_width may choose from (the kernel takes 128..256 in steps of 16)
@@ -459,7 +463,7 @@ def gated_linear(x: torch.Tensor, w: torch.Tensor, inner: int, group: int, plain
         swap = M <= 128
         bn = (16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128) if swap else (256 if (2 * inner) % 256 == 0 else 128)
         tall = tall_tiles(M, 2 * inner, swap, bn, 1) == 256      # the gated epilogue needs whole 128-column groups
-        if pair_tiles(M, 2 * inner, swap, bn):
+        if pair_tiles(M, 2 * inner, swap, bn, padded=False):
             tall = 2
         if swap and bn == 128 and (2 * inner) % 256 == 0:
             # 65..128 tokens: every SM takes in the token tile once for 256 weight rows instead of
