@@ -743,7 +743,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
                   const float g = have_acc ? __uint_as_float(ug[j]) : 0.f, u = have_acc ? __uint_as_float(uu[j]) : 0.f;
-                  v[j] = gate_act<false, ACT>(g) * u;
+                  v[j] = gate_act<true, ACT>(g) * u;
                 }
               });
               if (row < p.M) store_row32(p, row, (n0 + c) / 2 + 32 * k, 32, v);
@@ -1076,11 +1076,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
               tmem_ld32(lane_addr + c + 64 + 32 * k, uu);
               tmem_ld_wait();
             }
+            // (SiLU's quotient by __fdividef, as in the epilogues for few tokens: the result
+            // becomes bfloat16 at once, and the exact division has a slow path, a branch an element)
             WPC_WITH_ACT(p.gated, ACT, {
 #pragma unroll
               for (int jj = 0; jj < 32; ++jj) {
                 const float g = have_acc ? __uint_as_float(ug[jj]) : 0.f, u = have_acc ? __uint_as_float(uu[jj]) : 0.f;
-                v[jj] = gate_act<false, ACT>(g) * u;
+                v[jj] = gate_act<true, ACT>(g) * u;
               }
             });
             if (row < p.M && c < n_valid) store_row32(p, row, (n0 + c) / 2 + 32 * k, 32, v);
@@ -1154,9 +1156,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             }
           }
         }
-      } else if (ok && S > 1) {
-        // a slice of K: its share is added to the float32 output, 16 bytes a reduction (the bias
-        // comes with the first slice)
+      } else if (ok && (S > 1 || p.accumulate)) {
+        // Added to the float32 output, 16 bytes a reduction (the bias comes with the first slice
+        // of K).  Also when K is whole: a reduction needs no answer, where loading the old
+        // values, adding and storing is a round trip to L2 for each of the eight chunks of a row
+        // (about 19 us for a tile's epilogue, measured; each element still gets exactly one
+        // addition, so the result is the same bits every run).
         for (int c = 0; c < n_valid && have_acc; c += 32) {
           const int nc = min(32, n_valid - c);
           uint32_t uu[32];
