@@ -334,26 +334,29 @@ def test_attention_decode_splits(nh, nkv, hd, window, splits):
 
 @pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 16), (3, 1, 32), (4, 2, 48), (14, 2, 64), (28, 4, 128), (8, 1, 128), (2, 2, 80)])
 @pytest.mark.parametrize("window", [None, 100])
-@pytest.mark.parametrize("cluster", [2, 3, 8, 16])
-def test_attention_decode_clusters(nh, nkv, hd, window, cluster):
-    """A cluster of CTAs to each (sequence, kv head) pair: ranks without pages (a sequence of one
-    page among eight ranks), shares that do not divide, every length at once."""
+@pytest.mark.parametrize("cluster,groups", [(2, 1), (3, 1), (8, 1), (16, 1), (4, 3), (2, 5), (8, 2)])
+def test_attention_decode_clusters(nh, nkv, hd, window, cluster, groups):
+    """Clusters of CTAs to each (sequence, kv head) pair, one or several (groups): ranks and whole
+    groups without pages (a sequence of one page among eight ranks), shares that do not divide,
+    every length at once."""
     lens, new = [1, 64, 65, 700, 333, 128, 1000], [1] * 7
     qkv, kp, vp, table, seq, pos = paged_case(torch.bfloat16, nh, nkv, hd, lens, new, seed=19)
     cu = torch.arange(8, dtype=torch.int32, device=DEV)
     ctx = torch.tensor(lens, dtype=torch.int32, device=DEV)
     scale = 1.0 / math.sqrt(hd)
-    got = ops.attention(qkv, nh, nkv, hd, kp, vp, table, cu, ctx, seq, pos, scale, window, 1, max(lens), cluster=cluster)
-    again = ops.attention(qkv, nh, nkv, hd, kp, vp, table, cu, ctx, seq, pos, scale, window, 1, max(lens), cluster=cluster)
+    how = dict(cluster=cluster, groups=groups)
+    got = ops.attention(qkv, nh, nkv, hd, kp, vp, table, cu, ctx, seq, pos, scale, window, 1, max(lens), **how)
+    again = ops.attention(qkv, nh, nkv, hd, kp, vp, table, cu, ctx, seq, pos, scale, window, 1, max(lens), **how)
     want = ref.attention_plain(qkv.cpu(), nh, nkv, hd, kp.cpu(), vp.cpu(), table.cpu(), seq.cpu(), pos.cpu(),
                                scale, window)
     close(got.cpu(), want, torch.bfloat16)
-    assert torch.equal(got, again)              # ranks are added in order: the same bits every run
+    assert torch.equal(got, again)              # ranks and groups are added in order: the same bits every run
 
 
-def test_attention_decode_cluster_finds_one_far_key():
-    """One key among thousands is made to stand out; whichever rank holds its page, the output is
-    that key's value."""
+@pytest.mark.parametrize("cluster,groups", [(8, 1), (8, 4), (5, 3)])
+def test_attention_decode_cluster_finds_one_far_key(cluster, groups):
+    """One key among thousands is made to stand out; whichever rank of whichever group holds its
+    page, the output is that key's value."""
     nh, nkv, hd = 28, 4, 128
     lens = [4000, 3000]
     qkv, kp, vp, table, seq, pos = paged_case(torch.bfloat16, nh, nkv, hd, lens, [1, 1], seed=23)
@@ -368,7 +371,8 @@ def test_attention_decode_cluster_finds_one_far_key():
         q2 = qkv.clone()
         q2[:, : nh * hd] = 0
         q2[:, 0 : nh * hd : hd] = 40.0                      # every head asks for element 0
-        got = ops.attention(q2, nh, nkv, hd, kp2, vp, table, cu, ctx, seq, pos, 1.0, None, 1, max(lens), cluster=8)
+        got = ops.attention(q2, nh, nkv, hd, kp2, vp, table, cu, ctx, seq, pos, 1.0, None, 1, max(lens),
+                            cluster=cluster, groups=groups)
         for b in range(2):
             page = int(table[b, far // 64])
             want = vp[page, :, far % 64, :].float()            # [nkv, hd]

@@ -32,21 +32,24 @@ def test_decode_ctas_fit_the_device():
 
 def test_decode_clusters_only_where_all_run_at_once(capacity):
     # 32 pairs of 64 pages: clusters of 8 would need 32 of the 33 that fit; 7 leave room
-    assert ops.plan_decode_cluster(8, 4, 28, 128, 4096, None) == 7
+    assert ops.plan_decode_cluster(8, 4, 28, 128, 4096, None) == (7, 1)
     # one sequence: 4 pairs, as many ranks as a cluster can have
-    assert ops.plan_decode_cluster(1, 4, 28, 128, 4096, None) == 16
+    assert ops.plan_decode_cluster(1, 4, 28, 128, 4096, None) == (16, 1)
+    # one long sequence: several clusters to a pair, on all SMs
+    c, g = ops.plan_decode_cluster(1, 4, 28, 128, 32768, None)
+    assert g > 1 and 148 < 4 * c * g <= 296
     # too many pairs, too wide a group, or switched off: the fixed grid
-    assert ops.plan_decode_cluster(64, 4, 28, 128, 4096, None) == 0
-    assert ops.plan_decode_cluster(8, 1, 16, 128, 4096, None) == 0
+    assert ops.plan_decode_cluster(64, 4, 28, 128, 4096, None) == (0, 1)
+    assert ops.plan_decode_cluster(8, 1, 16, 128, 4096, None) == (0, 1)
     for seqs in range(1, 40):
-        for ctx in (1, 64, 65, 1000, 4096, 20000):
-            c = ops.plan_decode_cluster(seqs, 4, 28, 128, ctx, None)
+        for ctx in (1, 64, 65, 1000, 4096, 20000, 100000):
+            c, g = ops.plan_decode_cluster(seqs, 4, 28, 128, ctx, None)
             if c:
-                pairs, alone = seqs * 4, seqs * 4 * c <= 148
-                assert 2 <= c <= 16 and c <= (ctx + 63) // 64
-                assert pairs * 1.1 <= CAPACITY[(128, alone)][c - 2]
+                pairs, alone = seqs * 4, seqs * 4 * c * g <= 148
+                assert 2 <= c <= 16 and 1 <= g and c * g <= (ctx + 63) // 64 and pairs * c * g <= 296
+                assert pairs * g * 1.1 <= CAPACITY[(128, alone)][c - 2]
 
 
 def test_decode_clusters_can_be_switched_off(capacity, monkeypatch):
     monkeypatch.setattr(ops, "CLUSTER_DECODE", False)
-    assert ops.plan_decode_cluster(8, 4, 28, 128, 4096, None) == 0
+    assert ops.plan_decode_cluster(8, 4, 28, 128, 4096, None) == (0, 1)

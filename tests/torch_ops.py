@@ -143,7 +143,7 @@ def linear_qk_rope_kv_store(x, w, bias, n_heads, n_kv_heads, head_dim, cos, sin,
 
 def attention(q, n_heads, n_kv_heads, head_dim, k_pages, v_pages, page_table, cu_seqlens, ctx_lens,
               seq_of_token, positions, scale, window, max_new_tokens, max_ctx_len, splits=None, mma_only=False,
-              cluster=None):
+              cluster=None, groups=1):
     return attention_plain(q, n_heads, n_kv_heads, head_dim, k_pages, v_pages, page_table, seq_of_token,
                            positions, scale, window)
 

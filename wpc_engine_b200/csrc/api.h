@@ -72,7 +72,8 @@ int wpc_attention_decode(const void* q, int q_stride, void* out, int out_stride,
 int wpc_attention_decode_cluster_capacity(int hd, int cluster, int alone);
 int wpc_attention_decode_cluster(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                                  const void* v_pages, const int* page_table, int table_width, const int* ctx_lens,
-                                 int B, int nh, int nkv, int hd, float scale, int window, int cluster,
+                                 int B, int nh, int nkv, int hd, float scale, int window, int cluster, int groups,
+                                 float* part_o, float* part_ml, int* counters, int n_counters,
                                  cudaStream_t stream);
 int wpc_attention_prefill(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                           const void* v_pages, const int* page_table, int table_width, const int* cu_seqlens,

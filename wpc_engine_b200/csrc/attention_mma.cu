@@ -495,8 +495,12 @@ decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* 
 // into rank r''s shared memory, and its running maxima and sums into every rank's; one
 // cluster barrier makes them visible, and every rank then normalises and writes its share of
 // the output, adding the ranks in order.  No scratch, no tickets, no second pass.
+// One long sequence alone leaves most SMs without work even with 16 ranks: then G clusters (groups)
+// share a pair's pages, every group leaves its unnormalised sums and its maxima in global
+// scratch (a few KB), and the cluster of the pair that takes the last ticket adds the G parts in order.
 constexpr int CLUSTER_DECODE_MAX_OUT = 1024;      // n_rep * HD that the receive buffer takes
 constexpr int CLUSTER_DECODE_MAX_RANKS = 16;      // beyond 8 a cluster needs the kernel's consent (see the launch)
+constexpr int CLUSTER_DECODE_MAX_GROUPS = 16;     // clusters that share a pair's pages
 constexpr int CLUSTER_SEGMENT_PAGES = 256;        // page numbers of a rank's share kept in shared memory
 
 template <int HD, int DECODE_STAGES>
@@ -504,11 +508,13 @@ __global__ void __launch_bounds__(THREADS)
 decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* __restrict__ out, int out_stride,
                       const __nv_bfloat16* __restrict__ k_pages, const __nv_bfloat16* __restrict__ v_pages,
                       const int* __restrict__ page_table, int table_width, const int* __restrict__ ctx_lens, int B,
-                      int nh, int nkv, float scale_log2, int window, int C, int early_pages) {
+                      int nh, int nkv, float scale_log2, int window, int C, int early_pages, int G,
+                      float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters) {
   pdl_trigger();
   extern __shared__ __align__(16) uint8_t smem_raw[];
   __nv_bfloat16* ks = (__nv_bfloat16*)smem_raw;                       // [DECODE_STAGES][PAGE][STRIDE]
   __nv_bfloat16* vs = ks + DECODE_STAGES * Cfg<HD>::PAGE_ELEMS;
+  __shared__ int s_last;
   __shared__ int s_pages[CLUSTER_SEGMENT_PAGES];                      // page numbers of this rank's share
   __shared__ __align__(16) float s_recv_o[CLUSTER_DECODE_MAX_OUT + 4 * CLUSTER_DECODE_MAX_RANKS];   // [rank][element of this rank's share]
   __shared__ __align__(8) float s_recv_ml[CLUSTER_DECODE_MAX_RANKS * 16 * 2];      // [rank][row][maximum, sum]
@@ -516,15 +522,17 @@ decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bf
   const int n_rep = nh / nkv;
   const size_t page_elems = (size_t)nkv * PAGE * HD;
   const int rank = (int)cluster_rank();
-  const int pair = blockIdx.x / C, b = pair / nkv, g = pair - b * nkv;
+  const int cl = blockIdx.x / C, pair = cl / G, grp = cl - pair * G, b = pair / nkv, g = pair - b * nkv;
   cluster_sync_all();                       // every rank runs: its shared memory may be written
 
   const int L = ctx_lens[b];
   const int pos = L - 1;
   const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
   const int nb = pos >= 0 ? pos / PAGE - lo / PAGE + 1 : 0;           // pages that the query sees
-  const int base = nb / C, extra = nb - base * C;                     // the first `extra` ranks take a page more
-  const int blk0 = lo / PAGE + rank * base + min(rank, extra), blk1 = blk0 + base + (rank < extra ? 1 : 0);
+  const int g_base = nb / G, g_extra = nb - g_base * G;               // the first groups take a page more,
+  const int g_blk0 = lo / PAGE + grp * g_base + min(grp, g_extra), g_nb = g_base + (grp < g_extra ? 1 : 0);
+  const int base = g_nb / C, extra = g_nb - base * C;                 // and so do the first ranks of a group
+  const int blk0 = g_blk0 + rank * base + min(rank, extra), blk1 = blk0 + base + (rank < extra ? 1 : 0);
   const int* gtable = page_table + (size_t)b * table_width + blk0;
   const int n_seg = blk1 - blk0;
   for (int i = tid; i < min(n_seg, CLUSTER_SEGMENT_PAGES); i += THREADS) s_pages[i] = gtable[i];
@@ -648,6 +656,8 @@ decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bf
   }
   cluster_arrive();
   cluster_wait();                            // every rank's results for this rank's share have arrived
+  float* const group_o = part_o + (size_t)(pair * G + grp) * n_out;
+  float* const group_ml = part_ml + (size_t)(pair * G + grp) * 32;
   for (int t = tid; t < share; t += THREADS) {
     const int e = rank * share + t;
     if (e < n_out) {
@@ -661,6 +671,60 @@ decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bf
         num += f * s_recv_o[c * share + t];
         den += f * s_recv_ml[(c * 16 + row) * 2 + 1];
       }
+      if (G == 1) {
+        out[(size_t)b * out_stride + (size_t)(g * n_rep + row) * HD + d] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+      } else {
+        group_o[e] = num;
+        if (d == 0) *(float2*)(group_ml + row * 2) = make_float2(M, den);
+      }
+    }
+  }
+  if (G == 1) return;
+  // ---- several groups to the pair: the cluster that finishes last adds the groups' parts ----
+  // Every thread fences its part; after a cluster barrier rank 0 takes the pair's ticket and
+  // tells every rank whether this cluster is the last; if so each rank adds, for its share of
+  // the elements, the G parts in group order (all loads of a thread in flight at once).
+  __threadfence();
+  cluster_arrive();
+  cluster_wait();
+  if (rank == 0 && tid == 0) {
+    __threadfence();
+    const int ticket = atomicAdd(counters + pair, 1);
+    const int last = ticket == G - 1;
+    if (last) counters[pair] = 0;            // zero again for the next launch
+    __threadfence();
+    const uint32_t flag = smem_u32(&s_last);
+    for (int c = 0; c < C; ++c) st_peer_b32(peer_smem(flag, (uint32_t)c), (uint32_t)last);
+  }
+  cluster_arrive();
+  cluster_wait();
+  if (!s_last) return;
+  const float* const pair_o = part_o + (size_t)pair * G * n_out;
+  const float* const pair_ml = part_ml + (size_t)pair * G * 32;
+  for (int t = tid; t < share; t += THREADS) {
+    const int e = rank * share + t;
+    if (e < n_out) {
+      const int row = e / HD, d = e - row * HD;
+      float2 ml[CLUSTER_DECODE_MAX_GROUPS];
+      float po[CLUSTER_DECODE_MAX_GROUPS];
+#pragma unroll
+      for (int c = 0; c < CLUSTER_DECODE_MAX_GROUPS; ++c)
+        if (c < G) {
+          ml[c] = __ldcg((const float2*)(pair_ml + c * 32 + row * 2));
+          po[c] = __ldcg(pair_o + (size_t)c * n_out + e);
+        }
+      float M = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < CLUSTER_DECODE_MAX_GROUPS; ++c)
+        if (c < G) M = fmaxf(M, ml[c].x);
+      float num = 0.f, den = 0.f;
+#pragma unroll
+      for (int c = 0; c < CLUSTER_DECODE_MAX_GROUPS; ++c)             // in group order
+        if (c < G) {
+          const float f = (ml[c].x == -INFINITY) ? 0.f : exp2f(ml[c].x - M);
+          num += f * po[c];
+          den += f * ml[c].y;
+        }
       out[(size_t)b * out_stride + (size_t)(g * n_rep + row) * HD + d] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
     }
   }
@@ -812,7 +876,7 @@ static int launch_decode(const void* q, int q_stride, void* out, int out_stride,
                          int nh, int nkv, float scale, int window, int n_ctas, float* part_o, float* part_ml,
                          int* counters, cudaStream_t stream) {
   // with at most a CTA to an SM the ring takes all the shared memory it can use
-  if (n_ctas <= 148 && DECODE_STAGES_ALONE * 2 * Cfg<HD>::PAGE_ELEMS * 2 <= 220 * 1024)
+  if (n_ctas <= sm_count() && DECODE_STAGES_ALONE * 2 * Cfg<HD>::PAGE_ELEMS * 2 <= 220 * 1024)
     return launch_decode_stages<HD, DECODE_STAGES_ALONE>(q, q_stride, out, out_stride, k_pages, v_pages, page_table,
                                                          table_width, ctx_lens, B, nh, nkv, scale, window, n_ctas,
                                                          part_o, part_ml, counters, stream);
@@ -825,7 +889,8 @@ template <int HD, int STAGES>
 static int launch_decode_cluster_stages(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                                         const void* v_pages, const int* page_table, int table_width,
                                         const int* ctx_lens, int B, int nh, int nkv, float scale, int window,
-                                        int cluster, cudaStream_t stream) {
+                                        int cluster, int groups, float* part_o, float* part_ml, int* counters,
+                                        cudaStream_t stream) {
   const int merge_bytes = (4 * 16 * HD + 2 * 4 * 16) * (int)sizeof(float);
   int smem = STAGES * 2 * Cfg<HD>::PAGE_ELEMS * 2;
   if (merge_bytes > smem) smem = merge_bytes;
@@ -836,24 +901,27 @@ static int launch_decode_cluster_stages(const void* q, int q_stride, void* out, 
     if (e != cudaSuccess) return (int)e;
     if (int rc = allow_smem(decode_cluster_kernel<HD, STAGES>, smem, configured)) return rc;
   }
-  wpc::launch_clusters(decode_cluster_kernel<HD, STAGES>, dim3((unsigned)(B * nkv * cluster)), THREADS, smem, stream,
-                       (unsigned)cluster, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride,
+  wpc::launch_clusters(decode_cluster_kernel<HD, STAGES>, dim3((unsigned)(B * nkv * groups * cluster)), THREADS, smem,
+                       stream, (unsigned)cluster, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride,
                        (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, page_table, table_width, ctx_lens,
-                       B, nh, nkv, scale * LOG2E, window, cluster, early_pages());
+                       B, nh, nkv, scale * LOG2E, window, cluster, early_pages(), groups, part_o, part_ml, counters);
   return launch_status();
 }
 
 template <int HD>
 static int launch_decode_cluster(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                                  const void* v_pages, const int* page_table, int table_width, const int* ctx_lens,
-                                 int B, int nh, int nkv, float scale, int window, int cluster, cudaStream_t stream) {
-  if (B * nkv * cluster <= 148 && DECODE_STAGES_ALONE * 2 * Cfg<HD>::PAGE_ELEMS * 2 <= 215 * 1024)
+                                 int B, int nh, int nkv, float scale, int window, int cluster, int groups,
+                                 float* part_o, float* part_ml, int* counters, cudaStream_t stream) {
+  if (B * nkv * groups * cluster <= sm_count() && DECODE_STAGES_ALONE * 2 * Cfg<HD>::PAGE_ELEMS * 2 <= 215 * 1024)
     return launch_decode_cluster_stages<HD, DECODE_STAGES_ALONE>(q, q_stride, out, out_stride, k_pages, v_pages,
                                                                  page_table, table_width, ctx_lens, B, nh, nkv, scale,
-                                                                 window, cluster, stream);
+                                                                 window, cluster, groups, part_o, part_ml, counters,
+                                                                 stream);
   return launch_decode_cluster_stages<HD, DECODE_STAGES_SHARED>(q, q_stride, out, out_stride, k_pages, v_pages,
                                                                 page_table, table_width, ctx_lens, B, nh, nkv, scale,
-                                                                window, cluster, stream);
+                                                                window, cluster, groups, part_o, part_ml, counters,
+                                                                stream);
 }
 
 // How many clusters of `cluster` CTAs of the cluster decode kernel the device holds at once, by
@@ -951,18 +1019,26 @@ int wpc_attention_decode(const void* q, int q_stride, void* out, int out_stride,
 
 // The same with a thread-block cluster of `cluster` CTAs (2..16) to each (sequence, kv head) pair,
 // which share the pair's pages and add up through one another's shared memory; for few pairs
-// of about equal lengths.  Needs (nh / nkv) * hd <= 1024 and at most 1024 CTAs.
+// of about equal lengths.  Needs (nh / nkv) * hd <= 1024 and at most 1024 CTAs.  With groups > 1
+// that many clusters share a pair's pages through part_o (float32 [B * nkv * groups * (nh / nkv)
+// * hd]), part_ml (float32 [B * nkv * groups * 32]) and B * nkv tickets that are zero between
+// launches.
 int wpc_attention_decode_cluster(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                                  const void* v_pages, const int* page_table, int table_width, const int* ctx_lens,
-                                 int B, int nh, int nkv, int hd, float scale, int window, int cluster,
+                                 int B, int nh, int nkv, int hd, float scale, int window, int cluster, int groups,
+                                 float* part_o, float* part_ml, int* counters, int n_counters,
                                  cudaStream_t stream) {
   if (B <= 0) return 0;
   if (!wpc_attention_mma_supports(nh, nkv, hd) || (q_stride % 2) || (out_stride % 2) ||
       (nh / nkv) * hd > fa::CLUSTER_DECODE_MAX_OUT)
     return WPC_ERR_UNSUPPORTED;
-  if (cluster < 2 || cluster > fa::CLUSTER_DECODE_MAX_RANKS || (long)B * nkv * cluster > 1024) return WPC_ERR_BAD_ARGUMENT;
+  if (cluster < 2 || cluster > fa::CLUSTER_DECODE_MAX_RANKS || groups < 1 ||
+      groups > fa::CLUSTER_DECODE_MAX_GROUPS || (long)B * nkv * cluster * groups > 1024)
+    return WPC_ERR_BAD_ARGUMENT;
+  if (groups > 1 && (!part_o || !part_ml || !counters || B * nkv > n_counters)) return WPC_ERR_BAD_ARGUMENT;
   WPC_DISPATCH_HD(hd, fa::launch_decode_cluster<HD>(q, q_stride, out, out_stride, k_pages, v_pages, page_table,
-                                                   table_width, ctx_lens, B, nh, nkv, scale, window, cluster, stream));
+                                                   table_width, ctx_lens, B, nh, nkv, scale, window, cluster, groups,
+                                                   part_o, part_ml, counters, stream));
 }
 
 // Clusters of `cluster` CTAs of the cluster decode kernel that run at once: with the short ring

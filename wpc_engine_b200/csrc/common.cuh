@@ -114,6 +114,9 @@ __device__ __forceinline__ uint32_t peer_smem(uint32_t addr, uint32_t rank) {
 }
 // (a peer may be written once it runs: after a cluster barrier at the start of the kernel; every
 // store is a packet between two SMs, so the wide forms are the ones to use)
+__device__ __forceinline__ void st_peer_b32(uint32_t addr, uint32_t v) {
+  asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
 __device__ __forceinline__ void st_peer_f32x2(uint32_t addr, float a, float b) {
   asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(addr), "f"(a), "f"(b) : "memory");
 }

@@ -19,9 +19,6 @@ __device__ __forceinline__ bool is_banned(int i, const int* banned, int n_banned
     if (banned[j] == i) return true;
   return false;
 }
-__device__ __forceinline__ void st_peer_b32(uint32_t addr, uint32_t v) {
-  asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
-}
 
 // seq_state rows: [position, seed, request number, tokens drawn]
 __global__ void __launch_bounds__(SP_THREADS)

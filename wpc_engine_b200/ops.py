@@ -617,13 +617,13 @@ def attention(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, k_p
               v_pages: torch.Tensor, page_table: torch.Tensor, cu_seqlens: torch.Tensor, ctx_lens: torch.Tensor,
               seq_of_token: torch.Tensor, positions: torch.Tensor, scale: float, window: Optional[int],
               max_new_tokens: int, max_ctx_len: int, splits: Optional[int] = None,
-              mma_only: bool = False, cluster: Optional[int] = None) -> torch.Tensor:
+              mma_only: bool = False, cluster: Optional[int] = None, groups: int = 1) -> torch.Tensor:
     """softmax(q . k * scale) . v over the cached positions that each query sees: 0..its own,
     or the last `window` of them.  q: the first n_heads*head_dim columns of each row.
 
     bfloat16 with a head size that is a multiple of 16 up to 128 runs on the tensor cores: the
     split-KV kernel when every sequence brings one token (csrc/attention_mma.cu; `splits` forces
-    about that many CTAs to a pair, `cluster` a cluster of that size to a pair, 0 none); otherwise the
+    about that many CTAs to a pair, `cluster` `groups` clusters of that size to a pair, 0 none); otherwise the
     tcgen05 kernel for head sizes 64 and 128 (csrc/attention_tc.cu) and the mma.sync kernel for
     the others (or with `mma_only`).  Everything else runs the plain kernel."""
     if q.dtype != torch.bfloat16 or not library().wpc_attention_mma_supports(n_heads, n_kv_heads, head_dim):
@@ -637,12 +637,21 @@ def attention(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, k_p
     if max_new_tokens == 1 and B <= 1024 and B * n_kv_heads <= _WORKSPACE_COUNTERS:
         _need(T == B, "one token per sequence expected")
         if cluster is None:
-            cluster = 0 if splits else plan_decode_cluster(B, n_kv_heads, n_heads, head_dim, max_ctx_len, window)
+            cluster, groups = (0, 1) if splits else plan_decode_cluster(B, n_kv_heads, n_heads, head_dim,
+                                                                        max_ctx_len, window)
         if cluster:
+            part_o = part_ml = counters = None
+            if groups > 1:
+                pairs = B * n_kv_heads
+                part_o = torch.empty((pairs * groups * (n_heads // n_kv_heads) * head_dim,), dtype=torch.float32,
+                                     device=q.device)
+                part_ml = torch.empty((pairs * groups * 32,), dtype=torch.float32, device=q.device)
+                _, counters, _ = workspace(q.device)
             _check("attention_decode_cluster", library().wpc_attention_decode_cluster(
                 _p(q), q.stride(0), _p(out), out.stride(0), _p(k_pages), _p(v_pages), _p(page_table),
                 page_table.shape[1], _p(ctx_lens), B, n_heads, n_kv_heads, head_dim, ctypes.c_float(scale),
-                int(window or 0), int(cluster), _stream()))
+                int(window or 0), int(cluster), int(groups), _p(part_o), _p(part_ml), _p(counters),
+                0 if counters is None else counters.numel(), _stream()))
             return out
         n_ctas = plan_decode_ctas(B, n_kv_heads, max_ctx_len, window, splits)
         slots = n_ctas + B * n_kv_heads
@@ -735,35 +744,52 @@ def decode_cluster_capacity(head_dim: int, cluster: int, alone: bool) -> int:
     return _decode_cluster_capacity[key]
 
 
+# Microseconds of the cluster decode kernel, fitted to runs at the 7B shape (1 to 6 sequences of
+# 8 Ki to 64 Ki positions, every cluster size and group count that fits; root mean square error
+# 0.9 us): a page when a CTA has an SM to itself and when two share one, what sharing costs at
+# the start, the exchange through shared memory, and what several groups to a pair add (parts to
+# L2, a fence, a ticket, a cluster barrier, one pass over the parts) with so much more a group.
+CLUSTER_PAGE_ALONE_US, CLUSTER_PAGE_SHARED_US, CLUSTER_SHARED_START_US = 0.97, 1.29, 1.0
+CLUSTER_EXCHANGE_US, GROUP_COMBINE_US, GROUP_EACH_US = 4.1, 3.3, 0.23
+
+
 def plan_decode_cluster(n_seqs: int, n_kv_heads: int, n_heads: int, head_dim: int, max_ctx_len: int,
-                        window: Optional[int]) -> int:
-    """The size of the clusters (2..16) if a decode step should run with a cluster to a pair, else
-    0.  The estimate is that of plan_decode_ctas, with 3.5 us for the exchange through shared
-    memory in place of tickets and combining (measured at the 7B shape, 8 sequences of 4,000
-    positions: clusters of 7 take 20.3 us, 256 CTAs with tickets 24.8).  Every pair gets the
+                        window: Optional[int]):
+    """(cluster size 2..16, groups) if a decode step should run with clusters to a pair, else
+    (0, 1): whichever the estimates make fastest, the fixed grid's being that of plan_decode_ctas
+    (at the 7B shape, 8 sequences of 4,000 positions: clusters of 7 take 20.3 us, 256 CTAs with
+    tickets 24.8).  Every pair gets the
     same number of CTAs and all clusters must run at once, with a tenth of the device's
     capacity to spare: clusters are placed while CTAs of the kernel before still hold their
     SMs, and one that finds no room in any GPC waits for the others to end (32 clusters of 8
-    where 33 fit: 28 to 32 us in most launches, 18 us in the others)."""
+    where 33 fit: 28 to 32 us in most launches, 18 us in the others).  When 16 ranks to a pair
+    leave SMs idle (one or two long sequences), several clusters (groups) share a pair's pages
+    and the pair's last cluster adds their parts (one sequence of 32 Ki positions: 7 groups of 8,
+    21.7 us; the fixed grid 28.5, one cluster of 16 35)."""
     pairs = max(n_seqs * n_kv_heads, 1)
     if not CLUSTER_DECODE or (n_heads // n_kv_heads) * head_dim > CLUSTER_DECODE_MAX_OUT or pairs > sms():
-        return 0
+        return 0, 1
     blocks = (max_ctx_len + PAGE - 1) // PAGE
     if window:
         blocks = min(blocks, (window + PAGE - 1) // PAGE + 1)
-    best_c, best_t = 0, _plan_decode(n_seqs, n_kv_heads, max_ctx_len, window)[1]
+    best, best_t = (0, 1), _plan_decode(n_seqs, n_kv_heads, max_ctx_len, window)[1]
     for c in range(2, 17):
-        n = pairs * c
-        if n > 2 * sms() or c > blocks:
-            break
-        alone = n <= sms()
-        if pairs * 1.1 > decode_cluster_capacity(head_dim, c, alone):
-            continue
-        page, start = (1.05, 0.0) if alone else (1.5, 2.0)
-        t = start + -(-blocks // c) * page + 3.5 + 0.002 * n
-        if t < best_t:
-            best_c, best_t = c, t
-    return best_c
+        for g in range(1, 17):
+            n = pairs * c * g
+            if n > 2 * sms() or c * g > blocks:
+                break
+            if g > 1 and c < 4:
+                continue                    # small clusters in groups: larger clusters do the same with less combining
+            alone = n <= sms()
+            if pairs * g * 1.1 > decode_cluster_capacity(head_dim, c, alone):
+                continue                    # more groups may fit again once two CTAs share an SM
+            page, start = ((CLUSTER_PAGE_ALONE_US, 0.0) if alone else
+                           (CLUSTER_PAGE_SHARED_US, CLUSTER_SHARED_START_US))
+            t = (start + -(-blocks // (c * g)) * page + CLUSTER_EXCHANGE_US +
+                 (GROUP_COMBINE_US + GROUP_EACH_US * g if g > 1 else 0.0))
+            if t < best_t:
+                best, best_t = (c, g), t
+    return best
 
 
 def attention_plain(q, n_heads, n_kv_heads, head_dim, k_pages, v_pages, page_table, seq_of_token, positions,
