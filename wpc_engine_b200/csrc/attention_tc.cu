@@ -202,7 +202,7 @@ prefill_ws_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                   const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* __restrict__ out, int out_stride,
                   const int* __restrict__ page_table, int table_width, const int* __restrict__ cu_seqlens,
                   const int* __restrict__ ctx_lens, int nh, int nkv, float scale_log2, int window,
-                  int* __restrict__ status, unsigned long long wait_ns, int starve) {
+                  int* __restrict__ status, unsigned long long wait_ns, int starve, int n_sm) {
   using C = Cfg<HD>;
   using W = WsCfg<HD, NT>;
   constexpr int NS = W::NS;
@@ -212,8 +212,22 @@ prefill_ws_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
   extern __shared__ __align__(128) uint8_t smem_raw[];
   // The last tiles of a sequence see the most keys: they start first, and for all KV heads
   // before any lighter tile (the KV head is the fastest grid index), so that no heavy tile is
-  // left for the end.
-  const int tile = (int)gridDim.y - 1 - (int)blockIdx.y, g = blockIdx.x, b = blockIdx.z;
+  // left for the end.  An SM takes new CTAs of this kernel in turn: while the older of its two
+  // CTAs runs, the place of the younger one, once it has ended, stays empty (seen in a trace of
+  // start and end times; without tcgen05.relinquish_alloc_permit an SM even runs one CTA at a
+  // time).  So the two CTAs that an SM gets at the start should be equally heavy: the device
+  // hands the first n_sm CTAs of a grid to one SM each and the next n_sm to the same SMs in
+  // the same order, and position p of the grid takes rank 2 p, or 2 (p - n_sm) + 1, of the
+  // pieces in descending order (one sequence only; 53.7 -> 47.3 us at 2,048 tokens of the 7B shape).
+  int rank = (int)(blockIdx.y * gridDim.x + blockIdx.x);
+  if (gridDim.z == 1) {
+    const int n = (int)(gridDim.x * gridDim.y), two = n - n_sm < n_sm ? n - n_sm : n_sm;   // SMs that get two at the start
+    if (two > 0) {
+      if (rank < n_sm) rank = rank < two ? 2 * rank : rank + two;
+      else if (rank < 2 * n_sm) rank = 2 * (rank - n_sm) + 1;
+    }
+  }
+  const int tile = (int)gridDim.y - 1 - rank / (int)gridDim.x, g = rank % (int)gridDim.x, b = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_rep = nh / nkv;
   const int tok0 = cu_seqlens[b];
@@ -516,7 +530,7 @@ static int launch_ws(const void* q, int q_stride, void* out, int out_stride, con
   dim3 grid(nkv, (max_new * n_rep + NT * ROWS - 1) / (NT * ROWS), B);
   wpc::launch(prefill_ws_kernel<HD, NT>, grid, W::THREADS, W::SMEM, stream, mk, mv, (const __nv_bfloat16*)q, q_stride,
               (__nv_bfloat16*)out, out_stride, page_table, table_width, cu_seqlens, ctx_lens, nh, nkv, scale * LOG2E,
-              window, status, wait_policy().limit_ns, wait_policy().starve);
+              window, status, wait_policy().limit_ns, wait_policy().starve, NT == 1 ? sm_count() : 1 << 30);
   return launch_status();
 }
 
