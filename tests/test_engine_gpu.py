@@ -240,6 +240,55 @@ def test_long_prompt_in_chunks(tmp_path_factory, dtype):
     eng.cache.check()
 
 
+def test_one_long_sequence_decodes_with_several_clusters_to_a_pair(tmp_path_factory):
+    """At 12,000 positions a single sequence's decode attention is planned with several clusters
+    to each (sequence, kv head) pair, whose parts a ticket's last cluster adds.  The same positions
+    are reached once by single-token steps (replayed from a graph) and once inside a prompt's
+    last chunk, where the prefill kernels serve them; both must agree within bfloat16's noise,
+    and both with the float32 path."""
+    from conftest import make_folder
+    from wpc_engine_b200 import SequenceStep, ops
+    raw = dict(architectures=["Qwen2ForCausalLM"], num_hidden_layers=2, hidden_size=128, num_attention_heads=2,
+               num_key_value_heads=1, intermediate_size=192, vocab_size=500, rope_theta=1e6, rms_norm_eps=1e-6,
+               max_position_embeddings=16384, tie_word_embeddings=True)
+    folder = make_folder(tmp_path_factory, raw, 22, torch.bfloat16)
+    n, tail = 12000, 4
+    cluster, groups = ops.plan_decode_cluster(1, 1, 2, 64, n + tail, None)
+    assert cluster >= 2 and groups > 1, (cluster, groups)
+    tokens = random_tokens(500, n + tail, 902)
+
+    def chunks(eng, slot, upto, want_from):
+        rows, fed = [], 0
+        while fed < upto:
+            m = min(2048, upto - fed)
+            want = [i - fed for i in range(max(fed, want_from), fed + m)]
+            out = eng.step([SequenceStep(slot, tokens[fed:fed + m], want=want)])
+            rows += list(out.float().cpu().numpy()) if want else []
+            fed += m
+        return rows
+
+    got = {}
+    for dtype in ("bfloat16", "float32"):
+        eng = Engine.from_folder(folder, dtype=dtype, max_tokens=2 * 12288 + 128)
+        a, b = eng.open_sequence(), eng.open_sequence()
+        try:
+            chunks(eng, a, n, n)
+            one_by_one = [eng.step([SequenceStep(a, [tokens[i]], want=[0])]).float().cpu().numpy()[0]
+                          for i in range(n, n + tail)]
+            in_prompt = chunks(eng, b, n + tail, n)
+        finally:
+            eng.close_sequence(a)
+            eng.close_sequence(b)
+        eng.cache.check()
+        got[dtype] = (np.stack(one_by_one), np.stack(in_prompt))
+        assert ops.device_status() == 0
+    exact = got["float32"][1]
+    bound = bfloat16_bound(exact)
+    assert np.abs(got["float32"][0] - exact).max() <= 1e-3 * np.abs(exact).max()
+    for rows in got["bfloat16"]:
+        assert np.abs(rows - exact).max() <= bound, (np.abs(rows - exact).max(), bound)
+
+
 def test_medium_model_graphs_and_dependent_launch_change_nothing(tmp_path_factory):
     """A model large enough for the real tile shapes (split-K products, weight tiles fetched
     ahead, many CTAs per attention pair, persistent prefill products, tcgen05 attention):
