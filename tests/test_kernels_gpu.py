@@ -465,6 +465,23 @@ def test_silu_mul_groups(dtype, inner, group):
     close(ops.silu_mul(gu, inner, group), ref.silu_mul(gu.cpu(), inner, group).to(DEV), dtype)
 
 
+@pytest.mark.parametrize("M", [65, 96, 128])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_wide_written_product_of_up_to_128_tokens(M, out_dtype):
+    """65 to 128 tokens and a very wide output that is written (the output head's case): tiles on
+    pairs of SMs; rows of the 256-row tile beyond the tokens are neither read nor written."""
+    N, K = 256 * (ops.sms() // 2) + 72, 264
+    assert ops.wide_written(M, N, False) and not ops.wide_written(M, N - 400, False) and not ops.wide_written(M, N, True)
+    x, w = rnd((M, K), torch.bfloat16, 81), rnd((N, K), torch.bfloat16, 82, 0.05)
+    bias = rnd((N,), seed=83)
+    got = ops.linear(x, w, bias, out_dtype=out_dtype)
+    want = ref.linear(x.cpu(), w.cpu(), bias.cpu(), out_dtype=torch.float32)
+    mag = want.abs().max().item()
+    assert (got.cpu().float() - want).abs().max().item() <= (1e-2 if out_dtype == torch.bfloat16 else 2e-3) * mag
+    assert torch.equal(got, ops.linear(x, w, bias, out_dtype=out_dtype))
+    assert ops.device_status() == 0
+
+
 # ---- prefill attention on tcgen05 against the plain reference and the mma.sync twin ---------------
 @pytest.mark.parametrize("nh,nkv,hd", [(28, 4, 128), (14, 2, 64), (4, 4, 128), (3, 1, 64), (16, 1, 128)])
 @pytest.mark.parametrize("window", [None, 100])
