@@ -9,13 +9,16 @@
 //            head, page) work evenly; the 16 MMA rows hold the group's query heads; the four
 //            warps of a CTA take the four 16-key quarters of each 64-key page and are merged
 //            at the end; partial results of a pair that spans CTAs are combined by the last
-//            of them to finish.
+//            of them to finish.  With few pairs of about equal lengths, one or several
+//            thread-block clusters take a pair instead and add up through one another's shared
+//            memory (see decode_cluster_kernel).
 //   prefill  any number of new tokens per sequence.  grid = (row tiles, kv heads,
 //            sequences); a tile is 64 rows of (token, head-in-group), 16 per warp; every warp
 //            walks the pages up to the tile's last visible key.
 //
 // Keys and values of a page ([64, head_dim], contiguous) are copied to shared memory with
-// cp.async, two pages in flight, rows padded by 16 bytes so that ldmatrix is free of bank
+// cp.async, a ring of pages in flight (3 when two CTAs share an SM, 6 when one has it alone),
+// rows padded by 16 bytes so that ldmatrix is free of bank
 // conflicts.  head_dim: multiples of 16 up to 128 (other sizes take the plain kernel).
 #include "api.h"
 #include "common.cuh"
