@@ -69,6 +69,73 @@ def test_steps_that_mix_one_token_and_many(folders, name, dtype):
     assert eng.cache.slots.n_held == 0
 
 
+@pytest.mark.parametrize("name,dtype", CASES)
+@pytest.mark.parametrize("seed", [11, 12, 13])
+def test_random_schedules(folders, name, dtype, seed):
+    """Schedules drawn at random (a fixed seed each): requests join while others run, steps bring
+    one token each or chunks of any size or a mixture, only some places are wanted, the pool of
+    pages is small enough to run out (the step that asked for too much leaves the cache as it
+    was, and the longest request is closed to make room), slots and pages come back and are used
+    again.  Every wanted row against the plain implementation."""
+    from wpc_engine_b200 import CacheError
+    rng = np.random.default_rng(seed)
+    folder = folders[(name, dtype)]
+    eng = Engine.from_folder(folder, dtype=dtype, max_tokens=int(rng.choice([320, 512, 1024])), max_sequences=5)
+    cfg, tensors = P.read_model_folder(folder)
+    longest = min(600, eng.config.max_position_embeddings)
+    reqs = [random_tokens(eng.config.vocab_size, int(rng.integers(1, longest + 1)), 7000 + 10 * seed + i) for i in range(7)]
+    plain, fed, slots, waiting = {}, [0] * len(reqs), {}, list(range(len(reqs)))
+    bound = None
+    compared = evicted = 0
+    try:
+        for _ in range(4000):
+            if not (waiting or slots):
+                break
+            while waiting and len(slots) < 5 and rng.random() < 0.5:
+                slots[waiting.pop(0)] = eng.open_sequence()
+            if not slots:
+                continue
+            active = [r for r in slots if rng.random() < 0.8] or list(slots)[:1]
+            single = rng.random() < 0.7
+            entries, brought = [], []
+            for r in active:
+                left = len(reqs[r]) - fed[r]
+                n = 1 if single else max(1, min(left, int(rng.choice([1, 1, 2, 7, 40, 64, 65, 130, 300]))))
+                want = (sorted({int(x) for x in rng.integers(0, n, size=int(rng.integers(0, 4)))})
+                        if rng.random() < 0.7 else list(range(n)))
+                entries.append(SequenceStep(slots[r], reqs[r][fed[r]: fed[r] + n], want=want))
+                brought.append((r, n, want))
+            try:
+                out = eng.step(entries)
+            except CacheError:
+                eng.cache.check()
+                r = max(slots, key=lambda r: fed[r])
+                eng.close_sequence(slots.pop(r))
+                evicted += 1
+                continue
+            out = None if out is None else out.float().cpu().numpy()     # nothing wanted: nothing returned
+            at = 0
+            for r, n, want in brought:
+                if want:
+                    if r not in plain:
+                        plain[r] = P.forward(cfg, tensors, reqs[r], np.float64)
+                    ref = plain[r][[fed[r] + i for i in want]]
+                    bound = bfloat16_bound(plain[r]) if dtype == "bfloat16" else 1e-3 * np.abs(plain[r]).max()
+                    err = np.abs(out[at: at + len(want)] - ref).max()
+                    assert err <= bound, (seed, r, fed[r], n, want, err, bound, [(b[0], b[1]) for b in brought])
+                    at += len(want)
+                    compared += len(want)
+                fed[r] += n
+                if fed[r] >= len(reqs[r]):
+                    eng.close_sequence(slots.pop(r))
+    finally:
+        for s_ in slots.values():
+            eng.close_sequence(s_)
+    assert compared > 50
+    eng.cache.check()
+    assert eng.cache.slots.n_held == 0
+
+
 WIDE_GROUP = dict(architectures=["Qwen2ForCausalLM"], num_hidden_layers=2, hidden_size=896, num_attention_heads=7,
                   num_key_value_heads=1, head_dim=128, intermediate_size=1536, vocab_size=1000, rope_theta=1e6,
                   rms_norm_eps=1e-6, max_position_embeddings=2048, tie_word_embeddings=False)
