@@ -202,12 +202,12 @@ prefill_ws_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                   const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* __restrict__ out, int out_stride,
                   const int* __restrict__ page_table, int table_width, const int* __restrict__ cu_seqlens,
                   const int* __restrict__ ctx_lens, int nh, int nkv, float scale_log2, int window,
-                  int* __restrict__ status, unsigned long long wait_ns, int starve, int n_sm) {
+                  int* __restrict__ status, unsigned long long wait_ns, int starve, int n_sm, int late_trigger) {
   using C = Cfg<HD>;
   using W = WsCfg<HD, NT>;
   constexpr int NS = W::NS;
   constexpr int TROWS = NT * ROWS;
-  pdl_trigger();
+  if (!late_trigger) pdl_trigger();
   pdl_wait();
   extern __shared__ __align__(128) uint8_t smem_raw[];
   // The last tiles of a sequence see the most keys: they start first, and for all KV heads
@@ -312,6 +312,9 @@ prefill_ws_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
           tma_load_2d(v_s + st * C::PAGE_BYTES + hb * (PAGE * 128), &map_v, hb * 64, row, v_full + st);
       }
     }
+    // a long prompt's kernel lets the kernel after it go only now, when this CTA's copies are all
+    // on their way (its CTAs would otherwise sit on SMs that this kernel still needs)
+    if (late_trigger) pdl_trigger();
   } else if (warp == MMA_WARP) {
     // ---- MMA issue ----
     if (lane == 0) {
@@ -530,7 +533,8 @@ static int launch_ws(const void* q, int q_stride, void* out, int out_stride, con
   dim3 grid(nkv, (max_new * n_rep + NT * ROWS - 1) / (NT * ROWS), B);
   wpc::launch(prefill_ws_kernel<HD, NT>, grid, W::THREADS, W::SMEM, stream, mk, mv, (const __nv_bfloat16*)q, q_stride,
               (__nv_bfloat16*)out, out_stride, page_table, table_width, cu_seqlens, ctx_lens, nh, nkv, scale * LOG2E,
-              window, status, wait_policy().limit_ns, wait_policy().starve, NT == 1 ? sm_count() : 1 << 30);
+              window, status, wait_policy().limit_ns, wait_policy().starve, NT == 1 ? sm_count() : 1 << 30,
+              max_new >= 1024 ? 1 : 0);
   return launch_status();
 }
 
