@@ -839,7 +839,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (p.bias) {
 #pragma unroll
               for (int j = 0; j < 32; ++j)
-                if (j < nc) v[j] += p.bias[n0 + c + j];
+                if (j < nc) v[j] += __ldg(p.bias + n0 + c + j);
             }
             if (row < p.M) store_row32(p, row, n0 + c, nc, v);
           } else {
@@ -916,7 +916,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // then depend on the order of arrival).
 constexpr int PAIR_STAGES = 6;
 constexpr int PAIR_STAGE_BYTES = 2 * BM * BK * 2;       // this CTA's halves of A and B: 16 KiB each
-constexpr int PAIR_SMEM = 1024 + 1024 + PAIR_STAGES * PAIR_STAGE_BYTES;
+constexpr int PAIR_SMEM = 1024 + 1024 + PAIR_STAGES * PAIR_STAGE_BYTES + 1024;     // + a tile's bias
 constexpr int PAIR_N = 256;
 
 __device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, int x, int y, uint32_t leader_bar) {
@@ -1052,6 +1052,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     pdl_wait();
     const int q = warp & 3;
     const int r = q * 32 + lane;
+    // The bias of a tile's columns comes into shared memory while the tile's MMAs run: read from
+    // global memory chunk by chunk in the epilogue, each chunk's line was a trip to L2 or beyond
+    // between two stores (8 us a tile, measured with one tile to a pair).
+    float* s_bias = (float*)(tiles + PAIR_STAGES * PAIR_STAGE_BYTES);      // [256]
     int j = 0;
     for (int u = pair; u < n_units; u += n_pairs, ++j) {
       const int t = u / S, slice = u - t * S;
@@ -1059,8 +1063,33 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       const int m0 = tile_m * 2 * BM + (int)rank * BM, n0 = tile_n * PN;
       const int n_kb = max(min(p.k_blocks, (slice + 1) * kb_per) - slice * kb_per, 0);
       const int b = j & 1, use = j >> 1;
+      if (p.bias) {
+        asm volatile("bar.sync 1, 128;" ::: "memory");     // the epilogue of the tile before has read its bias
+        s_bias[r] = n0 + r < p.N ? __ldg(p.bias + n0 + r) : 0.f;
+        s_bias[r + 128] = n0 + r + 128 < p.N ? __ldg(p.bias + n0 + r + 128) : 0.f;
+      }
+      // (the place of this thread's token in the cache: three loads that hang on one another,
+      // looked up while the tile's MMAs run)
+      long long rope_base = -1;
+      if (ROPE && m0 + r < p.M) {
+        const int pos = p.positions[m0 + r], block = pos / WPC_PAGE;
+        const int page = block < p.table_width ? p.page_table[(size_t)p.seq_of_token[m0 + r] * p.table_width + block] : -1;
+        if (page >= 0 && page < p.n_pages) rope_base = (long long)page * p.rope_nkv * WPC_PAGE + pos % WPC_PAGE;
+      }
       bool ok = mbar_wait(accum_full + b, use & 1, p.wait_ns);
       ok = __all_sync(0xffffffffu, ok);
+      if (p.bias) {
+        // the bias is written; and the four warps agree on whether the wait ran out, so that
+        // none of them meets the barrier above alone
+        uint32_t all_ok;
+        asm volatile(
+            "{\n\t.reg .pred p, q;\n\t"
+            "setp.ne.u32 q, %1, 0;\n\t"
+            "bar.red.and.pred p, 1, 128, q;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(all_ok) : "r"((uint32_t)ok) : "memory");
+        ok = all_ok != 0;
+      }
       if (!ok) atomicExch(flags, 1);
       fence_after_sync();
       const int n_valid = min(PN, p.N - n0);
@@ -1098,22 +1127,31 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         // rotated k and v into the page of the token's position (model.rs:464-475).
         const int hd = p.rope_hd, half = hd >> 1;
         const int nq = p.rope_nh * hd, nk = p.rope_nkv * hd;
-        long long base = -1;                               // page * nkv * PAGE + place in the page
+        const long long base = rope_base;                  // page * nkv * PAGE + place in the page
         const bool in_m = row < p.M;
-        if (in_m) {
-          const int pos = p.positions[row], block = pos / WPC_PAGE;
-          const int page = block < p.table_width ? p.page_table[(size_t)p.seq_of_token[row] * p.table_width + block] : -1;
-          if (page >= 0 && page < p.n_pages) base = (long long)page * p.rope_nkv * WPC_PAGE + pos % WPC_PAGE;
-          else if (n0 + PN > nq && p.status) atomicExch(p.status, WPC_ERR_BAD_ARGUMENT);
-        }
+        if (in_m && base < 0 && n0 + PN > nq && p.status) atomicExch(p.status, WPC_ERR_BAD_ARGUMENT);
         // a block of 32 pairs at a time: its cosines and sines serve every head of the tile
+        // (each thread reads its own row of the tables: 16 bytes a load where the rows allow it; a
+        // load of 4 bytes a lane from 32 different lines costs the load unit as much)
+        const bool vec = (p.rope_R & 3) == 0 && ((((uintptr_t)p.rope_cos) | ((uintptr_t)p.rope_sin)) & 15) == 0;
         for (int pb = 0; pb < half; pb += 32) {
           float cs[32], sn[32];
+          if (vec) {
 #pragma unroll
-          for (int jj = 0; jj < 32; ++jj) {
-            const bool rot = in_m && pb + jj < p.rope_R;
-            cs[jj] = rot ? p.rope_cos[(size_t)row * p.rope_R + pb + jj] : 1.f;
-            sn[jj] = rot ? p.rope_sin[(size_t)row * p.rope_R + pb + jj] : 0.f;
+            for (int jj = 0; jj < 32; jj += 4) {
+              const bool rot = in_m && pb + jj < p.rope_R;
+              const float4 c4 = rot ? __ldg((const float4*)(p.rope_cos + (size_t)row * p.rope_R + pb + jj)) : make_float4(1.f, 1.f, 1.f, 1.f);
+              const float4 s4 = rot ? __ldg((const float4*)(p.rope_sin + (size_t)row * p.rope_R + pb + jj)) : make_float4(0.f, 0.f, 0.f, 0.f);
+              cs[jj] = c4.x; cs[jj + 1] = c4.y; cs[jj + 2] = c4.z; cs[jj + 3] = c4.w;
+              sn[jj] = s4.x; sn[jj + 1] = s4.y; sn[jj + 2] = s4.z; sn[jj + 3] = s4.w;
+            }
+          } else {
+#pragma unroll
+            for (int jj = 0; jj < 32; ++jj) {
+              const bool rot = in_m && pb + jj < p.rope_R;
+              cs[jj] = rot ? __ldg(p.rope_cos + (size_t)row * p.rope_R + pb + jj) : 1.f;
+              sn[jj] = rot ? __ldg(p.rope_sin + (size_t)row * p.rope_R + pb + jj) : 0.f;
+            }
           }
           for (int h0 = 0; h0 < n_valid; h0 += hd) {       // heads of the tile
             const int feat0 = n0 + h0;                     // first feature of the head
@@ -1127,8 +1165,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             float va[32], vb[32];
 #pragma unroll
             for (int jj = 0; jj < 32; ++jj) {
-              const float a = (have_acc ? __uint_as_float(ua[jj]) : 0.f) + (p.bias ? p.bias[feat0 + pb + jj] : 0.f);
-              const float bq = (have_acc ? __uint_as_float(ub[jj]) : 0.f) + (p.bias ? p.bias[feat0 + half + pb + jj] : 0.f);
+              const float a = (have_acc ? __uint_as_float(ua[jj]) : 0.f) + (p.bias ? s_bias[h0 + pb + jj] : 0.f);
+              const float bq = (have_acc ? __uint_as_float(ub[jj]) : 0.f) + (p.bias ? s_bias[h0 + half + pb + jj] : 0.f);
               if (kind < 2) {
                 va[jj] = a * cs[jj] - bq * sn[jj];
                 vb[jj] = bq * cs[jj] + a * sn[jj];
@@ -1178,13 +1216,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             for (int jj = 0; jj < 32; jj += 4) {
               float a4[4];
 #pragma unroll
-              for (int e = 0; e < 4; ++e) a4[e] = __uint_as_float(uu[jj + e]) + (with_bias ? p.bias[n0 + c + jj + e] : 0.f);
+              for (int e = 0; e < 4; ++e) a4[e] = __uint_as_float(uu[jj + e]) + (with_bias ? s_bias[c + jj + e] : 0.f);
               red_add_f32x4(dst + jj, a4[0], a4[1], a4[2], a4[3]);
             }
           } else {
 #pragma unroll
             for (int jj = 0; jj < 32; ++jj)
-              if (jj < nc) atomicAdd(dst + jj, __uint_as_float(uu[jj]) + (with_bias ? p.bias[n0 + c + jj] : 0.f));
+              if (jj < nc) atomicAdd(dst + jj, __uint_as_float(uu[jj]) + (with_bias ? s_bias[c + jj] : 0.f));
           }
         }
       } else if (ok) {
@@ -1201,7 +1239,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           if (p.bias) {
 #pragma unroll
             for (int jj = 0; jj < 32; ++jj)
-              if (jj < nc) v[jj] += p.bias[n0 + c + jj];
+              if (jj < nc) v[jj] += s_bias[c + jj];
           }
           if (row < p.M) store_row32(p, row, n0 + c, nc, v);
         }
