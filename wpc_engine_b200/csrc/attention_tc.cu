@@ -409,7 +409,12 @@ prefill_ws_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (valid && abs0 + PAGE - 1 <= p_row && abs0 >= lo_row) {
 #pragma unroll
-        for (int i = 0; i < 64; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(su[i]));
+        for (int i = 0; i < 64; i += 8) {                  // (pairs of values to a maximum: one three-input instruction)
+          mx4[0] = fmaxf(fmaxf(mx4[0], __uint_as_float(su[i])), __uint_as_float(su[i + 1]));
+          mx4[1] = fmaxf(fmaxf(mx4[1], __uint_as_float(su[i + 2])), __uint_as_float(su[i + 3]));
+          mx4[2] = fmaxf(fmaxf(mx4[2], __uint_as_float(su[i + 4])), __uint_as_float(su[i + 5]));
+          mx4[3] = fmaxf(fmaxf(mx4[3], __uint_as_float(su[i + 6])), __uint_as_float(su[i + 7]));
+        }
       } else {
 #pragma unroll
         for (int i = 0; i < 64; ++i) {
@@ -431,17 +436,19 @@ prefill_ws_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
       }
       l_sum *= alpha;
       const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;     // all scores are -inf then: p = 0
-      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      // (two values to an instruction where there is one: fma.f32x2, add.f32x2)
+      const float2 scale2 = make_float2(scale_log2, scale_log2), neg_m2 = make_float2(neg_m, neg_m);
+      float2 sum2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
       uint32_t pw[32];
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
-        const float p0 = ex2(fmaf(__uint_as_float(su[2 * i]), scale_log2, neg_m));
-        const float p1 = ex2(fmaf(__uint_as_float(su[2 * i + 1]), scale_log2, neg_m));
-        sum4[i & 3] += p0 + p1;
-        const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
+        const float2 x = __ffma2_rn(make_float2(__uint_as_float(su[2 * i]), __uint_as_float(su[2 * i + 1])), scale2, neg_m2);
+        const float2 pr = make_float2(ex2(x.x), ex2(x.y));
+        sum2[i & 1] = __fadd2_rn(sum2[i & 1], pr);
+        const __nv_bfloat162 pb = __floats2bfloat162_rn(pr.x, pr.y);
         pw[i] = *(const uint32_t*)&pb;
       }
-      l_sum += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      l_sum += (sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y);
       // the weighted values of the page before must be done before O and P are touched
       if (j > 0) {
         ok = mbar_wait(p_empty + t, (j - 1) & 1, wait_ns);
