@@ -57,6 +57,12 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 2^x in one instruction (x <= 0 here; results below the normal range are zero)
+__device__ __forceinline__ float ex2_fast(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *(uint32_t*)&v;
@@ -135,12 +141,14 @@ __device__ __forceinline__ void softmax_step(float (&s)[NT][4], float (&m)[2], f
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
     const float m_new = fmaxf(m[h], mx);
     const bool none = m_new == -INFINITY;
-    const float alpha = none ? 1.f : exp2f(m[h] - m_new);
+    // (one instruction an exponential: the arguments are at most 0, and exp2f's care for results
+    // below the normal range costs four more for each score of every page)
+    const float alpha = none ? 1.f : ex2_fast(m[h] - m_new);
     float sum = 0.f;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
-      const float p0 = none ? 0.f : exp2f(s[nt][2 * h] - m_new);
-      const float p1 = none ? 0.f : exp2f(s[nt][2 * h + 1] - m_new);
+      const float p0 = none ? 0.f : ex2_fast(s[nt][2 * h] - m_new);
+      const float p1 = none ? 0.f : ex2_fast(s[nt][2 * h + 1] - m_new);
       s[nt][2 * h] = p0;
       s[nt][2 * h + 1] = p1;
       sum += p0 + p1;
@@ -395,13 +403,13 @@ decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* 
 #pragma unroll
       for (int w = 0; w < 4; ++w) {
         const float mw = sm[w * 16 + row];
-        const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
+        const float f = (mw == -INFINITY) ? 0.f : ex2_fast(mw - M);
         acc += f * so[(w * 16 + row) * HD + d];
         Lsum += f * sl[w * 16 + row];
       }
       if (whole) {
         out[(size_t)b * out_stride + (size_t)(g * n_rep + row) * HD + d] =
-            __float2bfloat16_rn(Lsum > 0.f ? acc / Lsum : 0.f);
+            __float2bfloat16_rn(Lsum > 0.f ? __fdividef(acc, Lsum) : 0.f);
       } else {
         part_o[(slot * 16 + row) * HD + d] = acc;
         if (d == 0) {
@@ -459,7 +467,7 @@ decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* 
               float Lsum = 0.f;
               for (int sidx = lane; sidx < n_parts; sidx += 32) {
                 const float ms = wm[row * n_parts + sidx];
-                const float f = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
+                const float f = (ms == -INFINITY) ? 0.f : ex2_fast(ms - M);
                 wm[row * n_parts + sidx] = f;
                 Lsum += f * wl[row * n_parts + sidx];
               }
@@ -506,12 +514,12 @@ constexpr int CLUSTER_DECODE_MAX_RANKS = 16;      // beyond 8 a cluster needs th
 constexpr int CLUSTER_DECODE_MAX_GROUPS = 16;     // clusters that share a pair's pages
 constexpr int CLUSTER_SEGMENT_PAGES = 256;        // page numbers of a rank's share kept in shared memory
 
-template <int HD, int DECODE_STAGES>
+template <int HD, int DECODE_STAGES, bool GROUPED>
 __global__ void __launch_bounds__(THREADS)
 decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* __restrict__ out, int out_stride,
                       const __nv_bfloat16* __restrict__ k_pages, const __nv_bfloat16* __restrict__ v_pages,
                       const int* __restrict__ page_table, int table_width, const int* __restrict__ ctx_lens, int B,
-                      int nh, int nkv, float scale_log2, int window, int C, int early_pages, int G,
+                      int nh, int nkv, float scale_log2, int window, int C, int early_pages, int n_groups,
                       float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters) {
   pdl_trigger();
   extern __shared__ __align__(16) uint8_t smem_raw[];
@@ -525,6 +533,9 @@ decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bf
   const int n_rep = nh / nkv;
   const size_t page_elems = (size_t)nkv * PAGE * HD;
   const int rank = (int)cluster_rank();
+  // (the variant with one cluster to a pair is compiled on its own: the tail below is code that
+  // runs once a launch, and every line that it does not need is a line more to fetch)
+  const int G = GROUPED ? n_groups : 1;
   const int cl = blockIdx.x / C, pair = cl / G, grp = cl - pair * G, b = pair / nkv, g = pair - b * nkv;
   cluster_sync_all();                       // every rank runs: its shared memory may be written
 
@@ -644,7 +655,7 @@ decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bf
 #pragma unroll
     for (int w = 0; w < 4; ++w) {
       const float mw = sm[w * 16 + row];
-      const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
+      const float f = (mw == -INFINITY) ? 0.f : ex2_fast(mw - M);
       const float4 ow = *(const float4*)(so + (w * 16 + row) * HD + d);
       acc[0] += f * ow.x; acc[1] += f * ow.y; acc[2] += f * ow.z; acc[3] += f * ow.w;
       Lsum += f * sl[w * 16 + row];
@@ -670,12 +681,12 @@ decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bf
       float num = 0.f, den = 0.f;
       for (int c = 0; c < C; ++c) {                        // in rank order
         const float mc = s_recv_ml[(c * 16 + row) * 2];
-        const float f = (mc == -INFINITY) ? 0.f : exp2f(mc - M);
+        const float f = (mc == -INFINITY) ? 0.f : ex2_fast(mc - M);
         num += f * s_recv_o[c * share + t];
         den += f * s_recv_ml[(c * 16 + row) * 2 + 1];
       }
       if (G == 1) {
-        out[(size_t)b * out_stride + (size_t)(g * n_rep + row) * HD + d] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+        out[(size_t)b * out_stride + (size_t)(g * n_rep + row) * HD + d] = __float2bfloat16_rn(den > 0.f ? __fdividef(num, den) : 0.f);
       } else {
         group_o[e] = num;
         if (d == 0) *(float2*)(group_ml + row * 2) = make_float2(M, den);
@@ -724,11 +735,11 @@ decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bf
 #pragma unroll
       for (int c = 0; c < CLUSTER_DECODE_MAX_GROUPS; ++c)             // in group order
         if (c < G) {
-          const float f = (ml[c].x == -INFINITY) ? 0.f : exp2f(ml[c].x - M);
+          const float f = (ml[c].x == -INFINITY) ? 0.f : ex2_fast(ml[c].x - M);
           num += f * po[c];
           den += f * ml[c].y;
         }
-      out[(size_t)b * out_stride + (size_t)(g * n_rep + row) * HD + d] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+      out[(size_t)b * out_stride + (size_t)(g * n_rep + row) * HD + d] = __float2bfloat16_rn(den > 0.f ? __fdividef(num, den) : 0.f);
     }
   }
 }
@@ -888,7 +899,7 @@ static int launch_decode(const void* q, int q_stride, void* out, int out_stride,
                                                         part_o, part_ml, counters, stream);
 }
 
-template <int HD, int STAGES>
+template <int HD, int STAGES, bool GROUPED>
 static int launch_decode_cluster_stages(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                                         const void* v_pages, const int* page_table, int table_width,
                                         const int* ctx_lens, int B, int nh, int nkv, float scale, int window,
@@ -900,15 +911,30 @@ static int launch_decode_cluster_stages(const void* q, int q_stride, void* out, 
   static int configured[MAX_DEVICES];
   if (configured[current_device()] < smem) {
     // clusters of more than 8 CTAs need the kernel's consent
-    cudaError_t e = cudaFuncSetAttribute(decode_cluster_kernel<HD, STAGES>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    cudaError_t e = cudaFuncSetAttribute(decode_cluster_kernel<HD, STAGES, GROUPED>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
     if (e != cudaSuccess) return (int)e;
-    if (int rc = allow_smem(decode_cluster_kernel<HD, STAGES>, smem, configured)) return rc;
+    if (int rc = allow_smem(decode_cluster_kernel<HD, STAGES, GROUPED>, smem, configured)) return rc;
   }
-  wpc::launch_clusters(decode_cluster_kernel<HD, STAGES>, dim3((unsigned)(B * nkv * groups * cluster)), THREADS, smem,
+  wpc::launch_clusters(decode_cluster_kernel<HD, STAGES, GROUPED>, dim3((unsigned)(B * nkv * groups * cluster)), THREADS, smem,
                        stream, (unsigned)cluster, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride,
                        (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, page_table, table_width, ctx_lens,
                        B, nh, nkv, scale * LOG2E, window, cluster, early_pages(), groups, part_o, part_ml, counters);
   return launch_status();
+}
+
+template <int HD, bool GROUPED>
+static int launch_decode_cluster_grouped(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+                                         const void* v_pages, const int* page_table, int table_width,
+                                         const int* ctx_lens, int B, int nh, int nkv, float scale, int window,
+                                         int cluster, int groups, float* part_o, float* part_ml, int* counters,
+                                         cudaStream_t stream) {
+  if (B * nkv * groups * cluster <= sm_count() && DECODE_STAGES_ALONE * 2 * Cfg<HD>::PAGE_ELEMS * 2 <= 215 * 1024)
+    return launch_decode_cluster_stages<HD, DECODE_STAGES_ALONE, GROUPED>(
+        q, q_stride, out, out_stride, k_pages, v_pages, page_table, table_width, ctx_lens, B, nh, nkv, scale, window,
+        cluster, groups, part_o, part_ml, counters, stream);
+  return launch_decode_cluster_stages<HD, DECODE_STAGES_SHARED, GROUPED>(
+      q, q_stride, out, out_stride, k_pages, v_pages, page_table, table_width, ctx_lens, B, nh, nkv, scale, window,
+      cluster, groups, part_o, part_ml, counters, stream);
 }
 
 template <int HD>
@@ -916,15 +942,13 @@ static int launch_decode_cluster(const void* q, int q_stride, void* out, int out
                                  const void* v_pages, const int* page_table, int table_width, const int* ctx_lens,
                                  int B, int nh, int nkv, float scale, int window, int cluster, int groups,
                                  float* part_o, float* part_ml, int* counters, cudaStream_t stream) {
-  if (B * nkv * groups * cluster <= sm_count() && DECODE_STAGES_ALONE * 2 * Cfg<HD>::PAGE_ELEMS * 2 <= 215 * 1024)
-    return launch_decode_cluster_stages<HD, DECODE_STAGES_ALONE>(q, q_stride, out, out_stride, k_pages, v_pages,
-                                                                 page_table, table_width, ctx_lens, B, nh, nkv, scale,
-                                                                 window, cluster, groups, part_o, part_ml, counters,
-                                                                 stream);
-  return launch_decode_cluster_stages<HD, DECODE_STAGES_SHARED>(q, q_stride, out, out_stride, k_pages, v_pages,
-                                                                page_table, table_width, ctx_lens, B, nh, nkv, scale,
-                                                                window, cluster, groups, part_o, part_ml, counters,
-                                                                stream);
+  if (groups > 1)
+    return launch_decode_cluster_grouped<HD, true>(q, q_stride, out, out_stride, k_pages, v_pages, page_table,
+                                                   table_width, ctx_lens, B, nh, nkv, scale, window, cluster, groups,
+                                                   part_o, part_ml, counters, stream);
+  return launch_decode_cluster_grouped<HD, false>(q, q_stride, out, out_stride, k_pages, v_pages, page_table,
+                                                  table_width, ctx_lens, B, nh, nkv, scale, window, cluster, 1,
+                                                  part_o, part_ml, counters, stream);
 }
 
 // How many clusters of `cluster` CTAs of the cluster decode kernel the device holds at once, by
@@ -933,9 +957,9 @@ static int launch_decode_cluster(const void* q, int q_stride, void* out, int out
 template <int HD, int STAGES>
 static int decode_cluster_capacity(int cluster) {
   const int smem = STAGES * 2 * Cfg<HD>::PAGE_ELEMS * 2;
-  cudaError_t e = cudaFuncSetAttribute(decode_cluster_kernel<HD, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  cudaError_t e = cudaFuncSetAttribute(decode_cluster_kernel<HD, STAGES, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(decode_cluster_kernel<HD, STAGES>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    e = cudaFuncSetAttribute(decode_cluster_kernel<HD, STAGES, false>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
   if (e != cudaSuccess) { cudaGetLastError(); return -1; }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(cluster * sm_count()));
@@ -949,7 +973,7 @@ static int decode_cluster_capacity(int cluster) {
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   int n = 0;
-  e = cudaOccupancyMaxActiveClusters(&n, decode_cluster_kernel<HD, STAGES>, &cfg);
+  e = cudaOccupancyMaxActiveClusters(&n, decode_cluster_kernel<HD, STAGES, false>, &cfg);
   if (e != cudaSuccess) { cudaGetLastError(); return -1; }
   return n;
 }
