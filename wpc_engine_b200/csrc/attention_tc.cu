@@ -7,10 +7,11 @@
 //   S = Q K^T      tcgen05.mma, Q [128, hd] and the K page [64, hd] in shared memory (K-major,
 //                  128-byte swizzle), S [128, 64] float32 in tensor memory
 //   softmax        thread r owns row r: tcgen05.ld of its 64 scores, scale, mask, running
-//                  maximum and sum in float32, P = exp2(S - m) as bfloat16 into shared memory
-//   O += P V       tcgen05.mma, P [128, 64] K-major, the V page [64, hd] as it lies in the
-//                  cache (hd contiguous: an MN-major B operand), O [128, hd] float32 in tensor
-//                  memory
+//                  maximum and sum in float32, P = exp2(S - m) as bfloat16 back into tensor
+//                  memory, over the first 32 columns of the scores that it came from
+//   O += P V       tcgen05.mma with the A operand P [128, 64] from tensor memory, the V page
+//                  [64, hd] as it lies in the cache (hd contiguous: an MN-major B operand),
+//                  O [128, hd] float32 in tensor memory
 //
 // The running maximum that the exponentials use is only raised when the true maximum has
 // grown by more than 8 (a factor 256, harmless in float32); then the thread rescales its row
@@ -82,6 +83,16 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint
       ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// D[tmem] (+)= A[tmem] * B[smem]: A is 128 rows (lanes) of packed bfloat16 pairs, 8 columns for K = 16
+__device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                : "memory");
@@ -147,7 +158,6 @@ struct Cfg {
   static constexpr int NB = HD / 64;                      // 64-wide blocks along head_dim
   static constexpr int Q_BYTES = NB * ROWS * 128;
   static constexpr int PAGE_BYTES = NB * PAGE * 128;      // one K or V page
-  static constexpr int P_BYTES = ROWS * 128;
 };
 
 // ---- the kernel -------------------------------------------------------------------------------------
@@ -162,7 +172,7 @@ struct Cfg {
 //   k_empty[NS], v_empty[NS]  MMA (commit) -> TMA     the MMAs that read the page have finished
 //   s_full[NT][2]           MMA (commit) -> softmax   a tile's scores of a page are in tensor memory
 //   s_empty[NT][2]          softmax -> MMA            they have been read (128 arrivals)
-//   p_full[NT]              softmax -> MMA            P is in shared memory and O is rescaled (128)
+//   p_full[NT]              softmax -> MMA            P is in tensor memory and O is rescaled (128)
 //   p_empty[NT]             MMA (commit) -> softmax   P V of the page has finished: P may be
 //                                                     overwritten and O touched
 // While the threads do the softmax of page j the tensor pipe computes the scores of page j + 1
@@ -179,8 +189,8 @@ struct WsCfg {
   static constexpr int TMEM_COLS = NT == 2 ? 512 : 256;   // per tile: two score buffers of 64 and HD for O
   static constexpr int N_BARS = 1 + 4 * NS + 6 * NT;
   // 896 bytes of slack bring the 128-byte aligned start to a 1024-byte boundary; with one tile
-  // two CTAs fit an SM to the byte (2 x (115,712 + 1,024 reserved) = 233,472)
-  static constexpr int SMEM = 896 + NT * C::Q_BYTES + 2 * NS * C::PAGE_BYTES + NT * C::P_BYTES + N_BARS * 8 + 8;
+  // two CTAs fit an SM (tensor memory allows no third: 2 x 256 columns)
+  static constexpr int SMEM = 896 + NT * C::Q_BYTES + 2 * NS * C::PAGE_BYTES + N_BARS * 8 + 8;
 };
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
@@ -240,9 +250,7 @@ prefill_ws_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
   const uint32_t q_s = smem_u32(base);                                 // [NT] tiles of Q
   const uint32_t k_s = q_s + NT * C::Q_BYTES;                          // [NS] pages
   const uint32_t v_s = k_s + NS * C::PAGE_BYTES;                       // [NS] pages
-  uint8_t* p_ptr = base + NT * C::Q_BYTES + 2 * NS * C::PAGE_BYTES;    // [NT] tiles of P
-  const uint32_t p_s = smem_u32(p_ptr);
-  uint64_t* bars = (uint64_t*)(p_ptr + NT * C::P_BYTES);
+  uint64_t* bars = (uint64_t*)(base + NT * C::Q_BYTES + 2 * NS * C::PAGE_BYTES);
   uint64_t *q_full = bars, *k_full = bars + 1, *k_empty = k_full + NS, *v_full = k_empty + NS, *v_empty = v_full + NS,
            *s_full = v_empty + NS /* [NT][2] */, *s_empty = s_full + 2 * NT, *p_full = s_empty + 2 * NT,
            *p_empty = p_full + NT;
@@ -358,7 +366,7 @@ prefill_ws_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
         for (int kc = 0; kc < PAGE / 16; ++kc) {
 #pragma unroll
           for (int t = 0; t < NT; ++t)
-            umma_bf16(tmem_O(t), smem_desc(p_s + t * C::P_BYTES + kc * 32, 16), smem_desc(vb + kc * 2048, PAGE * 128),
+            umma_bf16_ts(tmem_O(t), tmem_S(t, j & 1) + kc * 8, smem_desc(vb + kc * 2048, PAGE * 128),
                       idesc_pv, (j > 0 || kc > 0) ? 1u : 0u);
         }
 #pragma unroll
@@ -377,7 +385,6 @@ prefill_ws_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
     const int p_row = start + t_row;
     const int lo_row = (window > 0 && p_row - window + 1 > 0) ? p_row - window + 1 : 0;
     const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
-    uint8_t* my_p = p_ptr + t * C::P_BYTES;
     {
       const __nv_bfloat16* src = q + (size_t)(tok0 + t_row) * q_stride + (size_t)h_row * HD;
       uint8_t* my_q = base + t * C::Q_BYTES;
@@ -470,10 +477,13 @@ prefill_ws_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
         }
         tmem_st_wait();
       }
-#pragma unroll
-      for (int c = 0; c < 8; ++c)
-        *(uint4*)(my_p + swz(rt, c)) = make_uint4(pw[4 * c], pw[4 * c + 1], pw[4 * c + 2], pw[4 * c + 3]);
-      fence_async_smem();
+      // P goes back into tensor memory, over the first 32 columns of the scores that it came
+      // from (two bfloat16 a column): P V takes its A operand from there.  The MMAs that wrote
+      // those columns and the one that read the weights of two pages ago are done (the scores'
+      // barrier came after them); the scores of the page after next, which will overwrite them,
+      // are issued after this page's P V and run after it.
+      tmem_st32(tmem_S(t, bb) + lane_off, pw);
+      tmem_st_wait();
       fence_before_sync();
       mbar_arrive(p_full + t);
     }
